@@ -1,0 +1,151 @@
+/*
+ * Fused routed-MoE layer entry points (CUDA, sm_100a).
+ *
+ * These have no one-to-one counterpart in the reference: they replace the
+ * *sequences* of operator calls, host scans, copies and stream
+ * synchronisations that the reference engine issues per layer -
+ * decode_routed_layer (k3_engine.cu:1553-1909) and prefill_routed_layer /
+ * prefill_stream_routed_layer / launch_prefill_expert
+ * (k3_engine_prefill.inc:938-997, 1137-1243, 1448-1609) - with device-resident
+ * routing, dispatch and grouped expert products.  Conventions are those of
+ * k3_moe_ops.h: caller-owned device pointers, a cudaStream_t as void *,
+ * bool return, no allocation, no synchronisation.
+ *
+ * The routed experts live in a caller-allocated slot table: six contiguous
+ * arrays holding `local_expert_count` experts, the expert-parallel shard
+ * [local_expert_first, local_expert_first + local_expert_count) of the
+ * layer's `expert_count` experts.  It takes the place of the reference's
+ * per-layer LRU cache slots fed from NVMe (k3_expert_cache.h:43-58,
+ * k3_engine.cu:1696-1822): every expert of the shard is resident.
+ */
+#ifndef K3_MOE_LAYER_H
+#define K3_MOE_LAYER_H
+
+#include <stdbool.h>
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct k3_moe_layer_desc {
+    uint32_t hidden;               /* d: router / expert input and output width   */
+    uint32_t expert_hidden;        /* I: routed expert intermediate width          */
+    uint32_t expert_count;         /* E: experts of the layer (<= 1024)            */
+    uint32_t top_k;                /* <= 32                                        */
+    uint32_t shared_hidden;        /* shared expert intermediate width, 0 = none   */
+    uint32_t q8_block;             /* shared expert quantisation block (32, 128)   */
+    int32_t  q8_scale_type;        /* K3_MOE_Q8_SCALE_F32 / _F16                   */
+    int32_t  activation;           /* K3_MOE_ACT_SITU / _SWIGLU                    */
+    float    beta;                 /* SiTU only                                    */
+    float    linear_beta;          /* SiTU only                                    */
+    float    route_scale;          /* router weight scaling factor (> 0)           */
+    uint32_t local_expert_first;   /* first expert held in the slot table          */
+    uint32_t local_expert_count;   /* experts held in the slot table               */
+    const void *router_weight;     /* bf16 [E, d]                                  */
+    const void *router_bias;       /* f32  [E]                                     */
+    const void *w1_packed;         /* u8 [local, I, d/2]   gate                    */
+    const void *w1_scales;         /* u8 [local, I, d/32]                          */
+    const void *w3_packed;         /* u8 [local, I, d/2]   up                      */
+    const void *w3_scales;         /* u8 [local, I, d/32]                          */
+    const void *w2_packed;         /* u8 [local, d, I/2]   down                    */
+    const void *w2_scales;         /* u8 [local, d, I/32]                          */
+    const void *shared_gate_q;     /* i8 [S, d]                                    */
+    const void *shared_gate_s;     /* scale [S, d/q8_block]                        */
+    const void *shared_up_q;
+    const void *shared_up_s;
+    const void *shared_down_q;     /* i8 [d, S]                                    */
+    const void *shared_down_s;     /* scale [d, S/q8_block]                        */
+} k3_moe_layer_desc;
+
+/* Copy one expert's six tensors into slot `slot` of the table described by
+ * `desc`.  `span` points at the expert's contiguous checkpoint span (host or
+ * device memory) and relative[i] are the byte offsets of w1.packed, w1.scale,
+ * w2.packed, w2.scale, w3.packed, w3.scale inside it - the order and meaning
+ * of k3_engine_expert_layout.relative (k3_engine.cu:105-114, 1038-1065).
+ * Source offsets need no alignment. */
+bool k3_moe_store_admit(const k3_moe_layer_desc *desc, uint32_t slot,
+                        const void *span, const uint64_t relative[6],
+                        void *stream);
+
+/* Bytes of device workspace the layer entry points need for `tokens` rows. */
+size_t k3_moe_layer_workspace_bytes(const k3_moe_layer_desc *desc,
+                                    uint32_t tokens);
+
+/* Token-to-expert dispatch (replaces the host scan of
+ * k3_engine_prefill.inc:1175-1194): from expert_ids u32 [tokens, top_k] build
+ * offsets u32 [experts+1], and for every sorted position p: sorted_route[p] =
+ * token*top_k+rank, sorted_token[p] = token; inv_perm[route] = p.  Order:
+ * expert ascending, route ascending inside an expert. */
+size_t k3_moe_dispatch_workspace_bytes(uint32_t tokens, uint32_t top_k,
+                                       uint32_t experts);
+bool k3_moe_dispatch_build(void *offsets, void *sorted_route,
+                           void *sorted_token, void *inv_perm,
+                           const void *expert_ids, uint32_t tokens,
+                           uint32_t top_k, uint32_t experts, void *workspace,
+                           size_t workspace_bytes, void *stream);
+
+/* Router for `tokens` rows: logits f32 [tokens, E] (scratch, caller-owned),
+ * ids u32 / weights f32 [tokens, top_k].  Replaces the pair
+ * k3_rocm_bf16_gemm_f32 + k3_rocm_router_topk_f32_batch
+ * (k3_engine_prefill.inc:1448-1460). */
+bool k3_moe_route(const k3_moe_layer_desc *desc, void *expert_ids,
+                  void *expert_weights, void *logits, const void *x,
+                  uint32_t tokens, void *stream);
+
+/* Grouped expert products over rows already grouped by expert: rows_in bf16
+ * [rows, d] where rows [offsets[e], offsets[e+1]) belong to local expert e
+ * (offsets has local_expert_count+1 u32 entries on the device).  Computes
+ * gate, up, activation and down for every row (replaces the per-expert
+ * sequence of launch_prefill_expert, k3_engine_prefill.inc:956-990) and
+ * writes rows_out bf16 [rows, d] in the same order.  `act` is scratch bf16
+ * [rows, I]. */
+bool k3_moe_experts_grouped(const k3_moe_layer_desc *desc, void *rows_out,
+                            void *act, const void *rows_in,
+                            const void *offsets, uint32_t rows, void *stream);
+
+/* Shared expert for `tokens` rows: out bf16 [tokens, d]; gate/up/act are
+ * scratch bf16 [tokens, S] (k3_engine_prefill.inc:1530-1551). */
+bool k3_moe_shared_expert(const k3_moe_layer_desc *desc, void *out, void *gate,
+                          void *up, void *act, const void *x, uint32_t tokens,
+                          void *stream);
+
+/* Combine: out[t] = bf16( bf16(sum_r weights[t,r] * rows[index[t*top_k+r]])
+ * + shared[t] ), r ascending; index == NULL means the identity; shared ==
+ * NULL skips the add (k3_engine_prefill.inc:1575-1580, 1598-1603). */
+bool k3_moe_combine(void *out, const void *rows, const void *index,
+                    const void *weights, const void *shared, uint32_t tokens,
+                    uint32_t top_k, uint32_t hidden, void *stream);
+
+/* Whole layer on one GPU holding every expert (local range == all experts):
+ * x bf16 [tokens, d] -> out bf16 [tokens, d].  `workspace` must hold
+ * k3_moe_layer_workspace_bytes(desc, tokens).  When ids_out / weights_out are
+ * non-NULL the routing decision is copied there (u32 / f32 [tokens, top_k]). */
+bool k3_moe_layer_forward(const k3_moe_layer_desc *desc, void *out,
+                          const void *x, uint32_t tokens, void *workspace,
+                          size_t workspace_bytes, void *ids_out,
+                          void *weights_out, void *stream);
+
+/* Seeded synthetic tensor fills used by the tests and the benchmark.  Element
+ * first+i of stream `key` is a pure function of (key, first+i), so a shard of a
+ * tensor can be filled on its own; the numpy mirror lives in
+ * moonshine_b200/synth.py.  `first` must be a multiple of 8 for the byte fills.
+ * bytes: low + floor(b*span/256); int8: uniform in [-127,127];
+ * uniform: low + u*width, u in [0,1) with 24 bits, one rounding per operation,
+ * stored as f32 or (as_f16) f16. */
+bool k3_synth_fill_bytes(void *out, uint64_t count, uint64_t key, uint64_t first,
+                         uint32_t low, uint32_t span, void *stream);
+bool k3_synth_fill_int8(void *out, uint64_t count, uint64_t key, uint64_t first,
+                        void *stream);
+bool k3_synth_fill_uniform(void *out, uint64_t count, uint64_t key,
+                           uint64_t first, float low, float width, int as_f16,
+                           void *stream);
+
+/* Version string of the library. */
+const char *k3_moe_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

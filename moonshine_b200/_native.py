@@ -1,0 +1,94 @@
+"""ctypes binding of the native library ``libk3moe.so`` (built in-tree by
+``moonshine_b200.build``).  There is no fallback: a missing library raises."""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libk3moe.so")
+
+u32, u64, f32, i32, vp, sz = C.c_uint32, C.c_uint64, C.c_float, C.c_int, C.c_void_p, C.c_size_t
+
+
+class LayerDesc(C.Structure):
+    """Mirror of ``k3_moe_layer_desc`` (include/k3_moe_layer.h)."""
+    _fields_ = [
+        ("hidden", u32), ("expert_hidden", u32), ("expert_count", u32), ("top_k", u32),
+        ("shared_hidden", u32), ("q8_block", u32), ("q8_scale_type", C.c_int32),
+        ("activation", C.c_int32), ("beta", f32), ("linear_beta", f32), ("route_scale", f32),
+        ("local_expert_first", u32), ("local_expert_count", u32),
+        ("router_weight", vp), ("router_bias", vp),
+        ("w1_packed", vp), ("w1_scales", vp), ("w3_packed", vp), ("w3_scales", vp),
+        ("w2_packed", vp), ("w2_scales", vp),
+        ("shared_gate_q", vp), ("shared_gate_s", vp), ("shared_up_q", vp), ("shared_up_s", vp),
+        ("shared_down_q", vp), ("shared_down_s", vp),
+    ]
+
+
+_DP = C.POINTER(LayerDesc)
+
+# name -> (restype, argtypes)
+SIGNATURES = {
+    # legacy operator interface
+    "k3_rocm_situ_bf16": (C.c_bool, [vp, vp, vp, u64, f32, f32, vp]),
+    "k3_rocm_mxfp4_gemv_bf16": (C.c_bool, [vp, vp, vp, vp, u32, u32, vp]),
+    "k3_rocm_mxfp4_gemm_bf16": (C.c_bool, [vp, vp, vp, vp, u32, u32, u32, vp]),
+    "k3_rocm_mxfp4_gemm_tiled_bf16": (C.c_bool, [vp, vp, vp, vp, u32, u32, u32, u32, vp]),
+    "k3_rocm_bf16_gemv_bf16": (C.c_bool, [vp, vp, vp, u32, u32, vp]),
+    "k3_rocm_bf16_gemm_tiled_bf16": (C.c_bool, [vp, vp, vp, u32, u32, u32, u32, vp]),
+    "k3_rocm_bf16_gemm_bf16": (C.c_bool, [vp, vp, vp, u32, u32, u32, vp]),
+    "k3_rocm_bf16_gemv_f32": (C.c_bool, [vp, vp, vp, u32, u32, vp]),
+    "k3_rocm_bf16_gemm_f32": (C.c_bool, [vp, vp, vp, u32, u32, u32, vp]),
+    "k3_rocm_bf16_gemm_tiled_f32": (C.c_bool, [vp, vp, vp, u32, u32, u32, u32, vp]),
+    "k3_rocm_bf16_quantize_q8_128": (C.c_bool, [vp, vp, vp, u32, u32, vp]),
+    "k3_rocm_q8_128_dequantize_bf16": (C.c_bool, [vp, vp, vp, u32, u32, vp]),
+    "k3_rocm_q8_128_gemv_bf16": (C.c_bool, [vp, vp, vp, vp, u32, u32, vp]),
+    "k3_rocm_q8_128_gemm_bf16": (C.c_bool, [vp, vp, vp, vp, u32, u32, u32, vp]),
+    "k3_rocm_q8_128_gemm_tiled_bf16": (C.c_bool, [vp, vp, vp, vp, u32, u32, u32, u32, vp]),
+    "k3_rocm_rms_norm_bf16": (C.c_bool, [vp, vp, vp, u32, u32, f32, vp]),
+    "k3_rocm_router_topk_f32": (C.c_bool, [vp, vp, vp, vp, u32, u32, f32, vp]),
+    "k3_rocm_router_topk_f32_batch": (C.c_bool, [vp, vp, vp, vp, u32, u32, u32, f32, vp]),
+    "k3_rocm_weighted_sum_bf16": (C.c_bool, [vp, vp, vp, u32, u32, vp]),
+    "k3_rocm_weighted_sum_bf16_batch": (C.c_bool, [vp, vp, vp, u32, u32, u32, vp]),
+    "k3_rocm_gather_rows_bf16": (C.c_bool, [vp, vp, vp, u32, u32, vp]),
+    "k3_rocm_scatter_rows_bf16": (C.c_bool, [vp, vp, vp, u32, u32, vp]),
+    "k3_rocm_add_bf16": (C.c_bool, [vp, vp, vp, u64, vp]),
+    # generalised operators
+    "k3_moe_activation_bf16": (C.c_bool, [vp, vp, vp, u64, i32, f32, f32, vp]),
+    "k3_moe_q8_quantize": (C.c_bool, [vp, vp, vp, u32, u32, u32, i32, vp]),
+    "k3_moe_q8_gemm_bf16": (C.c_bool, [vp, vp, vp, vp, u32, u32, u32, u32, i32, vp]),
+    # fused layer
+    "k3_moe_store_admit": (C.c_bool, [_DP, u32, vp, C.POINTER(u64), vp]),
+    "k3_moe_layer_workspace_bytes": (sz, [_DP, u32]),
+    "k3_moe_dispatch_workspace_bytes": (sz, [u32, u32, u32]),
+    "k3_moe_dispatch_build": (C.c_bool, [vp, vp, vp, vp, vp, u32, u32, u32, vp, sz, vp]),
+    "k3_moe_route": (C.c_bool, [_DP, vp, vp, vp, vp, u32, vp]),
+    "k3_moe_experts_grouped": (C.c_bool, [_DP, vp, vp, vp, vp, u32, vp]),
+    "k3_moe_shared_expert": (C.c_bool, [_DP, vp, vp, vp, vp, vp, u32, vp]),
+    "k3_moe_combine": (C.c_bool, [vp, vp, vp, vp, vp, u32, u32, u32, vp]),
+    "k3_moe_layer_forward": (C.c_bool, [_DP, vp, vp, u32, vp, sz, vp, vp, vp]),
+    "k3_synth_fill_bytes": (C.c_bool, [vp, u64, u64, u64, u32, u32, vp]),
+    "k3_synth_fill_int8": (C.c_bool, [vp, u64, u64, u64, vp]),
+    "k3_synth_fill_uniform": (C.c_bool, [vp, u64, u64, u64, f32, f32, i32, vp]),
+    "k3_moe_version": (C.c_char_p, []),
+}
+
+_lib = None
+
+
+def lib() -> C.CDLL:
+    """Load the library and attach signatures.  Raises if it was not built."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise RuntimeError(
+                f"{LIB_PATH} is missing: run `python -m moonshine_b200.build` "
+                "(nvcc, sm_100a).  There is no CPU or PyTorch fallback.")
+        handle = C.CDLL(LIB_PATH)
+        for name, (restype, argtypes) in SIGNATURES.items():
+            fn = getattr(handle, name)   # AttributeError if a symbol is missing
+            fn.restype = restype
+            fn.argtypes = argtypes
+        _lib = handle
+    return _lib

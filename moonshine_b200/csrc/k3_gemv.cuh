@@ -1,0 +1,263 @@
+// Bandwidth-bound matrix-vector building blocks shared by the legacy entry
+// points and the fused decode path.
+//
+// MXFP4 rows are consumed in their checkpoint-native form: packed [rows, K/2]
+// (even column = low nibble) and E8M0 scales [rows, K/32].  A warp owns 16
+// rows.  Every lane streams 16-byte nibble chunks (one 32-column scale group)
+// of rows g and g+8, converts them in registers with the hardware
+// e2m1x2 -> f16x2 conversion, and feeds them to mma.sync.m16n8k16 as the A
+// operand.  The B operand is block-diagonal: column n of the MMA carries the
+// activation slice of scale group n only, so after 8 MMAs the accumulator
+// column n holds the fp32 dot product of exactly one 32-column group.  The
+// E8M0 scale (a power of two) is then applied with one fp32 FMA per group into
+// a running fp32 sum - the same "dot per group, scale, accumulate" structure
+// as the reference kernel (k3_rocm_ops.cu:193-273), with the 32 products of a
+// group summed by the tensor core in fp32.
+//
+// Activations are held in shared memory as f16 after an exact power-of-two
+// rescale that maps the vector's largest magnitude into [2^14, 2^15): every
+// bf16 value within 2^28 of the maximum converts without rounding, and the
+// inverse power of two is applied to the final sum.
+#pragma once
+
+#include "k3_common.cuh"
+
+namespace k3 {
+
+constexpr int kGemvWarps = 8;               // warps per CTA
+constexpr int kGemvThreads = kGemvWarps * kWarp;
+constexpr int kGemvKSplit = 4;              // warps sharing one 16-row block along K
+constexpr int kGemvRowBlocks = kGemvWarps / kGemvKSplit;  // 16-row blocks per CTA item
+constexpr int kGemvRowsPerItem = 16 * kGemvRowBlocks;     // 32
+
+K3_DEVINL uint32_t cvt_e2m1x2_to_f16x2(uint32_t byte) {
+    uint32_t out;
+    const uint16_t b = (uint16_t)byte;
+    asm("{ .reg .b8 t; cvt.u8.u16 t, %1; cvt.rn.f16x2.e2m1x2 %0, t; }" : "=r"(out) : "h"(b));
+    return out;
+}
+
+K3_DEVINL void mma_f16_m16n8k16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2,
+                                uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 "
+        "{%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// Stage `nvec` (1 or 2) bf16 vectors of K columns into shared memory as f16,
+// zero padded to k_pad (multiple of 128).  Returns through inv_scale[v] the
+// power of two to multiply final sums with.  All threads of the CTA call it.
+K3_DEVINL void stage_vectors_f16(__half *xs, float *inv_scale, const uint16_t *x0,
+                                 const uint16_t *x1, uint32_t k, uint32_t k_pad,
+                                 float *scratch /* >= 2*warps floats */) {
+    const uint32_t tid = threadIdx.x;
+    const uint32_t nthreads = blockDim.x;
+    const uint16_t *src[2] = {x0, x1};
+    float mx[2] = {0.f, 0.f};
+#pragma unroll
+    for (int v = 0; v < 2; v++) {
+        if (src[v] == nullptr) continue;
+        for (uint32_t i = tid; i < k; i += nthreads) {
+            mx[v] = fmaxf(mx[v], fabsf(bf16_bits_to_float(src[v][i])));
+        }
+        mx[v] = warp_max(mx[v]);
+        if ((tid % kWarp) == 0) scratch[v * (nthreads / kWarp) + tid / kWarp] = mx[v];
+    }
+    __syncthreads();
+    float mul[2];
+#pragma unroll
+    for (int v = 0; v < 2; v++) {
+        float m = 0.f;
+        for (uint32_t w = 0; w < nthreads / kWarp; w++) m = fmaxf(m, scratch[v * (nthreads / kWarp) + w]);
+        int e = 0;
+        if (m > 0.f && m <= 3.0e38f) {
+            e = (int)((__float_as_uint(m) >> 23) & 0xffu) - 127 - 14;
+            e = max(-100, min(100, e));
+        }
+        mul[v] = __uint_as_float((uint32_t)(127 - e) << 23);   // 2^-e
+        if (tid == 0) inv_scale[v] = __uint_as_float((uint32_t)(127 + e) << 23);  // 2^e
+    }
+#pragma unroll
+    for (int v = 0; v < 2; v++) {
+        __half *dst = xs + (size_t)v * k_pad;
+        for (uint32_t i = tid; i < k_pad; i += nthreads) {
+            float val = 0.f;
+            if (src[v] != nullptr && i < k) val = bf16_bits_to_float(src[v][i]) * mul[v];
+            dst[i] = __float2half_rn(val);
+        }
+    }
+    __syncthreads();
+}
+
+// Partial sums of one 16-row block over 128-column steps [step_begin, step_end).
+// sum[0] / sum[1]: rows g / g+8 for the vector this lane accumulates
+// (lanes t=0,1 -> vector 0; t=2,3 -> vector 1), already reduced over the lane
+// pair.  Rows >= rows_valid are clamped (their sums are garbage, not stored).
+template <bool kAligned16>
+K3_DEVINL void mxfp4_rowblock_partial(float (&sum)[2], const uint8_t *packed, const uint8_t *scales,
+                                      uint32_t row0, uint32_t rows_valid_end, uint32_t k,
+                                      uint32_t step_begin, uint32_t step_end, const __half *xs,
+                                      uint32_t k_pad, uint32_t nvec) {
+    const uint32_t lane = threadIdx.x % kWarp;
+    const uint32_t g = lane >> 2, t = lane & 3u;
+    const uint32_t groups = k / 32u;
+    const uint32_t row_a = min(row0 + g, rows_valid_end - 1u);
+    const uint32_t row_b = min(row0 + g + 8u, rows_valid_end - 1u);
+    const uint8_t *pa = packed + (uint64_t)row_a * (k / 2u);
+    const uint8_t *pb = packed + (uint64_t)row_b * (k / 2u);
+    const uint8_t *sa = scales + (uint64_t)row_a * groups;
+    const uint8_t *sb = scales + (uint64_t)row_b * groups;
+    // B operand: lane (g,t) carries data only when (g & 3) == t; vector g >> 2.
+    const uint32_t bvec = g >> 2;
+    const bool b_active = ((g & 3u) == t) && (bvec < nvec);
+    const __half *xv = xs + (size_t)bvec * k_pad + 32u * t;
+    // scale groups this lane applies: 4*step + 2*(t&1) + {0,1}
+    const uint32_t sgrp = 2u * (t & 1u);
+    float acc_a = 0.f, acc_b = 0.f;
+#pragma unroll 2
+    for (uint32_t step = step_begin; step < step_end; step++) {
+        const uint32_t grp = 4u * step + t;       // the group whose nibbles this lane loads
+        uint4 wa = make_uint4(0, 0, 0, 0), wb = make_uint4(0, 0, 0, 0);
+        if (grp < groups) {
+            if (kAligned16) {
+                wa = ld_stream_16(pa + (uint64_t)grp * 16u);
+                wb = ld_stream_16(pb + (uint64_t)grp * 16u);
+            } else {
+                const uint2 a0 = ld_stream_8(pa + (uint64_t)grp * 16u);
+                const uint2 a1 = ld_stream_8(pa + (uint64_t)grp * 16u + 8u);
+                const uint2 b0 = ld_stream_8(pb + (uint64_t)grp * 16u);
+                const uint2 b1 = ld_stream_8(pb + (uint64_t)grp * 16u + 8u);
+                wa = make_uint4(a0.x, a0.y, a1.x, a1.y);
+                wb = make_uint4(b0.x, b0.y, b1.x, b1.y);
+            }
+        }
+        uint32_t xr[16];
+        if (b_active) {
+            const uint4 *p = reinterpret_cast<const uint4 *>(xv + 128u * step);
+#pragma unroll
+            for (int q = 0; q < 4; q++) {
+                const uint4 v = p[q];
+                xr[4 * q + 0] = v.x; xr[4 * q + 1] = v.y; xr[4 * q + 2] = v.z; xr[4 * q + 3] = v.w;
+            }
+        } else {
+#pragma unroll
+            for (int q = 0; q < 16; q++) xr[q] = 0u;
+        }
+        // scales of the two groups this lane finishes, rows a and b
+        const uint32_t g0 = 4u * step + sgrp;
+        float s_a0 = 0.f, s_a1 = 0.f, s_b0 = 0.f, s_b1 = 0.f;
+        if (g0 < groups) { s_a0 = e8m0_to_float(sa[g0]); s_b0 = e8m0_to_float(sb[g0]); }
+        if (g0 + 1u < groups) { s_a1 = e8m0_to_float(sa[g0 + 1u]); s_b1 = e8m0_to_float(sb[g0 + 1u]); }
+
+        float c[4] = {0.f, 0.f, 0.f, 0.f};
+        const uint32_t wa_w[4] = {wa.x, wa.y, wa.z, wa.w};
+        const uint32_t wb_w[4] = {wb.x, wb.y, wb.z, wb.w};
+#pragma unroll
+        for (int j = 0; j < 8; j++) {
+            const uint32_t word_a = wa_w[j >> 1], word_b = wb_w[j >> 1];
+            const uint32_t sh = (j & 1) * 16;
+            const uint32_t a0 = cvt_e2m1x2_to_f16x2((word_a >> sh) & 0xffu);
+            const uint32_t a2 = cvt_e2m1x2_to_f16x2((word_a >> (sh + 8)) & 0xffu);
+            const uint32_t a1 = cvt_e2m1x2_to_f16x2((word_b >> sh) & 0xffu);
+            const uint32_t a3 = cvt_e2m1x2_to_f16x2((word_b >> (sh + 8)) & 0xffu);
+            mma_f16_m16n8k16(c, a0, a1, a2, a3, xr[2 * j], xr[2 * j + 1]);
+        }
+        acc_a = fmaf(s_a0, c[0], acc_a);
+        acc_a = fmaf(s_a1, c[1], acc_a);
+        acc_b = fmaf(s_b0, c[2], acc_b);
+        acc_b = fmaf(s_b1, c[3], acc_b);
+    }
+    // lanes t and t^1 hold the two halves of the same vector
+    acc_a += __shfl_xor_sync(0xffffffffu, acc_a, 1);
+    acc_b += __shfl_xor_sync(0xffffffffu, acc_b, 1);
+    sum[0] = acc_a;
+    sum[1] = acc_b;
+}
+
+// One CTA item: two 16-row blocks, each with its own matrix / first row, K
+// split over 4 warps per block.  Results (fp32, already multiplied by
+// inv_scale) land in out_s[vec][32] (block 0 -> entries 0..15, block 1 ->
+// 16..31) in shared memory; a __syncthreads() separates them from the caller's
+// epilogue.  red must hold kGemvWarps*32 floats.
+struct RowBlock {
+    const uint8_t *packed;
+    const uint8_t *scales;
+    uint32_t row0;       // first row of the block
+    uint32_t rows_end;   // rows in the matrix (block is skipped if row0 >= rows_end)
+};
+
+template <bool kAligned16>
+K3_DEVINL void mxfp4_item_2x16(float *out_s /* [2][32] */, float *red, const RowBlock &b0,
+                               const RowBlock &b1, uint32_t k, const __half *xs, uint32_t k_pad,
+                               uint32_t nvec, const float *inv_scale) {
+    const uint32_t warp = threadIdx.x / kWarp;
+    const uint32_t lane = threadIdx.x % kWarp;
+    const uint32_t rb = warp / kGemvKSplit;       // row block inside the item
+    const uint32_t ks = warp % kGemvKSplit;       // K split index
+    const uint32_t steps = k_pad / 128u;
+    const uint32_t per = (steps + kGemvKSplit - 1) / kGemvKSplit;
+    const uint32_t sb = min(steps, ks * per), se = min(steps, sb + per);
+    const RowBlock &b = rb == 0u ? b0 : b1;
+    float sum[2] = {0.f, 0.f};
+    if (b.row0 < b.rows_end) {
+        mxfp4_rowblock_partial<kAligned16>(sum, b.packed, b.scales, b.row0, b.rows_end, k, sb, se,
+                                           xs, k_pad, nvec);
+    }
+    const uint32_t g = lane >> 2, t = lane & 3u;
+    if ((t & 1u) == 0u) {
+        const uint32_t vec = t >> 1;
+        red[((warp * 2u + vec) * 16u) + g] = sum[0];
+        red[((warp * 2u + vec) * 16u) + g + 8u] = sum[1];
+    }
+    __syncthreads();
+    // 64 outputs (2 vectors x 32 rows): sum the K splits in ascending order
+    if (threadIdx.x < 64u) {
+        const uint32_t vec = threadIdx.x >> 5, r = threadIdx.x & 31u;
+        const uint32_t block = r >> 4, rr = r & 15u;
+        float total = 0.f;
+#pragma unroll
+        for (uint32_t s = 0; s < (uint32_t)kGemvKSplit; s++) {
+            total += red[(((block * kGemvKSplit + s) * 2u + vec) * 16u) + rr];
+        }
+        out_s[vec * 32u + r] = total * inv_scale[vec];
+    }
+    __syncthreads();
+}
+
+template <bool kAligned16>
+K3_DEVINL void mxfp4_item_32rows(float *out_s, float *red, const uint8_t *packed,
+                                 const uint8_t *scales, uint32_t row0, uint32_t rows_end,
+                                 uint32_t k, const __half *xs, uint32_t k_pad, uint32_t nvec,
+                                 const float *inv_scale) {
+    const RowBlock b0{packed, scales, row0, rows_end};
+    const RowBlock b1{packed, scales, row0 + 16u, rows_end};
+    mxfp4_item_2x16<kAligned16>(out_s, red, b0, b1, k, xs, k_pad, nvec, inv_scale);
+}
+
+// Shared-memory layout used by every kernel built on the item routine.
+struct GemvSmem {
+    __half *xs;        // [2][k_pad]
+    float *red;        // [kGemvWarps*32]
+    float *out_s;      // [64]
+    float *inv_scale;  // [2]
+    float *scratch;    // [2*kGemvWarps]
+};
+
+K3_DEVINL GemvSmem carve_gemv_smem(unsigned char *raw, uint32_t k_pad) {
+    GemvSmem s;
+    s.xs = reinterpret_cast<__half *>(raw);
+    s.red = reinterpret_cast<float *>(raw + (size_t)2 * k_pad * sizeof(__half));
+    s.out_s = s.red + kGemvWarps * 32;
+    s.inv_scale = s.out_s + 64;
+    s.scratch = s.inv_scale + 2;
+    return s;
+}
+
+inline size_t gemv_smem_bytes(uint32_t k_pad) {
+    return (size_t)2 * k_pad * sizeof(__half) +
+           (size_t)(kGemvWarps * 32 + 64 + 2 + 2 * kGemvWarps) * sizeof(float);
+}
+
+}  // namespace k3

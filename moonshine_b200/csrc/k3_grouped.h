@@ -1,0 +1,25 @@
+// Internal interface between the layer composition and the tensor-core
+// (tcgen05) GEMM kernels.  Each function picks the tensor-core kernel when the
+// shape, alignment and row count suit it and otherwise runs the exact-order
+// SIMT kernel behind the legacy entry points.
+#pragma once
+
+#include "k3_moe_layer.h"
+
+#include <stdint.h>
+
+// logits f32 [tokens, rows] = x bf16 [tokens, cols] * W bf16 [rows, cols]^T
+bool k3_grouped_dense_bf16_f32(void *out, const void *weights, const void *x, uint32_t tokens,
+                               uint32_t rows, uint32_t cols, void *stream);
+
+// out bf16 [tokens, rows] = x bf16 [tokens, cols] * dequant(q, scales)^T
+bool k3_grouped_q8_bf16(void *out, const void *q, const void *scales, const void *x,
+                        uint32_t tokens, uint32_t rows, uint32_t cols, uint32_t block,
+                        int scale_type, void *stream);
+
+// true when the grouped tensor-core path can run this layer / row count
+bool k3_grouped_tc_supported(const k3_moe_layer_desc *desc, uint32_t rows);
+
+// gate/up + activation and down over rows grouped by local expert
+bool k3_grouped_tc_experts(const k3_moe_layer_desc *desc, void *rows_out, void *act,
+                           const void *rows_in, const void *offsets, uint32_t rows, void *stream);
