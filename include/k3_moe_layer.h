@@ -127,6 +127,25 @@ bool k3_moe_layer_forward(const k3_moe_layer_desc *desc, void *out,
                           size_t workspace_bytes, void *ids_out,
                           void *weights_out, void *stream);
 
+/* Same as k3_moe_layer_forward, recording caller-created cudaEvent_t handles
+ * (as void *, NULL entries skipped) on `stream` at the phase boundaries:
+ * events[0] start, [1] router done, [2] shared expert done, [3] dispatch and
+ * row gather done, [4] grouped expert products done, [5] combine done.  This is
+ * the device-timed form of the reference's host phase ledger
+ * (router_seconds, routed_expert_pipeline_seconds, moe_tail_seconds of
+ * k3_engine_prefill_stats, k3_engine.h:69-99). */
+bool k3_moe_layer_forward_events(const k3_moe_layer_desc *desc, void *out,
+                                 const void *x, uint32_t tokens,
+                                 void *workspace, size_t workspace_bytes,
+                                 void *const *events, void *stream);
+
+/* Event helpers for hosts without CUDA runtime bindings: create / destroy a
+ * timing event and read the milliseconds between two recorded events (waits
+ * for `end`; negative on error). */
+void *k3_moe_event_create(void);
+void k3_moe_event_destroy(void *event);
+float k3_moe_event_elapsed_ms(void *begin, void *end);
+
 /* Seeded synthetic tensor fills used by the tests and the benchmark.  Element
  * first+i of stream `key` is a pure function of (key, first+i), so a shard of a
  * tensor can be filled on its own; the numpy mirror lives in

@@ -68,6 +68,10 @@ SIGNATURES = {
     "k3_moe_shared_expert": (C.c_bool, [_DP, vp, vp, vp, vp, vp, u32, vp]),
     "k3_moe_combine": (C.c_bool, [vp, vp, vp, vp, vp, u32, u32, u32, vp]),
     "k3_moe_layer_forward": (C.c_bool, [_DP, vp, vp, u32, vp, sz, vp, vp, vp]),
+    "k3_moe_layer_forward_events": (C.c_bool, [_DP, vp, vp, u32, vp, sz, C.POINTER(vp), vp]),
+    "k3_moe_event_create": (vp, []),
+    "k3_moe_event_destroy": (None, [vp]),
+    "k3_moe_event_elapsed_ms": (f32, [vp, vp]),
     "k3_synth_fill_bytes": (C.c_bool, [vp, u64, u64, u64, u32, u32, vp]),
     "k3_synth_fill_int8": (C.c_bool, [vp, u64, u64, u64, vp]),
     "k3_synth_fill_uniform": (C.c_bool, [vp, u64, u64, u64, f32, f32, i32, vp]),

@@ -356,9 +356,16 @@ extern "C" bool k3_moe_combine(void *out, const void *rows, const void *index,
     return launch_ok();
 }
 
-extern "C" bool k3_moe_layer_forward(const k3_moe_layer_desc *d, void *out, const void *x,
-                                     uint32_t tokens, void *workspace, size_t workspace_bytes,
-                                     void *ids_out, void *weights_out, void *stream_pointer) {
+namespace {
+
+bool mark(void *const *events, int index, cudaStream_t stream) {
+    if (!events || !events[index]) return true;
+    return cudaEventRecord((cudaEvent_t)events[index], stream) == cudaSuccess;
+}
+
+bool layer_forward_impl(const k3_moe_layer_desc *d, void *out, const void *x, uint32_t tokens,
+                        void *workspace, size_t workspace_bytes, void *ids_out,
+                        void *weights_out, void *const *events, void *stream_pointer) {
     if (!desc_ok(d) || !out || !x || tokens == 0 || tokens > 65535u || !workspace ||
         d->local_expert_first != 0 || d->local_expert_count != d->expert_count ||
         !slot_pointers_aligned(d)) {
@@ -369,14 +376,18 @@ extern "C" bool k3_moe_layer_forward(const k3_moe_layer_desc *d, void *out, cons
     cudaStream_t stream = (cudaStream_t)stream_pointer;
     const uint32_t routes = tokens * d->top_k;
 
+    if (!mark(events, 0, stream)) return false;
     if (!k3_moe_route(d, w.ids, w.weights, w.logits, x, tokens, stream)) return false;
+    if (!mark(events, 1, stream)) return false;
     if (d->shared_hidden &&
         !k3_moe_shared_expert(d, w.sh_out, w.sh_gate, w.sh_up, w.sh_act, x, tokens, stream)) {
         return false;
     }
+    if (!mark(events, 2, stream)) return false;
     const uint32_t *index = nullptr;
     if (tokens == 1u) {
         // one token: every selected expert reads the same row; rows stay in rank order
+        if (!mark(events, 3, stream)) return false;
         if (!launch_grouped_rows(d, w.rows_out, w.act, x, nullptr, w.ids, d->top_k, true, stream)) {
             return false;
         }
@@ -384,23 +395,70 @@ extern "C" bool k3_moe_layer_forward(const k3_moe_layer_desc *d, void *out, cons
         if (!k3_moe_dispatch_build(w.offsets, w.sorted_route, w.sorted_token, w.inv_perm, w.ids,
                                    tokens, d->top_k, d->expert_count, w.dispatch_ws,
                                    w.dispatch_bytes, stream) ||
-            !k3_rocm_gather_rows_bf16(w.rows_in, x, w.sorted_token, routes, d->hidden, stream) ||
-            !k3_moe_experts_grouped(d, w.rows_out, w.act, w.rows_in, w.offsets, routes, stream)) {
+            !k3_rocm_gather_rows_bf16(w.rows_in, x, w.sorted_token, routes, d->hidden, stream)) {
+            return false;
+        }
+        if (!mark(events, 3, stream)) return false;
+        if (!k3_moe_experts_grouped(d, w.rows_out, w.act, w.rows_in, w.offsets, routes, stream)) {
             return false;
         }
         index = w.inv_perm;
     }
+    if (!mark(events, 4, stream)) return false;
     if (!k3_moe_combine(out, w.rows_out, index, w.weights, d->shared_hidden ? w.sh_out : nullptr,
                         tokens, d->top_k, d->hidden, stream)) {
         return false;
     }
-    if (ids_out && cudaMemcpyAsync(ids_out, w.ids, (size_t)routes * 4u, cudaMemcpyDeviceToDevice,
+    if (!mark(events, 5, stream)) return false;
+    if (ids_out && cudaMemcpyAsync(ids_out, w.ids, (size_t)routes * 4u, cudaMemcpyDefault,
                                    stream) != cudaSuccess) {
         return false;
     }
     if (weights_out && cudaMemcpyAsync(weights_out, w.weights, (size_t)routes * 4u,
-                                       cudaMemcpyDeviceToDevice, stream) != cudaSuccess) {
+                                       cudaMemcpyDefault, stream) != cudaSuccess) {
         return false;
     }
     return true;
+}
+
+}  // namespace
+
+extern "C" bool k3_moe_layer_forward(const k3_moe_layer_desc *d, void *out, const void *x,
+                                     uint32_t tokens, void *workspace, size_t workspace_bytes,
+                                     void *ids_out, void *weights_out, void *stream) {
+    return layer_forward_impl(d, out, x, tokens, workspace, workspace_bytes, ids_out, weights_out,
+                              nullptr, stream);
+}
+
+extern "C" bool k3_moe_layer_forward_events(const k3_moe_layer_desc *d, void *out, const void *x,
+                                            uint32_t tokens, void *workspace,
+                                            size_t workspace_bytes, void *const *events,
+                                            void *stream) {
+    return layer_forward_impl(d, out, x, tokens, workspace, workspace_bytes, nullptr, nullptr,
+                              events, stream);
+}
+
+// Thin wrappers so a host language without CUDA runtime bindings can own the
+// events it hands to k3_moe_layer_forward_events.
+extern "C" void *k3_moe_event_create(void) {
+    cudaEvent_t e = nullptr;
+    if (cudaEventCreate(&e) != cudaSuccess) {
+        (void)cudaGetLastError();
+        return nullptr;
+    }
+    return (void *)e;
+}
+
+extern "C" void k3_moe_event_destroy(void *event) {
+    if (event) (void)cudaEventDestroy((cudaEvent_t)event);
+}
+
+extern "C" float k3_moe_event_elapsed_ms(void *begin, void *end) {
+    float ms = -1.0f;
+    if (!begin || !end || cudaEventSynchronize((cudaEvent_t)end) != cudaSuccess ||
+        cudaEventElapsedTime(&ms, (cudaEvent_t)begin, (cudaEvent_t)end) != cudaSuccess) {
+        (void)cudaGetLastError();
+        return -1.0f;
+    }
+    return ms;
 }

@@ -125,5 +125,29 @@ class MoELayer:
             raise RuntimeError("k3_moe_layer_forward failed")
         return (out, ids, wts) if want_routes else out
 
+    def phase_times(self, x: torch.Tensor, steps: int = 5) -> dict:
+        """Average device time of each phase over ``steps`` passes, from CUDA events
+        recorded by the library on the launching stream."""
+        tokens = x.shape[0]
+        self.reserve(tokens)
+        out = torch.empty_like(x)
+        names = ["router_ms", "shared_ms", "dispatch_ms", "experts_ms", "combine_ms"]
+        total = dict.fromkeys(names, 0.0)
+        events = [ops.k3_moe_event_create() for _ in range(6)]
+        if not all(events):
+            raise RuntimeError("cudaEventCreate failed")
+        arr = (C.c_void_p * 6)(*events)
+        try:
+            for _ in range(steps):
+                if not ops.k3_moe_layer_forward_events(self.desc, out, x, tokens, self.workspace,
+                                                       self.workspace.numel(), arr):
+                    raise RuntimeError("k3_moe_layer_forward_events failed")
+                for i, name in enumerate(names):
+                    total[name] += ops.k3_moe_event_elapsed_ms(events[i], events[i + 1])
+        finally:
+            for e in events:
+                ops.k3_moe_event_destroy(e)
+        return {k: v / steps for k, v in total.items()}
+
     def weight_bytes(self) -> int:
         return sum(v.numel() * v.element_size() for v in self.t.values())

@@ -6,7 +6,7 @@ DEV = "cuda:0"
 
 
 def dev(a):
-    a = np.ascontiguousarray(a)
+    a = np.array(a, copy=True)
     if a.dtype == np.uint16:
         return torch.from_numpy(a.view(np.int16)).to(DEV)
     if a.dtype == np.uint32:
