@@ -139,6 +139,11 @@ bool k3_moe_layer_forward_events(const k3_moe_layer_desc *desc, void *out,
                                  void *workspace, size_t workspace_bytes,
                                  void *const *events, void *stream);
 
+/* Device-side status of the tensor-core kernels since the library was loaded:
+ * 0 = ok, 1 = a bounded barrier wait gave up (the launch's output is then
+ * undefined).  Synchronises with the device. */
+uint32_t k3_moe_device_status(void);
+
 /* Event helpers for hosts without CUDA runtime bindings: create / destroy a
  * timing event and read the milliseconds between two recorded events (waits
  * for `end`; negative on error). */

@@ -69,6 +69,7 @@ SIGNATURES = {
     "k3_moe_combine": (C.c_bool, [vp, vp, vp, vp, vp, u32, u32, u32, vp]),
     "k3_moe_layer_forward": (C.c_bool, [_DP, vp, vp, u32, vp, sz, vp, vp, vp]),
     "k3_moe_layer_forward_events": (C.c_bool, [_DP, vp, vp, u32, vp, sz, C.POINTER(vp), vp]),
+    "k3_moe_device_status": (u32, []),
     "k3_moe_event_create": (vp, []),
     "k3_moe_event_destroy": (None, [vp]),
     "k3_moe_event_elapsed_ms": (f32, [vp, vp]),
