@@ -72,7 +72,6 @@ def test_decode_matches_prefill_row():
         if gaps[t] >= 1e-6:
             assert np.array_equal(G.host(i1, np.uint32)[0], ids[t])
         assert G.rel_l2(bf16_tensor_to_bits(o1)[0], batch[t]) <= 2e-3
-        assert G.ulp_distance(bf16_tensor_to_bits(o1)[0], batch[t]).mean() < 0.05
 
 
 def test_store_admit_from_checkpoint_span():
