@@ -86,6 +86,27 @@ bool k3_moe_dispatch_build(void *offsets, void *sorted_route,
                            uint32_t top_k, uint32_t experts, void *workspace,
                            size_t workspace_bytes, void *stream);
 
+/* Dispatch without a caller workspace.  No counterpart in the reference.
+ * For hosts that may not allocate device memory (a plugin inside an engine
+ * that carved all of its memory at start-up, or a call made while allocation
+ * is off limits): the per-chunk histograms live in a fixed array of about
+ * 1 MiB inside the library's device image, present once on every GPU that
+ * loads the library until the process exits.  Same outputs as
+ * k3_moe_dispatch_build.  Limits: tokens*top_k <= 131072 (also returned by
+ * k3_moe_dispatch_noalloc_max_routes) and experts <= 1024; anything larger
+ * returns false with a message in `error` (optional, NUL-terminated) and
+ * launches nothing.  All calls on a GPU share the array: calls whose kernels
+ * may overlap on the GPU race and must be serialised by the caller.  The
+ * first call on each GPU resolves the array's device address and should be
+ * made outside stream capture.  Never calls cudaMalloc or cudaFree. */
+size_t k3_moe_dispatch_noalloc_max_routes(void);
+bool k3_moe_dispatch_build_noalloc(void *offsets, void *sorted_route,
+                                   void *sorted_token, void *inv_perm,
+                                   const void *expert_ids, uint32_t tokens,
+                                   uint32_t top_k, uint32_t experts,
+                                   char *error, size_t error_size,
+                                   void *stream);
+
 /* Router for `tokens` rows: logits f32 [tokens, E] (scratch, caller-owned),
  * ids u32 / weights f32 [tokens, top_k].  Replaces the pair
  * k3_rocm_bf16_gemm_f32 + k3_rocm_router_topk_f32_batch

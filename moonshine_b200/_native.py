@@ -63,6 +63,8 @@ SIGNATURES = {
     "k3_moe_layer_workspace_bytes": (sz, [_DP, u32]),
     "k3_moe_dispatch_workspace_bytes": (sz, [u32, u32, u32]),
     "k3_moe_dispatch_build": (C.c_bool, [vp, vp, vp, vp, vp, u32, u32, u32, vp, sz, vp]),
+    "k3_moe_dispatch_noalloc_max_routes": (sz, []),
+    "k3_moe_dispatch_build_noalloc": (C.c_bool, [vp, vp, vp, vp, vp, u32, u32, u32, C.c_char_p, sz, vp]),
     "k3_moe_route": (C.c_bool, [_DP, vp, vp, vp, vp, u32, vp]),
     "k3_moe_experts_grouped": (C.c_bool, [_DP, vp, vp, vp, vp, u32, vp]),
     "k3_moe_shared_expert": (C.c_bool, [_DP, vp, vp, vp, vp, vp, u32, vp]),

@@ -161,3 +161,116 @@ extern "C" bool k3_moe_dispatch_build(void *offsets, void *sorted_route, void *s
         (const uint32_t *)offsets, (const uint32_t *)expert_ids, routes, experts, chunks, top_k);
     return launch_ok();
 }
+
+// ---------------------------------------------------------------------------
+// Dispatch for callers that cannot allocate device memory.
+//
+// Some hosts of this library never get to call cudaMalloc themselves: a plugin
+// loaded into an engine whose memory pool was sized and handed out at start-up
+// (the reference engine does exactly that: every buffer is carved from one
+// preflighted allocation and the operators "never allocate"), or a call site
+// that runs while allocation is forbidden.  k3_moe_dispatch_build needs a
+// caller-supplied workspace for its per-chunk histograms; this variant keeps
+// that workspace in a fixed array inside the library's device image instead.
+// The array exists once per GPU that loads the library, for the life of the
+// process, and costs kNoAllocScratchBytes (about 1 MiB) of device memory there.
+//
+// Limits and rules:
+//   * tokens * top_k <= kNoAllocMaxRoutes (131072) and experts <= 1024; larger
+//     problems are refused with a message, nothing is launched.
+//   * All calls on one GPU share the array.  Two calls whose kernels overlap in
+//     time (different streams, or different host threads) corrupt each other's
+//     histograms: serialise them on one stream.  The array keeps the previous
+//     call's contents; the status words are cleared and every histogram entry
+//     a call reads is rewritten by that call first.
+//   * The first call on each GPU looks up the array's device address
+//     (cudaGetSymbolAddress, with that GPU current).  Make that first call
+//     outside any stream capture.
+// No cudaMalloc, cudaFree or other allocating routine is called.
+constexpr uint32_t kNoAllocMaxRoutes = 131072;
+constexpr uint32_t kNoAllocMaxChunks = kNoAllocMaxRoutes / kChunk;
+constexpr size_t kNoAllocScratchBytes = 256 + (size_t)kNoAllocMaxChunks * kMaxExperts * sizeof(uint32_t);
+
+static __device__ __align__(256) unsigned char g_dispatch_scratch[kNoAllocScratchBytes];
+
+namespace {
+
+constexpr int kMaxDevices = 64;
+void *g_scratch_address[kMaxDevices] = {};   // device address of g_dispatch_scratch, per GPU
+
+void set_error(char *error, size_t error_size, const char *message) {
+    if (!error || error_size == 0) return;
+    size_t i = 0;
+    for (; message[i] != '\0' && i + 1 < error_size; i++) error[i] = message[i];
+    error[i] = '\0';
+}
+
+// The array's name is only a host-side handle: kernels must be given the address
+// cudaGetSymbolAddress reports for the current device.
+void *scratch_for_current_device(char *error, size_t error_size) {
+    int device = -1;
+    if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= kMaxDevices) {
+        (void)cudaGetLastError();
+        set_error(error, error_size, "no current CUDA device (or ordinal >= 64)");
+        return nullptr;
+    }
+    if (g_scratch_address[device] == nullptr) {
+        void *address = nullptr;
+        if (cudaGetSymbolAddress(&address, g_dispatch_scratch) != cudaSuccess || !address) {
+            (void)cudaGetLastError();
+            set_error(error, error_size, "cudaGetSymbolAddress failed for the dispatch scratch");
+            return nullptr;
+        }
+        g_scratch_address[device] = address;
+    }
+    return g_scratch_address[device];
+}
+
+}  // namespace
+
+extern "C" size_t k3_moe_dispatch_noalloc_max_routes(void) { return kNoAllocMaxRoutes; }
+
+extern "C" bool k3_moe_dispatch_build_noalloc(void *offsets, void *sorted_route,
+                                              void *sorted_token, void *inv_perm,
+                                              const void *expert_ids, uint32_t tokens,
+                                              uint32_t top_k, uint32_t experts, char *error,
+                                              size_t error_size, void *stream_pointer) {
+    set_error(error, error_size, "");
+    if (!offsets || !sorted_route || !sorted_token || !inv_perm || !expert_ids || tokens == 0u ||
+        top_k == 0u || experts == 0u) {
+        set_error(error, error_size, "null pointer or zero size");
+        return false;
+    }
+    const uint64_t routes64 = (uint64_t)tokens * top_k;
+    if (routes64 > kNoAllocMaxRoutes || experts > kMaxExperts) {
+        set_error(error, error_size,
+                  "problem exceeds the built-in scratch: tokens*top_k must be <= 131072 and "
+                  "experts <= 1024; use k3_moe_dispatch_build with a caller workspace");
+        return false;
+    }
+    unsigned char *scratch = (unsigned char *)scratch_for_current_device(error, error_size);
+    if (!scratch) return false;
+    const uint32_t routes = (uint32_t)routes64;
+    const uint32_t chunks = (routes + kChunk - 1) / kChunk;
+    cudaStream_t stream = (cudaStream_t)stream_pointer;
+    uint32_t *error_flag = (uint32_t *)scratch;                 // status words, must start at zero
+    uint32_t *hist = (uint32_t *)(scratch + 256);               // rewritten below before it is read
+    if (cudaMemsetAsync(error_flag, 0, 256, stream) != cudaSuccess) {
+        (void)cudaGetLastError();
+        set_error(error, error_size, "cudaMemsetAsync of the status words failed");
+        return false;
+    }
+    const uint32_t blocks = (chunks + kWarpsPerBlock - 1) / kWarpsPerBlock;
+    const size_t smem = (size_t)kWarpsPerBlock * experts * sizeof(uint32_t);
+    route_hist_kernel<<<blocks, kWarpsPerBlock * 32, smem, stream>>>(
+        hist, (const uint32_t *)expert_ids, routes, experts, chunks, error_flag);
+    route_scan_kernel<<<1, kMaxExperts, 0, stream>>>(hist, (uint32_t *)offsets, experts, chunks);
+    route_place_kernel<<<blocks, kWarpsPerBlock * 32, smem, stream>>>(
+        (uint32_t *)sorted_route, (uint32_t *)sorted_token, (uint32_t *)inv_perm, hist,
+        (const uint32_t *)offsets, (const uint32_t *)expert_ids, routes, experts, chunks, top_k);
+    if (!launch_ok()) {
+        set_error(error, error_size, "kernel launch failed");
+        return false;
+    }
+    return true;
+}
