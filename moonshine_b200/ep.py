@@ -1,0 +1,204 @@
+"""Expert-parallel routed-MoE layer over ``torch.distributed``.
+
+Partitioning: tokens data-parallel (rank r owns the contiguous rows
+[r*T/G, (r+1)*T/G)), experts expert-parallel (rank g holds the contiguous
+experts [g*E/G, (g+1)*E/G) in its HBM slot table).  Router, top-k and the
+shared expert are computed where the token lives.  Per layer there is one
+exchange step each way:
+
+  1. route + dispatch on the source: rows sorted (expert asc, route asc); the
+     rows for destination g are one contiguous slice because experts are
+     contiguous per rank;
+  2. all-to-all of the per-destination row counts, of the rows' expert ids, and
+     of the bf16 rows themselves (``all_to_all_single`` with uneven splits);
+  3. on the destination a second dispatch (one "route" per received row) orders
+     the rows (expert asc, source rank asc, route asc) - with the contiguous
+     token partition this is exactly the single-GPU grouping order - and the
+     grouped expert products run on the local shard;
+  4. rows go back through the inverse permutation and the reverse all-to-all;
+  5. combine on the source in rank order (same arithmetic as one GPU).
+
+The arithmetic is delegated to a *backend*: ``NativeBackend`` calls the CUDA
+library; tests pass a CPU backend to exercise this file's exchange logic with
+``gloo`` ranks.  No collective is used beyond the all-to-alls above.
+"""
+from __future__ import annotations
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+from . import ops, synth
+from .layer import MoELayer
+
+
+def shard_range(experts: int, world: int, rank: int) -> tuple[int, int]:
+    if experts % world != 0:
+        raise ValueError("expert count must divide evenly over the ranks")
+    per = experts // world
+    return rank * per, per
+
+
+def destination_splits(offsets: torch.Tensor, experts: int, world: int) -> list[int]:
+    """Rows this rank sends to each destination, from the expert offsets [E+1]."""
+    per = experts // world
+    bounds = offsets[::per][: world + 1].to("cpu", torch.int64)
+    return [int(bounds[g + 1] - bounds[g]) for g in range(world)]
+
+
+class NativeBackend:
+    """Arithmetic on the GPU through the C-ABI (one MoELayer holding the shard)."""
+
+    def __init__(self, layer: MoELayer):
+        self.layer = layer
+        self.cfg = layer.cfg
+        self.device = layer.device
+        self._bufs = {}
+
+    def _buf(self, name, shape, dtype):
+        t = self._bufs.get(name)
+        n = int(np.prod(shape))
+        if t is None or t.numel() < n or t.dtype != dtype:
+            t = torch.empty(max(n, 1), dtype=dtype, device=self.device)
+            self._bufs[name] = t
+        return t[:n].view(*shape)
+
+    def route(self, x):
+        t, k, e = x.shape[0], self.cfg["top_k"], self.cfg["experts"]
+        ids = self._buf("ids", (t, k), torch.int32)
+        w = self._buf("w", (t, k), torch.float32)
+        logits = self._buf("logits", (t, e), torch.float32)
+        if not ops.k3_moe_route(self.layer.desc, ids, w, logits, x, t):
+            raise RuntimeError("k3_moe_route failed")
+        return ids, w
+
+    def dispatch(self, ids, tokens, top_k, experts, tag):
+        routes = tokens * top_k
+        offsets = self._buf(tag + "off", (experts + 1,), torch.int32)
+        sr = self._buf(tag + "sr", (routes,), torch.int32)
+        st = self._buf(tag + "st", (routes,), torch.int32)
+        inv = self._buf(tag + "inv", (routes,), torch.int32)
+        nbytes = ops.k3_moe_dispatch_workspace_bytes(tokens, top_k, experts)
+        ws = self._buf(tag + "ws", (nbytes,), torch.uint8)
+        if not ops.k3_moe_dispatch_build(offsets, sr, st, inv, ids, tokens, top_k, experts, ws, nbytes):
+            raise RuntimeError("k3_moe_dispatch_build failed")
+        return offsets, sr, st, inv
+
+    def gather(self, rows, index, tag):
+        n, width = index.numel(), rows.shape[1]
+        out = self._buf(tag, (n, width), rows.dtype)
+        if n and not ops.k3_rocm_gather_rows_bf16(out, rows, index, n, width):
+            raise RuntimeError("k3_rocm_gather_rows_bf16 failed")
+        return out
+
+    def experts(self, rows, offsets_local):
+        n, d, i = rows.shape[0], self.cfg["hidden"], self.cfg["expert_hidden"]
+        out = self._buf("eo", (n, d), rows.dtype)
+        act = self._buf("ea", (n, i), rows.dtype)
+        if n and not ops.k3_moe_experts_grouped(self.layer.desc, out, act, rows, offsets_local, n):
+            raise RuntimeError("k3_moe_experts_grouped failed")
+        return out
+
+    def shared(self, x):
+        s = self.cfg["shared_hidden"]
+        if not s:
+            return None
+        t, d = x.shape
+        out = self._buf("so", (t, d), x.dtype)
+        g, u, a = (self._buf("s" + n, (t, s), x.dtype) for n in "gua")
+        if not ops.k3_moe_shared_expert(self.layer.desc, out, g, u, a, x, t):
+            raise RuntimeError("k3_moe_shared_expert failed")
+        return out
+
+    def combine(self, rows, index, weights, shared, tokens):
+        d, k = self.cfg["hidden"], self.cfg["top_k"]
+        out = torch.empty((tokens, d), dtype=rows.dtype, device=self.device)
+        if not ops.k3_moe_combine(out, rows, index, weights, shared, tokens, k, d):
+            raise RuntimeError("k3_moe_combine failed")
+        return out
+
+
+def ep_forward(backend, x, cfg: dict, group=None, timings: dict | None = None):
+    """One expert-parallel layer pass for this rank's rows ``x`` [T_local, d]
+    (2-byte elements: bf16, or int16 bit patterns on a CPU backend)."""
+    world = dist.get_world_size(group)
+    rank = dist.get_rank(group)
+    e, k = cfg["experts"], cfg["top_k"]
+    first, per = shard_range(e, world, rank)
+    t_local = x.shape[0]
+
+    ids, weights = backend.route(x)
+    shared = backend.shared(x)
+    offsets, sorted_route, sorted_token, inv_perm = backend.dispatch(ids, t_local, k, e, "src")
+    rows_send = backend.gather(x, sorted_token, "rows_send")
+    ids_sorted = ids.reshape(-1)[sorted_route.long()].contiguous()
+
+    send = destination_splits(offsets, e, world)                 # host sync: G+1 integers
+    send_t = torch.tensor(send, dtype=torch.int64, device=x.device)
+    recv_t = torch.empty_like(send_t)
+    dist.all_to_all_single(recv_t, send_t, group=group)
+    recv = [int(v) for v in recv_t.cpu()]
+    n_recv = sum(recv)
+
+    ids_recv = torch.empty(n_recv, dtype=ids_sorted.dtype, device=x.device)
+    dist.all_to_all_single(ids_recv, ids_sorted, recv, send, group=group)
+    rows_recv = torch.empty((n_recv, x.shape[1]), dtype=x.dtype, device=x.device)
+    dist.all_to_all_single(rows_recv.view(torch.uint8), rows_send.view(torch.uint8), recv, send, group=group)
+
+    if n_recv:
+        local_ids = (ids_recv - first).contiguous()
+        off_l, order, _unused, inv_l = backend.dispatch(local_ids, n_recv, 1, per, "dst")
+        rows_in = backend.gather(rows_recv, order, "rows_in")     # (expert, source rank, route) order
+        rows_out = backend.experts(rows_in, off_l)
+        rows_back = backend.gather(rows_out, inv_l, "rows_back")  # received order again
+    else:
+        rows_back = rows_recv
+    rows_home = torch.empty_like(rows_send)
+    dist.all_to_all_single(rows_home.view(torch.uint8), rows_back.view(torch.uint8), send, recv, group=group)
+    return backend.combine(rows_home, inv_perm, weights, shared, t_local), ids, weights
+
+
+class ExpertParallelLayer:
+    """The benchmark's layer sharded over the default process group (one rank per GPU)."""
+
+    def __init__(self, cfg: dict, seed: int, device, tokens: int, weights: dict | None = None):
+        self.world, self.rank = dist.get_world_size(), dist.get_rank()
+        if tokens % self.world != 0:
+            raise ValueError("token count must divide evenly over the ranks")
+        self.cfg = dict(cfg)
+        self.local_tokens = tokens // self.world
+        first, per = shard_range(cfg["experts"], self.world, self.rank)
+        self.layer = MoELayer(cfg, weights, seed=seed, device=device, local=(first, per), max_tokens=1)
+        self.backend = NativeBackend(self.layer)
+        self.device = self.layer.device
+
+    def forward(self, x: torch.Tensor, want_routes: bool = False):
+        out, ids, w = ep_forward(self.backend, x, self.cfg)
+        return (out, ids, w) if want_routes else out
+
+    def phase_times(self, x: torch.Tensor, steps: int = 5) -> dict:
+        """Device time of the grouped expert products on this rank's received rows,
+        plus the whole-pass time, averaged over ``steps`` passes."""
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        orig = self.backend.experts
+        spans = []
+
+        def timed(rows, offsets_local):
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            r = orig(rows, offsets_local)
+            b.record()
+            spans.append((a, b))
+            return r
+
+        self.backend.experts = timed
+        try:
+            start.record()
+            for _ in range(steps):
+                self.forward(x)
+            stop.record()
+            torch.cuda.synchronize()
+        finally:
+            self.backend.experts = orig
+        experts_ms = sum(a.elapsed_time(b) for a, b in spans) / steps
+        return {"experts_ms": experts_ms, "pass_ms": start.elapsed_time(stop) / steps}

@@ -1,0 +1,126 @@
+"""Expert-parallel exchange logic on CPU: two gloo ranks, arithmetic supplied by
+the CPU oracle through the backend interface of moonshine_b200.ep.  The result
+of every rank must equal the single-process oracle layer bit for bit, including
+when one rank receives no rows at all."""
+import os
+import sys
+
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+class OracleBackend:
+    """CPU stand-in for NativeBackend: same methods, numpy + oracle arithmetic."""
+
+    def __init__(self, cfg, weights, first, per):
+        from oracle import k3_oracle as o
+        self.o, self.cfg, self.w, self.first, self.per = o, cfg, weights, first, per
+
+    @staticmethod
+    def _u16(t):
+        return t.numpy().view(np.uint16)
+
+    def route(self, x):
+        o, c = self.o, self.cfg
+        logits = o.bf16_gemm(self.w["router_weight"], self._u16(x), c["experts"], c["hidden"])
+        ids, w = o.router_topk(logits, self.w["router_bias"], c["top_k"], c["route_scale"])
+        return torch.from_numpy(ids.view(np.int32).copy()), torch.from_numpy(w)
+
+    def dispatch(self, ids, tokens, top_k, experts, tag):
+        idn = ids.numpy().view(np.uint32).reshape(tokens, top_k)
+        off, toks, slots = self.o.group_routes(idn, experts)
+        inv = np.empty(tokens * top_k, np.uint32)
+        inv[slots] = np.arange(tokens * top_k, dtype=np.uint32)
+        t = lambda a: torch.from_numpy(a.view(np.int32).copy())
+        return t(off), t(slots), t(toks), t(inv)
+
+    def gather(self, rows, index, tag):
+        return rows[index.long()].contiguous()
+
+    def experts(self, rows, offsets_local):
+        o, c, w = self.o, self.cfg, self.w
+        off = offsets_local.numpy()
+        x = self._u16(rows)
+        out = np.zeros_like(x)
+        for le in range(self.per):
+            lo, hi = int(off[le]), int(off[le + 1])
+            if lo == hi:
+                continue
+            e = self.first + le
+            g = o.mxfp4_gemm(w["w1_packed"][e], w["w1_scales"][e], x[lo:hi], c["expert_hidden"], c["hidden"])
+            u = o.mxfp4_gemm(w["w3_packed"][e], w["w3_scales"][e], x[lo:hi], c["expert_hidden"], c["hidden"])
+            a = o.activation(g, u, c["activation"], c["beta"], c["linear_beta"])
+            out[lo:hi] = o.mxfp4_gemm(w["w2_packed"][e], w["w2_scales"][e], a, c["hidden"], c["expert_hidden"])
+        return torch.from_numpy(out.view(np.int16).copy())
+
+    def shared(self, x):
+        o, c, w = self.o, self.cfg, self.w
+        s, d = c["shared_hidden"], c["hidden"]
+        if not s:
+            return None
+        xs = self._u16(x)
+        g = o.q8_gemm(w["shared_gate_q"], w["shared_gate_s"], xs, s, d, c["q8_block"], c["q8_scale_type"])
+        u = o.q8_gemm(w["shared_up_q"], w["shared_up_s"], xs, s, d, c["q8_block"], c["q8_scale_type"])
+        a = o.activation(g, u, c["activation"], c["beta"], c["linear_beta"])
+        out = o.q8_gemm(w["shared_down_q"], w["shared_down_s"], a, d, s, c["q8_block"], c["q8_scale_type"])
+        return torch.from_numpy(out.view(np.int16).copy())
+
+    def combine(self, rows, index, weights, shared, tokens):
+        o, c = self.o, self.cfg
+        k, d = c["top_k"], c["hidden"]
+        picked = self._u16(rows)[index.numpy().view(np.uint32)].reshape(tokens, k, d)
+        out = o.weighted_sum(np.ascontiguousarray(picked), weights.numpy(), tokens, k, d)
+        if shared is not None:
+            out = o.add(out, self._u16(shared))
+        return torch.from_numpy(out.view(np.int16).copy())
+
+
+def _worker(rank, world, port, mode, results):
+    sys.path.insert(0, ROOT)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from moonshine_b200 import ep, synth
+        from oracle import k3_oracle as o
+        cfg = synth.tiny_config()
+        weights = synth.make_layer(cfg, seed=31)
+        if mode == "rank1_idle":
+            weights["router_bias"][: cfg["experts"] // 2] += np.float32(5.0)   # every route stays on rank 0
+        tokens = 24
+        x = synth.activations(31, tokens, cfg["hidden"])
+        want, want_ids, _, _, _ = o.moe_layer(weights, x)
+        first, per = ep.shard_range(cfg["experts"], world, rank)
+        backend = OracleBackend(cfg, weights, first, per)
+        lo, hi = rank * tokens // world, (rank + 1) * tokens // world
+        xl = torch.from_numpy(x[lo:hi].view(np.int16).copy())
+        out, ids, _ = ep.ep_forward(backend, xl, cfg)
+        got = out.numpy().view(np.uint16)
+        ok = np.array_equal(got, want[lo:hi]) and np.array_equal(ids.numpy().view(np.uint32), want_ids[lo:hi])
+        results[rank] = bool(ok)
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("mode", ["balanced", "rank1_idle"])
+def test_two_rank_expert_parallel_equals_single_process(mode, oracle):
+    world = 2
+    port = 29600 + (os.getpid() % 200) + (0 if mode == "balanced" else 1)
+    with mp.Manager() as manager:
+        results = manager.dict()
+        mp.spawn(_worker, args=(world, port, mode, results), nprocs=world, join=True)
+        assert dict(results) == {0: True, 1: True}
+
+
+def test_destination_splits():
+    from moonshine_b200 import ep
+    offsets = torch.tensor([0, 2, 2, 5, 9, 9, 9, 10, 12], dtype=torch.int32)
+    assert ep.destination_splits(offsets, 8, 2) == [9, 3]
+    assert ep.destination_splits(offsets, 8, 4) == [2, 7, 0, 3]
+    assert ep.shard_range(896, 8, 3) == (336, 112)
+    with pytest.raises(ValueError):
+        ep.shard_range(10, 4, 0)
