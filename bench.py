@@ -37,14 +37,21 @@ UNIT = "tokens/s"
 L2_BYTES = 126 * 1024 * 1024
 
 
-def workload_config(name: str):
+def workload_config(name: str, args=None):
     if name == "prefill8k":
-        return synth.baseline_config(bias_mode="zipf"), 8192
-    if name == "prefill512":
-        return synth.baseline_config(), 512
-    if name == "decode":
-        return synth.baseline_config(), 1
-    raise SystemExit(f"unknown workload {name}")
+        cfg, tokens = synth.baseline_config(bias_mode="zipf"), 8192
+    elif name == "prefill512":
+        cfg, tokens = synth.baseline_config(), 512
+    elif name == "decode":
+        cfg, tokens = synth.baseline_config(), 1
+    else:
+        raise SystemExit(f"unknown workload {name}")
+    if args is not None:                      # reduced cases for profiler captures only
+        if args.experts:
+            cfg["experts"] = args.experts
+        if args.tokens:
+            tokens = args.tokens
+    return cfg, tokens
 
 
 def measured_peaks():
@@ -179,7 +186,7 @@ def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    cfg, tokens = workload_config(args.workload)
+    cfg, tokens = workload_config(args.workload, args)
     values = []
     for step in range(args.warmup + args.steps):
         r = cpu_baseline(cfg, tokens, budget_s=6.0)
@@ -255,7 +262,7 @@ def run_native(args):
     if world > 1:
         dist.init_process_group("nccl", device_id=device)
 
-    cfg, tokens = workload_config(args.workload)
+    cfg, tokens = workload_config(args.workload, args)
     peaks = measured_peaks()
     d, k = cfg["hidden"], cfg["top_k"]
     flops = synth.prefill_flops_per_token(cfg)
@@ -278,7 +285,7 @@ def run_native(args):
             dist.barrier()
         torch.cuda.synchronize()
 
-    for _ in range(max(args.warmup, 3)):
+    for _ in range(args.warmup if args.lean else max(args.warmup, 3)):
         layer.forward(x_dev)
     barrier()
 
@@ -300,6 +307,15 @@ def run_native(args):
         ms_total = float(t.item())
     ms_step = ms_total / args.steps
     value = tokens / (ms_step * 1e-3)
+
+    if args.lean:           # profiler capture: timed region only
+        if rank == 0:
+            print(json.dumps({"metric": METRIC, "value": value, "unit": UNIT, "ms_per_step": ms_step,
+                              "config": {"workload": args.workload, "tokens": tokens,
+                                         "experts": cfg["experts"]}, "lean": True}))
+        if world > 1:
+            dist.destroy_process_group()
+        return
 
     # ---- end to end: pinned host input -> device -> layer -> pinned host output
     barrier()
@@ -390,6 +406,9 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="native", choices=["native", "reference"])
     ap.add_argument("--workload", default="prefill8k", choices=["prefill8k", "prefill512", "decode"])
+    ap.add_argument("--lean", action="store_true", help="timed region only (for profiler captures)")
+    ap.add_argument("--experts", type=int, default=0, help="override the expert count (profiler captures)")
+    ap.add_argument("--tokens", type=int, default=0, help="override the token count (profiler captures)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

@@ -4,9 +4,8 @@
 // MXFP4 rows are consumed in their checkpoint-native form: packed [rows, K/2]
 // (even column = low nibble) and E8M0 scales [rows, K/32].  A warp owns 16
 // rows.  Every lane streams 16-byte nibble chunks (one 32-column scale group)
-// of rows g and g+8, converts them in registers with the hardware
-// e2m1x2 -> f16x2 conversion, and feeds them to mma.sync.m16n8k16 as the A
-// operand.  The B operand is block-diagonal: column n of the MMA carries the
+// of rows g and g+8, converts them in registers to f16 (exact) with byte-permute
+// table lookups, and feeds them to mma.sync.m16n8k16 as the A operand.  The B operand is block-diagonal: column n of the MMA carries the
 // activation slice of scale group n only, so after 8 MMAs the accumulator
 // column n holds the fp32 dot product of exactly one 32-column group.  The
 // E8M0 scale (a power of two) is then applied with one fp32 FMA per group into
@@ -30,11 +29,25 @@ constexpr int kGemvKSplit = 4;              // warps sharing one 16-row block al
 constexpr int kGemvRowBlocks = kGemvWarps / kGemvKSplit;  // 16-row blocks per CTA item
 constexpr int kGemvRowsPerItem = 16 * kGemvRowBlocks;     // 32
 
-K3_DEVINL uint32_t cvt_e2m1x2_to_f16x2(uint32_t byte) {
-    uint32_t out;
-    const uint16_t b = (uint16_t)byte;
-    asm("{ .reg .b8 t; cvt.u8.u16 t, %1; cvt.rn.f16x2.e2m1x2 %0, t; }" : "=r"(out) : "h"(b));
-    return out;
+// Eight E2M1 nibbles (one 32-bit word, low nibble first) -> four f16x2
+// registers holding elements (0,1), (2,3), (4,5), (6,7).  The f16 encodings of
+// the magnitudes 0, .5, 1, 1.5, 2, 3, 4, 6 have a zero low byte, so one PRMT
+// looks up four high bytes at once; signs are gathered with a second PRMT and
+// the bytes are then spread into 16-bit lanes.  Everything runs on the integer
+// pipe (the hardware e2m1x2 conversion is issued at a quarter of that rate).
+constexpr uint32_t kF16HiLut0 = 0x3E3C3800u, kF16HiLut1 = 0x46444240u;
+
+K3_DEVINL void dequant_word_f16(uint32_t w, uint32_t (&out)[4]) {
+    const uint32_t sel = w & 0x77777777u;
+    uint32_t m03 = __byte_perm(kF16HiLut0, kF16HiLut1, sel);
+    uint32_t m47 = __byte_perm(kF16HiLut0, kF16HiLut1, sel >> 16);
+    const uint32_t w4 = w << 4;
+    m03 |= __byte_perm(w4, w, 0x5140u) & 0x80808080u;
+    m47 |= __byte_perm(w4, w, 0x7362u) & 0x80808080u;
+    out[0] = __byte_perm(m03, 0u, 0x1404u);
+    out[1] = __byte_perm(m03, 0u, 0x3424u);
+    out[2] = __byte_perm(m47, 0u, 0x1404u);
+    out[3] = __byte_perm(m47, 0u, 0x3424u);
 }
 
 K3_DEVINL void mma_f16_m16n8k16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2,
@@ -155,14 +168,12 @@ K3_DEVINL void mxfp4_rowblock_partial(float (&sum)[2], const uint8_t *packed, co
         const uint32_t wa_w[4] = {wa.x, wa.y, wa.z, wa.w};
         const uint32_t wb_w[4] = {wb.x, wb.y, wb.z, wb.w};
 #pragma unroll
-        for (int j = 0; j < 8; j++) {
-            const uint32_t word_a = wa_w[j >> 1], word_b = wb_w[j >> 1];
-            const uint32_t sh = (j & 1) * 16;
-            const uint32_t a0 = cvt_e2m1x2_to_f16x2((word_a >> sh) & 0xffu);
-            const uint32_t a2 = cvt_e2m1x2_to_f16x2((word_a >> (sh + 8)) & 0xffu);
-            const uint32_t a1 = cvt_e2m1x2_to_f16x2((word_b >> sh) & 0xffu);
-            const uint32_t a3 = cvt_e2m1x2_to_f16x2((word_b >> (sh + 8)) & 0xffu);
-            mma_f16_m16n8k16(c, a0, a1, a2, a3, xr[2 * j], xr[2 * j + 1]);
+        for (int i = 0; i < 4; i++) {
+            uint32_t fa[4], fb[4];          // elements 8i .. 8i+7 of rows g and g+8
+            dequant_word_f16(wa_w[i], fa);
+            dequant_word_f16(wb_w[i], fb);
+            mma_f16_m16n8k16(c, fa[0], fb[0], fa[1], fb[1], xr[4 * i], xr[4 * i + 1]);
+            mma_f16_m16n8k16(c, fa[2], fb[2], fa[3], fb[3], xr[4 * i + 2], xr[4 * i + 3]);
         }
         acc_a = fmaf(s_a0, c[0], acc_a);
         acc_a = fmaf(s_a1, c[1], acc_a);

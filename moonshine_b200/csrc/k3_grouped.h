@@ -6,6 +6,7 @@
 
 #include "k3_moe_layer.h"
 
+#include <cuda_runtime.h>
 #include <stdint.h>
 
 // logits f32 [tokens, rows] = x bf16 [tokens, cols] * W bf16 [rows, cols]^T
@@ -23,3 +24,11 @@ bool k3_grouped_tc_supported(const k3_moe_layer_desc *desc, uint32_t rows);
 // gate/up + activation and down over rows grouped by local expert
 bool k3_grouped_tc_experts(const k3_moe_layer_desc *desc, void *rows_out, void *act,
                            const void *rows_in, const void *offsets, uint32_t rows, void *stream);
+
+// One-token layer on persistent matrix-vector kernels (router, routing, expert
+// gate/up/down and shared-expert rows; the caller runs the combine).  All
+// buffers are caller-owned scratch.
+bool k3_decode_supported(const k3_moe_layer_desc *desc);
+bool k3_decode_layer(const k3_moe_layer_desc *desc, const void *x, void *logits, void *ids,
+                     void *weights, void *sh_gate, void *sh_up, void *sh_act, void *sh_out,
+                     void *act, void *rows_out, cudaStream_t stream);

@@ -377,32 +377,40 @@ bool layer_forward_impl(const k3_moe_layer_desc *d, void *out, const void *x, ui
     const uint32_t routes = tokens * d->top_k;
 
     if (!mark(events, 0, stream)) return false;
-    if (!k3_moe_route(d, w.ids, w.weights, w.logits, x, tokens, stream)) return false;
-    if (!mark(events, 1, stream)) return false;
-    if (d->shared_hidden &&
-        !k3_moe_shared_expert(d, w.sh_out, w.sh_gate, w.sh_up, w.sh_act, x, tokens, stream)) {
-        return false;
-    }
-    if (!mark(events, 2, stream)) return false;
     const uint32_t *index = nullptr;
-    if (tokens == 1u) {
-        // one token: every selected expert reads the same row; rows stay in rank order
-        if (!mark(events, 3, stream)) return false;
-        if (!launch_grouped_rows(d, w.rows_out, w.act, x, nullptr, w.ids, d->top_k, true, stream)) {
+    if (tokens == 1u && k3_decode_supported(d)) {
+        // one token: persistent matrix-vector kernels, rows stay in rank order
+        if (!mark(events, 1, stream) || !mark(events, 2, stream) || !mark(events, 3, stream)) return false;
+        if (!k3_decode_layer(d, x, w.logits, w.ids, w.weights, w.sh_gate, w.sh_up, w.sh_act,
+                             w.sh_out, w.act, w.rows_out, stream)) {
             return false;
         }
     } else {
-        if (!k3_moe_dispatch_build(w.offsets, w.sorted_route, w.sorted_token, w.inv_perm, w.ids,
-                                   tokens, d->top_k, d->expert_count, w.dispatch_ws,
-                                   w.dispatch_bytes, stream) ||
-            !k3_rocm_gather_rows_bf16(w.rows_in, x, w.sorted_token, routes, d->hidden, stream)) {
+        if (!k3_moe_route(d, w.ids, w.weights, w.logits, x, tokens, stream)) return false;
+        if (!mark(events, 1, stream)) return false;
+        if (d->shared_hidden &&
+            !k3_moe_shared_expert(d, w.sh_out, w.sh_gate, w.sh_up, w.sh_act, x, tokens, stream)) {
             return false;
         }
-        if (!mark(events, 3, stream)) return false;
-        if (!k3_moe_experts_grouped(d, w.rows_out, w.act, w.rows_in, w.offsets, routes, stream)) {
-            return false;
+        if (!mark(events, 2, stream)) return false;
+        if (tokens == 1u) {
+            if (!mark(events, 3, stream)) return false;
+            if (!launch_grouped_rows(d, w.rows_out, w.act, x, nullptr, w.ids, d->top_k, true, stream)) {
+                return false;
+            }
+        } else {
+            if (!k3_moe_dispatch_build(w.offsets, w.sorted_route, w.sorted_token, w.inv_perm, w.ids,
+                                       tokens, d->top_k, d->expert_count, w.dispatch_ws,
+                                       w.dispatch_bytes, stream) ||
+                !k3_rocm_gather_rows_bf16(w.rows_in, x, w.sorted_token, routes, d->hidden, stream)) {
+                return false;
+            }
+            if (!mark(events, 3, stream)) return false;
+            if (!k3_moe_experts_grouped(d, w.rows_out, w.act, w.rows_in, w.offsets, routes, stream)) {
+                return false;
+            }
+            index = w.inv_perm;
         }
-        index = w.inv_perm;
     }
     if (!mark(events, 4, stream)) return false;
     if (!k3_moe_combine(out, w.rows_out, index, w.weights, d->shared_hidden ? w.sh_out : nullptr,
