@@ -21,6 +21,7 @@
 // k3_gemv.cuh for the fragment layout).  No cross-warp reduction is needed.
 #include "k3_gemv.cuh"
 #include "k3_grouped.h"
+#include "k3_rowdot.cuh"
 #include "k3_moe_layer.h"
 #include "k3_moe_ops.h"
 
@@ -34,72 +35,6 @@ constexpr int kDecodeWarps = 16;
 constexpr int kDecodeThreads = kDecodeWarps * kWarp;
 constexpr int kPrefetch = 3;
 
-// ------------------------------------------------------------ exact row dots
-// BF16 row x vector in the reference's order (lane = column mod 256, fused
-// multiply-add per term, tree 128..1); one warp, result valid in lane 0.
-K3_DEVINL float bf16_row_dot_exact(const uint16_t *__restrict__ wr, const uint16_t *__restrict__ x,
-                                   uint32_t columns, uint32_t lane) {
-    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-    for (uint32_t c0 = lane * 8u; c0 < columns; c0 += 256u) {
-        const uint4 q = *reinterpret_cast<const uint4 *>(wr + c0);
-        const uint4 v = *reinterpret_cast<const uint4 *>(x + c0);
-        acc[0] = fmaf(bf16_lo(q.x), bf16_lo(v.x), acc[0]);
-        acc[1] = fmaf(bf16_hi(q.x), bf16_hi(v.x), acc[1]);
-        acc[2] = fmaf(bf16_lo(q.y), bf16_lo(v.y), acc[2]);
-        acc[3] = fmaf(bf16_hi(q.y), bf16_hi(v.y), acc[3]);
-        acc[4] = fmaf(bf16_lo(q.z), bf16_lo(v.z), acc[4]);
-        acc[5] = fmaf(bf16_hi(q.z), bf16_hi(v.z), acc[5]);
-        acc[6] = fmaf(bf16_lo(q.w), bf16_lo(v.w), acc[6]);
-        acc[7] = fmaf(bf16_hi(q.w), bf16_hi(v.w), acc[7]);
-    }
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) {
-#pragma unroll
-        for (int i = 0; i < 8; i++) acc[i] += __shfl_down_sync(0xffffffffu, acc[i], o);
-    }
-    float r0 = acc[0] + acc[4], r1 = acc[1] + acc[5], r2 = acc[2] + acc[6], r3 = acc[3] + acc[7];
-    r0 += r2; r1 += r3;
-    return r0 + r1;
-}
-
-// Q8 row x vector in the reference's order (lane = octet mod 256, eight fused
-// multiply-adds per octet, tree); one warp, result valid in lane 0.
-K3_DEVINL float q8_row_dot_exact(const int8_t *__restrict__ qr, const void *__restrict__ scales,
-                                 uint64_t scale_base, const uint16_t *__restrict__ x,
-                                 uint32_t columns, uint32_t block, int scale_f16, uint32_t lane) {
-    const uint32_t octets = columns / 8u;
-    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-    for (uint32_t o0 = 0; o0 < octets; o0 += 256u) {
-#pragma unroll
-        for (int i = 0; i < 8; i++) {
-            const uint32_t octet = o0 + 32u * i + lane;
-            if (octet >= octets) continue;
-            const uint2 wq = *reinterpret_cast<const uint2 *>(qr + (uint64_t)octet * 8u);
-            const uint32_t sidx = (octet * 8u) / block;
-            const float s = scale_f16
-                                ? __half2float(reinterpret_cast<const __half *>(scales)[scale_base + sidx])
-                                : reinterpret_cast<const float *>(scales)[scale_base + sidx];
-            const uint4 xq = *reinterpret_cast<const uint4 *>(x + (uint64_t)octet * 8u);
-            float a = acc[i];
-            a = fmaf(__fmul_rn((float)(int8_t)(wq.x), s), bf16_lo(xq.x), a);
-            a = fmaf(__fmul_rn((float)(int8_t)(wq.x >> 8), s), bf16_hi(xq.x), a);
-            a = fmaf(__fmul_rn((float)(int8_t)(wq.x >> 16), s), bf16_lo(xq.y), a);
-            a = fmaf(__fmul_rn((float)(int8_t)(wq.x >> 24), s), bf16_hi(xq.y), a);
-            a = fmaf(__fmul_rn((float)(int8_t)(wq.y), s), bf16_lo(xq.z), a);
-            a = fmaf(__fmul_rn((float)(int8_t)(wq.y >> 8), s), bf16_hi(xq.z), a);
-            a = fmaf(__fmul_rn((float)(int8_t)(wq.y >> 16), s), bf16_lo(xq.w), a);
-            a = fmaf(__fmul_rn((float)(int8_t)(wq.y >> 24), s), bf16_hi(xq.w), a);
-            acc[i] = a;
-        }
-    }
-    float p0 = acc[0] + acc[4], p1 = acc[1] + acc[5], p2 = acc[2] + acc[6], p3 = acc[3] + acc[7];
-    p0 += p2; p1 += p3;
-    p0 += p1;
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) p0 += __shfl_down_sync(0xffffffffu, p0, o);
-    return p0;
-}
-
 struct DecodeArgs {
     k3_moe_layer_desc d;
     const uint16_t *x;        // [hidden]
@@ -109,6 +44,8 @@ struct DecodeArgs {
     uint16_t *sh_gate, *sh_up, *sh_act, *sh_out;   // shared expert buffers
     uint16_t *act;            // [top_k, I]
     uint16_t *rows_out;       // [top_k, hidden]
+    uint32_t shared_only;     // down kernel: only the shared expert's rows
+    uint32_t skip_shared;     // front/route: the shared expert is computed elsewhere
 };
 
 // ------------------------------------------------------------------- front
@@ -117,7 +54,7 @@ decode_front_kernel(DecodeArgs a) {
     const uint32_t lane = threadIdx.x % kWarp;
     const uint32_t warps = (gridDim.x * blockDim.x) / kWarp;
     const uint32_t E = a.d.expert_count, S = a.d.shared_hidden, H = a.d.hidden;
-    const uint32_t tasks = E + 2u * S;
+    const uint32_t tasks = E + (a.skip_shared ? 0u : 2u * S);
     const uint32_t blocks_per_row = H / a.d.q8_block;
     for (uint32_t task = (blockIdx.x * blockDim.x + threadIdx.x) / kWarp; task < tasks; task += warps) {
         if (task < E) {
@@ -179,7 +116,7 @@ decode_route_kernel(DecodeArgs a) {
     const uint32_t warp = threadIdx.x / kWarp, lane = threadIdx.x % kWarp;
     const uint32_t E = a.d.expert_count, k = a.d.top_k;
     // shared-expert activation
-    for (uint32_t i = threadIdx.x; i < a.d.shared_hidden; i += blockDim.x) {
+    for (uint32_t i = threadIdx.x; i < (a.skip_shared ? 0u : a.d.shared_hidden); i += blockDim.x) {
         a.sh_act[i] = float_to_bf16_bits(activation(bf16_bits_to_float(a.sh_gate[i]),
                                                     bf16_bits_to_float(a.sh_up[i]), a.d.activation,
                                                     a.d.beta, a.d.linear_beta));
@@ -350,7 +287,7 @@ decode_down_kernel(DecodeArgs a) {
     __half *xs = reinterpret_cast<__half *>(smem_raw);                       // [k][I]
     float *inv_scale = reinterpret_cast<float *>(smem_raw + (size_t)(k + 1u) * I * sizeof(__half));  // [k+1]
     float *scratch = inv_scale + 34;
-    for (uint32_t r = 0; r < k; r += 2u) {
+    for (uint32_t r = 0; r < (a.shared_only ? 0u : k); r += 2u) {
         __syncthreads();
         stage_vectors_f16(xs + (size_t)r * I, inv_scale + r, a.act + (uint64_t)r * I,
                           r + 1u < k ? a.act + (uint64_t)(r + 1u) * I : nullptr, I, I, scratch);
@@ -360,7 +297,7 @@ decode_down_kernel(DecodeArgs a) {
     const uint32_t lane = threadIdx.x % kWarp;
     const uint32_t blocks = H / 16u;
     const uint64_t pstride = (uint64_t)H * (I / 2u), sstride = (uint64_t)H * (I / 32u);
-    const uint32_t expert_tasks = k * blocks;
+    const uint32_t expert_tasks = a.shared_only ? 0u : k * blocks;
     const uint32_t shared_tasks = S ? H : 0u;            // one warp per shared down row
     for (uint32_t task = warp_global; task < expert_tasks + shared_tasks; task += warps) {
         if (task < expert_tasks) {
@@ -412,7 +349,8 @@ bool k3_decode_supported(const k3_moe_layer_desc *d) {
 // buffers: see DecodeArgs; all caller-owned scratch carved from the layer workspace
 bool k3_decode_layer(const k3_moe_layer_desc *d, const void *x, void *logits, void *ids,
                      void *weights, void *sh_gate, void *sh_up, void *sh_act, void *sh_out,
-                     void *act, void *rows_out, cudaStream_t stream) {
+                     void *act, void *rows_out, void *scratch, size_t scratch_bytes,
+                     cudaStream_t stream) {
     DecodeArgs a{};
     a.d = *d;
     a.x = (const uint16_t *)x;
@@ -426,11 +364,17 @@ bool k3_decode_layer(const k3_moe_layer_desc *d, const void *x, void *logits, vo
     a.act = (uint16_t *)act;
     a.rows_out = (uint16_t *)rows_out;
     const int sms = sm_count();
-    const uint32_t front_tasks = d->expert_count + 2u * d->shared_hidden;
+    const bool mx = scratch != nullptr && k3_decode_mx_supported(d) &&
+                    scratch_bytes >= k3_decode_mx_scratch_bytes(d);
+    a.skip_shared = mx ? 1u : 0u;
+    const uint32_t front_tasks = d->expert_count + (mx ? 0u : 2u * d->shared_hidden);
     decode_front_kernel<<<std::min<uint32_t>((front_tasks + 7u) / 8u, (uint32_t)sms * 8u), 256, 0, stream>>>(a);
     if (!launch_ok()) return false;
     decode_route_kernel<<<1, 256, 0, stream>>>(a);
     if (!launch_ok()) return false;
+    if (mx) {
+        return k3_decode_mx_experts(d, x, ids, act, rows_out, sh_gate, sh_up, sh_out, scratch, stream);
+    }
     size_t smem = (size_t)2 * d->hidden * sizeof(__half) + (2 + 2 * kDecodeWarps) * sizeof(float);
     if (!set_smem((const void *)decode_gateup_kernel, smem)) return false;
     decode_gateup_kernel<<<sms, kDecodeThreads, smem, stream>>>(a);

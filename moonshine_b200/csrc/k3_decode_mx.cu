@@ -1,0 +1,555 @@
+// One-token expert products on the block-scaled tensor-core path
+// (tcgen05.mma kind::mxf8f6f4, scale_vec::1X).
+//
+// The MXFP4 weights are consumed as they are: packed E2M1 nibbles arrive by TMA
+// (tensor-map type 16U4_ALIGN16B expands them into the 8-bit containers the MMA
+// reads) and the E8M0 scales are written into tensor memory with tcgen05.st, so
+// no thread touches a weight.  The activation vector is split once into two
+// E4M3 terms with a shared E8M0 scale per 32 elements, x = 2^s * (hi + lo):
+// bf16 has 8 significant bits, each E4M3 term carries 4, so every element within
+// 2^10 of its block maximum is represented exactly and the rest to 2^-17 of the
+// block maximum.  hi and lo are rows 0 and 1 of the N=16 operand, so accumulator
+// columns 0 and 1 hold the two partial dot products and their sum is the result.
+//
+// One CTA per SM, persistent over (expert rank, 128-row tile) items:
+//   warp 0      TMA producer (A: 128 rows x 128 K, B: 16 rows x 128 K per step)
+//   warp 1      MMA issuer: 4 MMAs of K=32 per step, scale ids 0..3
+//   warps 2-5   scale writers: per step the tile's 128x4 E8M0 bytes -> 4 TMEM
+//               columns (lane = row % 32, column = row / 32, copied into every
+//               lane quadrant) plus the activation block scales
+//   warps 6-9   epilogue: tcgen05.ld columns 0/1 (+16/17), sum, bf16, activation;
+//               the gate/up epilogue also splits the activation it produces into
+//               the two E4M3 terms the down projection reads
+//   warps 10-15 shared-expert Q8 rows (gate and up next to the routed gate/up,
+//               down next to the routed down), exact reference order, overlapping
+//               the HBM-bound tensor pipeline
+// Every barrier wait is bounded (see k3_tc_ptx.cuh).
+#include "k3_grouped.h"
+#include "k3_rowdot.cuh"
+#include "k3_tc_ptx.cuh"
+
+#include <cuda.h>
+#include <cudaTypedefs.h>
+#include <cuda_fp8.h>
+
+#include <algorithm>
+#include <cstdlib>
+#include <mutex>
+
+using namespace k3;
+using namespace k3::tc;
+
+namespace {
+
+constexpr uint32_t kStages = 12;            // TMA ring (multiple of 4)
+constexpr uint32_t kSfBatches = 6;          // scale ring: batches of 4 steps
+constexpr uint32_t kSfStages = 4 * kSfBatches;
+constexpr uint32_t kATile = 128 * 128;     // bytes in shared memory (8-bit containers)
+constexpr uint32_t kATx = 128 * 64;        // bytes the TMA transaction counts (packed)
+constexpr uint32_t kBTile = 16 * 128;
+constexpr uint32_t kStageBytes = kATile + kBTile;
+constexpr uint32_t kThreads = 512;
+constexpr uint32_t kSideWarps = 5;          // warps 11..15 (warp 10 is the second TMA producer)
+constexpr uint32_t kTmemCols = 256;
+constexpr uint32_t kAccCol = 0;            // 2 buffers x 32 columns
+constexpr uint32_t kSfaCol = 64;           // kSfStages x 4 columns
+constexpr uint32_t kSfbCol = 64 + 4 * kSfStages;   // kSfStages x 4 columns
+constexpr uint32_t kBarrierBytes = 512;
+constexpr uint32_t kSmemBytes = kStages * kStageBytes + 1024 + kBarrierBytes;   // + shared activation vector
+
+__device__ uint32_t g_mx_status = 0;
+
+K3_DEVINL void tmem_st_32x1(uint32_t taddr, uint32_t v) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x1.b32 [%0], {%1};" ::"r"(taddr), "r"(v) : "memory");
+}
+// 16 consecutive 32-bit columns of this warp's lane quadrant in one instruction
+K3_DEVINL void tmem_st_32x16(uint32_t taddr, const uint32_t (&v)[16]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};" ::"r"(taddr),
+        "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]), "r"(v[8]),
+        "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15])
+        : "memory");
+}
+K3_DEVINL void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+K3_DEVINL void tmem_ld_32x2(uint32_t taddr, uint32_t &r0, uint32_t &r1) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x2.b32 {%0, %1}, [%2];" : "=r"(r0), "=r"(r1) : "r"(taddr) : "memory");
+}
+
+K3_DEVINL void mma_mx(uint32_t d, uint64_t a, uint64_t b, uint32_t idesc, uint32_t sfa, uint32_t sfb,
+                      uint32_t acc) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %6, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::mxf8f6f4.block_scale.scale_vec::1X [%0], %1, %2, %3, [%4], [%5], p;\n\t}" ::
+            "r"(d), "l"(a), "l"(b), "r"(idesc), "r"(sfa), "r"(sfb), "r"(acc)
+        : "memory");
+}
+
+// Block-scaled instruction descriptor: A = E2M1 (5), B = E4M3 (0), UE8M0 scales,
+// M = 128, N = 16, K-major operands; sf = which byte of the 32-bit scale column.
+K3_DEVINL uint32_t make_idesc_mx(uint32_t sf) {
+    return (5u << 7) | (0u << 10) | ((16u >> 3) << 17) | (1u << 23) | ((128u >> 4) << 24) | (sf << 29) |
+           (sf << 4);
+}
+
+struct MxArgs {
+    const uint8_t *scales_a0;   // E8M0 table of phase 0 (gate / down)
+    const uint8_t *scales_a1;   // E8M0 table of phase 1 (up), gate/up mode only
+    const uint8_t *sfb;         // activation block scales [vectors, K/32]
+    const uint32_t *ids;        // expert id per rank
+    uint16_t *out;              // [ranks, out_width] bf16
+    uint32_t ranks, first_local, local_count;
+    uint32_t w_rows;            // rows per expert per matrix
+    uint32_t k;
+    uint32_t shared_vector;     // 1: every rank uses activation vector 0 (gate/up)
+    int activation;
+    float beta, linear_beta;
+    uint8_t *act_hl;            // gate/up: E4M3 split of the produced activation [2*ranks, w_rows]
+    uint8_t *act_sf;            //          and its block scales [ranks, w_rows/32]
+    // shared-expert side work (Q8 rows, one warp per row)
+    const int8_t *q8_q0, *q8_q1;
+    const void *q8_s0, *q8_s1;
+    uint16_t *q8_out0, *q8_out1;
+    const uint16_t *q8_x;       // input vector in global memory, or nullptr: act(q8_gate, q8_up)
+    const uint16_t *q8_gate, *q8_up;
+    uint32_t q8_rows, q8_cols, q8_block;
+    int q8_scale_f16;
+    uint32_t exp_flags;         // timing experiments only
+};
+
+// value -> (hi, lo) E4M3 pair and block scale of a 32-element block held one
+// element per lane
+K3_DEVINL void split_block_e4m3(float val, uint8_t &hi, uint8_t &lo, uint8_t &scale_byte) {
+    const float mx = warp_max(fabsf(val));
+    int e = 0;
+    if (mx > 0.f && mx < 3.0e38f) e = (int)((__float_as_uint(mx) >> 23) & 0xffu) - 127 - 7;
+    e = max(-126, min(127, e));
+    const float scaled = val * __uint_as_float((uint32_t)(127 - e) << 23);      // |scaled| < 256
+    hi = __nv_cvt_float_to_fp8(scaled, __NV_SATFINITE, __NV_E4M3);
+    const float hi_f = __half2float(__half(__nv_cvt_fp8_to_halfraw(hi, __NV_E4M3)));
+    lo = __nv_cvt_float_to_fp8(scaled - hi_f, __NV_SATFINITE, __NV_E4M3);
+    scale_byte = (uint8_t)(e + 127);
+}
+
+// kGateUp: two phases (w1 then w3) into accumulator columns [0,16) and [16,32),
+// fused activation.  Otherwise one phase, plain bf16 output.
+template <bool kGateUp>
+__global__ void __launch_bounds__(kThreads, 1)
+decode_mx_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_constant__ CUtensorMap map_a1,
+                 const __grid_constant__ CUtensorMap map_b, MxArgs a) {
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char *base = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+    uint64_t *bars = reinterpret_cast<uint64_t *>(base + kStages * kStageBytes);
+    uint64_t *full = bars, *empty = bars + kStages;
+    uint64_t *sf_full = bars + 2 * kStages;            // [kSfBatches]
+    uint64_t *sf_empty = sf_full + kSfBatches;         // [kSfBatches]
+    uint64_t *acc_full = sf_empty + kSfBatches, *acc_empty = acc_full + 2;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(acc_empty + 2);
+    volatile uint32_t *abort_flag = tmem_slot + 1;
+    uint16_t *side_x = reinterpret_cast<uint16_t *>(base + kStages * kStageBytes + kBarrierBytes);
+    const uint32_t warp = threadIdx.x / kWarp, lane = threadIdx.x % kWarp;
+    const uint32_t steps = a.k / 128u;
+    const uint32_t phases = kGateUp ? 2u : 1u;
+    const uint32_t tiles = a.w_rows / 128u;
+    const uint32_t items = a.ranks * tiles;
+
+    if (threadIdx.x == 0) {
+        *abort_flag = 0u;
+        for (uint32_t s = 0; s < kStages; s++) {
+            mbar_init(&full[s], 1);
+            mbar_init(&empty[s], 1);
+        }
+        for (uint32_t b = 0; b < kSfBatches; b++) {
+            mbar_init(&sf_full[b], 4);
+            mbar_init(&sf_empty[b], 1);
+        }
+        for (uint32_t b = 0; b < 2; b++) {
+            mbar_init(&acc_full[b], 1);
+            mbar_init(&acc_empty[b], 4);
+        }
+        fence_barrier_init();
+    }
+    if (warp == 1) {
+        tmem_alloc(tmem_slot, kTmemCols);
+        tmem_relinquish();
+    }
+    if (a.q8_rows != 0u && a.q8_x == nullptr) {
+        for (uint32_t i = threadIdx.x; i < a.q8_cols; i += blockDim.x) {
+            side_x[i] = float_to_bf16_bits(activation(bf16_bits_to_float(a.q8_gate[i]),
+                                                      bf16_bits_to_float(a.q8_up[i]), a.activation,
+                                                      a.beta, a.linear_beta));
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = *tmem_slot;
+
+    if (warp >= 11) {
+        // ---- shared-expert rows (SIMT), independent of the tensor pipeline
+        const uint16_t *xin = a.q8_x ? a.q8_x : side_x;
+        const uint32_t side = blockIdx.x * kSideWarps + (warp - 11u);
+        const uint32_t side_total = gridDim.x * kSideWarps;
+        const uint32_t mats = a.q8_q1 ? 2u : 1u;
+        const uint32_t bpr = a.q8_cols / (a.q8_block ? a.q8_block : 1u);
+        for (uint32_t task = side; task < a.q8_rows * mats; task += side_total) {
+            const bool second = task >= a.q8_rows;
+            const uint32_t row = second ? task - a.q8_rows : task;
+            const float v = q8_row_dot_exact((second ? a.q8_q1 : a.q8_q0) + (uint64_t)row * a.q8_cols,
+                                             second ? a.q8_s1 : a.q8_s0, (uint64_t)row * bpr, xin,
+                                             a.q8_cols, a.q8_block, a.q8_scale_f16, lane);
+            if (lane == 0) (second ? a.q8_out1 : a.q8_out0)[row] = float_to_bf16_bits(v);
+        }
+    } else if (warp == 0 || warp == 10) {
+        // two producers issue alternate K steps (a TMA issue occupies its thread for
+        // a few hundred cycles)
+        if (lane == 0) {
+            const uint32_t mine = warp == 0 ? 0u : 1u;
+            uint32_t turn = 0u;
+            prefetch_tensormap(&map_a0);
+            prefetch_tensormap(&map_a1);
+            prefetch_tensormap(&map_b);
+            uint32_t s = 0, ph = 0;
+            bool ok = true;
+            for (uint32_t it = blockIdx.x; ok && it < items; it += gridDim.x) {
+                const uint32_t rank = it / tiles, tile = it % tiles;
+                const uint32_t id = a.ids[rank];
+                if (id < a.first_local || id >= a.first_local + a.local_count) continue;
+                const int32_t y = (int32_t)((id - a.first_local) * a.w_rows + tile * 128u);
+                const int32_t yb = a.shared_vector ? 0 : (int32_t)(2u * rank);
+                for (uint32_t p = 0; ok && p < phases; p++) {
+                    const void *map_a = p == 0 ? (const void *)&map_a0 : (const void *)&map_a1;
+                    for (uint32_t st = 0; st < steps; st++) {
+                        if ((turn++ & 1u) == mine) {
+                            if (!mbar_wait(&empty[s], ph ^ 1u, abort_flag)) { ok = false; break; }
+                            unsigned char *dst = base + s * kStageBytes;
+                            if (a.exp_flags & 2u) {
+                                mbar_arrive_expect_tx(&full[s], kATx);
+                                tma_load_2d(dst, map_a, &full[s], (int32_t)(st * 128u), y);
+                            } else {
+                            mbar_arrive_expect_tx(&full[s], kATx + kBTile);
+                            tma_load_2d(dst, map_a, &full[s], (int32_t)(st * 128u), y);
+                            tma_load_2d(dst + kATile, &map_b, &full[s], (int32_t)(st * 128u), yb);
+                            }
+                        }
+                        if (++s == kStages) { s = 0; ph ^= 1u; }
+                    }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            uint32_t s = 0, ph = 0, buf = 0, pacc = 0, sb = 0, sph = 0;
+            bool ok = true;
+            for (uint32_t it = blockIdx.x; ok && it < items; it += gridDim.x) {
+                const uint32_t rank = it / tiles;
+                const uint32_t id = a.ids[rank];
+                if (id < a.first_local || id >= a.first_local + a.local_count) continue;
+                if (!mbar_wait(&acc_empty[buf], pacc ^ 1u, abort_flag)) break;
+                tc_fence_after();
+                for (uint32_t p = 0; ok && p < phases; p++) {
+                    const uint32_t d = tmem + kAccCol + buf * 32u + p * 16u;
+                    for (uint32_t st = 0; st < steps; st++) {
+                        if (!mbar_wait(&full[s], ph, abort_flag) ||
+                            ((st & 3u) == 0u && !(a.exp_flags & 4u) && !mbar_wait(&sf_full[sb], sph, abort_flag))) {
+                            ok = false;
+                            break;
+                        }
+                        tc_fence_after();
+                        unsigned char *src = base + s * kStageBytes;
+                        const uint64_t da = make_desc_sw128(smem_u32(src));
+                        const uint64_t db = make_desc_sw128(smem_u32(src + kATile));
+#pragma unroll
+                        for (uint32_t j = 0; j < 4u; j++) {
+                            if ((a.exp_flags & 1u) && j != 0u) break;
+                            if ((a.exp_flags & 8u)) break;
+                            const uint32_t sfs = sb * 4u + (st & 3u);
+                            mma_mx(d, da + 2u * j, db + 2u * j, make_idesc_mx(j), tmem + kSfaCol + sfs * 4u,
+                                   tmem + kSfbCol + sfs * 4u, (st | j) != 0u ? 1u : 0u);
+                        }
+                        mma_commit(&empty[s]);
+                        if (++s == kStages) { s = 0; ph ^= 1u; }
+                        if ((st & 3u) == 3u) {
+                            mma_commit(&sf_empty[sb]);
+                            if (++sb == kSfBatches) { sb = 0; sph ^= 1u; }
+                        }
+                    }
+                }
+                if (!ok) break;
+                mma_commit(&acc_full[buf]);
+                if (++buf == 2u) { buf = 0; pacc ^= 1u; }
+            }
+        }
+    } else if (warp < 6) {
+        // scale writers: warp w fills lane quadrant w % 4
+        const uint32_t quad = warp & 3u;
+        const uint32_t lane_base = (32u * quad) << 16;
+        const uint32_t pitch = a.k / 32u;
+        uint32_t sb = 0, sph = 0;
+        bool ok = true;
+        for (uint32_t it = blockIdx.x; ok && it < items; it += gridDim.x) {
+            const uint32_t rank = it / tiles, tile = it % tiles;
+            const uint32_t id = a.ids[rank];
+            if (id < a.first_local || id >= a.first_local + a.local_count) continue;
+            const uint64_t row0 = (uint64_t)(id - a.first_local) * a.w_rows + tile * 128u;
+            const uint8_t *sfb_row = a.sfb + (uint64_t)(a.shared_vector ? 0u : rank) * pitch;
+            for (uint32_t p = 0; ok && p < phases; p++) {
+                const uint8_t *table = p == 0 ? a.scales_a0 : a.scales_a1;
+                const uint8_t *r0 = table + (row0 + lane) * pitch;
+                // 16 bytes per row = the scales of 4 steps; rows lane, lane+32, lane+64, lane+96
+                uint4 v[4], vb;
+#pragma unroll
+                for (uint32_t c = 0; c < 4u; c++) v[c] = *reinterpret_cast<const uint4 *>(r0 + (uint64_t)(32u * c) * pitch);
+                vb = *reinterpret_cast<const uint4 *>(sfb_row);
+                for (uint32_t st = 0; st < steps; st += 4u) {
+                    uint4 cur[4];
+#pragma unroll
+                    for (uint32_t c = 0; c < 4u; c++) cur[c] = v[c];
+                    const uint4 curb = vb;
+                    if (st + 4u < steps) {          // prefetch the next four steps
+#pragma unroll
+                        for (uint32_t c = 0; c < 4u; c++) {
+                            v[c] = *reinterpret_cast<const uint4 *>(r0 + (uint64_t)(32u * c) * pitch + (st + 4u) * 4u);
+                        }
+                        vb = *reinterpret_cast<const uint4 *>(sfb_row + (st + 4u) * 4u);
+                    }
+                    if (!mbar_wait(&sf_empty[sb], sph ^ 1u, abort_flag)) { ok = false; break; }
+                    tc_fence_after();
+                    // column (step q, row group c) = q * 4 + c of the batch's 16 columns
+                    const uint32_t va[16] = {cur[0].x, cur[1].x, cur[2].x, cur[3].x, cur[0].y, cur[1].y,
+                                             cur[2].y, cur[3].y, cur[0].z, cur[1].z, cur[2].z, cur[3].z,
+                                             cur[0].w, cur[1].w, cur[2].w, cur[3].w};
+                    const uint32_t vbb[16] = {curb.x, curb.x, curb.x, curb.x, curb.y, curb.y, curb.y, curb.y,
+                                              curb.z, curb.z, curb.z, curb.z, curb.w, curb.w, curb.w, curb.w};
+                    tmem_st_32x16(tmem + lane_base + kSfaCol + sb * 16u, va);
+                    tmem_st_32x16(tmem + lane_base + kSfbCol + sb * 16u, vbb);
+                    tmem_st_wait();
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&sf_full[sb]);
+                    if (++sb == kSfBatches) { sb = 0; sph ^= 1u; }
+                }
+            }
+        }
+    } else if (warp < 10) {
+        // epilogue: warp w reads lane quadrant w % 4
+        const uint32_t quad = warp & 3u;
+        const uint32_t m = 32u * quad + lane;
+        uint32_t buf = 0, pacc = 0;
+        for (uint32_t it = blockIdx.x; it < items; it += gridDim.x) {
+            const uint32_t rank = it / tiles, tile = it % tiles;
+            const uint32_t id = a.ids[rank];
+            if (id < a.first_local || id >= a.first_local + a.local_count) continue;
+            if (!mbar_wait(&acc_full[buf], pacc, abort_flag)) break;
+            tc_fence_after();
+            const uint32_t t0 = tmem + ((32u * quad) << 16) + kAccCol + buf * 32u;
+            uint32_t h0, l0, h1 = 0, l1 = 0;
+            tmem_ld_32x2(t0, h0, l0);
+            if (kGateUp) tmem_ld_32x2(t0 + 16u, h1, l1);
+            tmem_ld_wait();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&acc_empty[buf]);
+            if (++buf == 2u) { buf = 0; pacc ^= 1u; }
+            const float v0 = __uint_as_float(h0) + __uint_as_float(l0);
+            uint16_t *dst = a.out + (uint64_t)rank * a.w_rows + tile * 128u + m;
+            if (kGateUp) {
+                const float v1 = __uint_as_float(h1) + __uint_as_float(l1);
+                const float g = bf16_bits_to_float(float_to_bf16_bits(v0));
+                const float u = bf16_bits_to_float(float_to_bf16_bits(v1));
+                const uint16_t act_bits = float_to_bf16_bits(activation(g, u, a.activation, a.beta, a.linear_beta));
+                *dst = act_bits;
+                if (a.act_hl != nullptr) {
+                    uint8_t hi, lo, sb;
+                    split_block_e4m3(bf16_bits_to_float(act_bits), hi, lo, sb);
+                    const uint32_t col = tile * 128u + m;
+                    a.act_hl[(uint64_t)(2u * rank) * a.w_rows + col] = hi;
+                    a.act_hl[(uint64_t)(2u * rank + 1u) * a.w_rows + col] = lo;
+                    if (lane == 0) a.act_sf[(uint64_t)rank * (a.w_rows / 32u) + col / 32u] = sb;
+                }
+            } else {
+                *dst = float_to_bf16_bits(v0);
+            }
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (threadIdx.x == 0 && *abort_flag != 0u) atomicExch(&g_mx_status, 1u);
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem, kTmemCols);
+    }
+}
+
+// ---- activation split: bf16 rows -> interleaved E4M3 rows [2*vectors, K] (row 2v = hi,
+// 2v+1 = lo) and E8M0 block scales [vectors, K/32]; one warp per 32-element block.
+__global__ void __launch_bounds__(256)
+split_e4m3_kernel(uint8_t *__restrict__ hl, uint8_t *__restrict__ sf, const uint16_t *__restrict__ x,
+                  uint32_t vectors, uint32_t k) {
+    const uint32_t lane = threadIdx.x % kWarp;
+    const uint32_t blocks_per_row = k / 32u;
+    const uint32_t total = vectors * blocks_per_row;
+    const uint32_t warps = (gridDim.x * blockDim.x) / kWarp;
+    for (uint32_t b = (blockIdx.x * blockDim.x + threadIdx.x) / kWarp; b < total; b += warps) {
+        const uint32_t v = b / blocks_per_row, blk = b % blocks_per_row;
+        const float val = bf16_bits_to_float(x[(uint64_t)v * k + blk * 32u + lane]);
+        const float mx = warp_max(fabsf(val));
+        int e = 0;
+        if (mx > 0.f && mx < 3.0e38f) e = (int)((__float_as_uint(mx) >> 23) & 0xffu) - 127 - 7;
+        e = max(-127, min(127, e));
+        const float scaled = val * __uint_as_float((uint32_t)(127 - e) << 23);      // |scaled| < 256
+        const __nv_fp8_storage_t hi = __nv_cvt_float_to_fp8(scaled, __NV_SATFINITE, __NV_E4M3);
+        const float hi_f = __half2float(__half(__nv_cvt_fp8_to_halfraw(hi, __NV_E4M3)));
+        const __nv_fp8_storage_t lo = __nv_cvt_float_to_fp8(scaled - hi_f, __NV_SATFINITE, __NV_E4M3);
+        hl[(uint64_t)(2u * v) * k + blk * 32u + lane] = hi;
+        hl[(uint64_t)(2u * v + 1u) * k + blk * 32u + lane] = lo;
+        if (lane == 0) sf[(uint64_t)v * blocks_per_row + blk] = (uint8_t)(e + 127);
+    }
+}
+
+PFN_cuTensorMapEncodeTiled_v12000 encode_fn() {
+    static PFN_cuTensorMapEncodeTiled_v12000 fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void *p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess) {
+            fn = (PFN_cuTensorMapEncodeTiled_v12000)p;
+        } else {
+            (void)cudaGetLastError();
+        }
+    });
+    return fn;
+}
+
+bool map_fp4(CUtensorMap *map, const void *ptr, uint64_t rows, uint64_t k) {
+    auto fn = encode_fn();
+    if (!fn || (((uintptr_t)ptr) & 31u) != 0) return false;
+    const cuuint64_t dims[2] = {k, rows};
+    const cuuint64_t strides[1] = {k / 2u};
+    const cuuint32_t box[2] = {128, 128};
+    const cuuint32_t es[2] = {1, 1};
+    return fn(map, CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B, 2, const_cast<void *>(ptr), dims, strides, box,
+              es, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+              CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+bool map_u8(CUtensorMap *map, const void *ptr, uint64_t rows, uint64_t k) {
+    auto fn = encode_fn();
+    if (!fn || (((uintptr_t)ptr) & 15u) != 0) return false;
+    const cuuint64_t dims[2] = {k, rows};
+    const cuuint64_t strides[1] = {k};
+    const cuuint32_t box[2] = {128, 16};
+    const cuuint32_t es[2] = {1, 1};
+    return fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void *>(ptr), dims, strides, box, es,
+              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+}  // namespace
+
+uint32_t k3_decode_mx_status() {
+    uint32_t v = 0xffffffffu;
+    if (cudaMemcpyFromSymbol(&v, g_mx_status, sizeof(v)) != cudaSuccess) (void)cudaGetLastError();
+    return v;
+}
+
+size_t k3_decode_mx_scratch_bytes(const k3_moe_layer_desc *d) {
+    return (size_t)2 * d->hidden + d->hidden / 32u + (size_t)2 * d->top_k * d->expert_hidden +
+           (size_t)d->top_k * d->expert_hidden / 32u + 4u * 256u;
+}
+
+bool k3_decode_mx_supported(const k3_moe_layer_desc *d) {
+    return d->hidden % 512u == 0 && d->expert_hidden % 512u == 0 && d->top_k <= 32u && encode_fn() != nullptr &&
+           d->shared_hidden <= 8192u &&
+           ((((uintptr_t)d->w1_packed) | ((uintptr_t)d->w3_packed) | ((uintptr_t)d->w2_packed)) & 31u) == 0 &&
+           ((((uintptr_t)d->w1_scales) | ((uintptr_t)d->w3_scales) | ((uintptr_t)d->w2_scales)) & 15u) == 0;
+}
+
+// Routed experts of one token: act [top_k, I] and rows_out [top_k, hidden] in rank
+// order (ids on the device), plus - riding along on spare warps - the shared
+// expert: sh_gate / sh_up [S] next to the gate/up products and sh_out [hidden]
+// next to the down products.
+bool k3_decode_mx_experts(const k3_moe_layer_desc *d, const void *x, const void *ids, void *act,
+                          void *rows_out, void *sh_gate, void *sh_up, void *sh_out, void *scratch,
+                          cudaStream_t stream) {
+    const uint32_t H = d->hidden, I = d->expert_hidden, k = d->top_k, S = d->shared_hidden;
+    auto align = [](uint8_t *p) { return (uint8_t *)(((uintptr_t)p + 255u) & ~(uintptr_t)255u); };
+    uint8_t *x_hl = align((uint8_t *)scratch);
+    uint8_t *x_sf = align(x_hl + (size_t)2 * H);
+    uint8_t *a_hl = align(x_sf + H / 32u);
+    uint8_t *a_sf = align(a_hl + (size_t)2 * k * I);
+    const size_t smem = kSmemBytes + (size_t)S * 2u;
+    static size_t configured = 0;
+    if (configured < smem) {
+        if (cudaFuncSetAttribute(decode_mx_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess ||
+            cudaFuncSetAttribute(decode_mx_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
+            (void)cudaGetLastError();
+            return false;
+        }
+        configured = smem;
+    }
+    const uint64_t total = (uint64_t)d->local_expert_count;
+    CUtensorMap m1, m3, m2, mbx, mba;
+    if (!map_fp4(&m1, d->w1_packed, total * I, H) || !map_fp4(&m3, d->w3_packed, total * I, H) ||
+        !map_fp4(&m2, d->w2_packed, total * H, I) || !map_u8(&mbx, x_hl, 2, H) ||
+        !map_u8(&mba, a_hl, 2ull * k, I)) {
+        return false;
+    }
+    MxArgs a{};
+    a.ids = (const uint32_t *)ids;
+    a.ranks = k;
+    a.first_local = d->local_expert_first;
+    a.local_count = d->local_expert_count;
+    a.activation = d->activation;
+    a.beta = d->beta;
+    a.linear_beta = d->linear_beta;
+    a.q8_block = d->q8_block;
+    a.q8_scale_f16 = d->q8_scale_type;
+    const int sms = sm_count();
+    // gate/up + activation (+ shared gate/up rows)
+    split_e4m3_kernel<<<(H / 32u + 7u) / 8u, 256, 0, stream>>>(x_hl, x_sf, (const uint16_t *)x, 1u, H);
+    a.scales_a0 = (const uint8_t *)d->w1_scales;
+    a.scales_a1 = (const uint8_t *)d->w3_scales;
+    a.sfb = x_sf;
+    a.out = (uint16_t *)act;
+    a.act_hl = a_hl;
+    a.act_sf = a_sf;
+    a.w_rows = I;
+    a.k = H;
+    a.shared_vector = 1u;
+    const bool side = S != 0 && getenv("K3_MX_NOSIDE") == nullptr;
+    a.exp_flags = getenv("K3_MX_EXP") ? (uint32_t)atoi(getenv("K3_MX_EXP")) : 0u;
+    if (side) {
+        a.q8_q0 = (const int8_t *)d->shared_gate_q; a.q8_s0 = d->shared_gate_s; a.q8_out0 = (uint16_t *)sh_gate;
+        a.q8_q1 = (const int8_t *)d->shared_up_q;   a.q8_s1 = d->shared_up_s;   a.q8_out1 = (uint16_t *)sh_up;
+        a.q8_x = (const uint16_t *)x;
+        a.q8_rows = S;
+        a.q8_cols = H;
+    }
+    decode_mx_kernel<true><<<sms, kThreads, smem, stream>>>(m1, m3, mbx, a);
+    if (!launch_ok()) return false;
+    // down (+ shared down rows on act(sh_gate, sh_up))
+    a.scales_a0 = a.scales_a1 = (const uint8_t *)d->w2_scales;
+    a.sfb = a_sf;
+    a.out = (uint16_t *)rows_out;
+    a.act_hl = nullptr;
+    a.act_sf = nullptr;
+    a.w_rows = H;
+    a.k = I;
+    a.shared_vector = 0u;
+    if (side) {
+        a.q8_q0 = (const int8_t *)d->shared_down_q; a.q8_s0 = d->shared_down_s; a.q8_out0 = (uint16_t *)sh_out;
+        a.q8_q1 = nullptr; a.q8_s1 = nullptr; a.q8_out1 = nullptr;
+        a.q8_x = nullptr;
+        a.q8_gate = (const uint16_t *)sh_gate;
+        a.q8_up = (const uint16_t *)sh_up;
+        a.q8_rows = H;
+        a.q8_cols = S;
+    }
+    decode_mx_kernel<false><<<sms, kThreads, smem, stream>>>(m2, m2, mba, a);
+    return launch_ok();
+}

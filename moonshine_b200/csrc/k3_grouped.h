@@ -31,4 +31,13 @@ bool k3_grouped_tc_experts(const k3_moe_layer_desc *desc, void *rows_out, void *
 bool k3_decode_supported(const k3_moe_layer_desc *desc);
 bool k3_decode_layer(const k3_moe_layer_desc *desc, const void *x, void *logits, void *ids,
                      void *weights, void *sh_gate, void *sh_up, void *sh_act, void *sh_out,
-                     void *act, void *rows_out, cudaStream_t stream);
+                     void *act, void *rows_out, void *scratch, size_t scratch_bytes,
+                     cudaStream_t stream);
+
+// Block-scaled tensor-core expert products for one token (k3_decode_mx.cu).
+bool k3_decode_mx_supported(const k3_moe_layer_desc *desc);
+size_t k3_decode_mx_scratch_bytes(const k3_moe_layer_desc *desc);
+bool k3_decode_mx_experts(const k3_moe_layer_desc *desc, const void *x, const void *ids, void *act,
+                          void *rows_out, void *sh_gate, void *sh_up, void *sh_out, void *scratch,
+                          cudaStream_t stream);
+uint32_t k3_decode_mx_status();

@@ -110,8 +110,10 @@ combine_kernel(uint16_t *__restrict__ out, const uint16_t *__restrict__ rows,
             idx_s[threadIdx.x] = index ? index[route] : route;
         }
         __syncthreads();
-        for (uint32_t c = threadIdx.x; c < hidden / 8u; c += blockDim.x) {
+        for (uint32_t c = blockIdx.y * blockDim.x + threadIdx.x; c < hidden / 8u;
+             c += gridDim.y * blockDim.x) {
             float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll 4
             for (uint32_t r = 0; r < top_k; r++) {
                 const uint4 q = reinterpret_cast<const uint4 *>(rows + (uint64_t)idx_s[r] * hidden)[c];
                 const float w = w_s[r];
@@ -349,8 +351,12 @@ extern "C" bool k3_moe_combine(void *out, const void *rows, const void *index,
         return false;
     }
     if ((((uintptr_t)out | (uintptr_t)rows | (uintptr_t)shared) & 15u) != 0) return false;
-    const uint32_t blocks = std::min<uint32_t>(tokens, (uint32_t)sm_count() * 8u);
-    combine_kernel<<<blocks, 256, 0, (cudaStream_t)stream>>>(
+    // few tokens: spread the columns of a token over several small CTAs
+    const bool few = tokens < 128u;
+    const uint32_t threads = few ? 64u : 256u;
+    const dim3 grid(std::min<uint32_t>(tokens, (uint32_t)sm_count() * 8u),
+                    few ? (hidden / 8u + threads - 1u) / threads : 1u);
+    combine_kernel<<<grid, threads, 0, (cudaStream_t)stream>>>(
         (uint16_t *)out, (const uint16_t *)rows, (const uint32_t *)index, (const float *)weights,
         (const uint16_t *)shared, tokens, top_k, hidden);
     return launch_ok();
@@ -382,7 +388,8 @@ bool layer_forward_impl(const k3_moe_layer_desc *d, void *out, const void *x, ui
         // one token: persistent matrix-vector kernels, rows stay in rank order
         if (!mark(events, 1, stream) || !mark(events, 2, stream) || !mark(events, 3, stream)) return false;
         if (!k3_decode_layer(d, x, w.logits, w.ids, w.weights, w.sh_gate, w.sh_up, w.sh_act,
-                             w.sh_out, w.act, w.rows_out, stream)) {
+                             w.sh_out, w.act, w.rows_out, w.rows_in,
+                             (size_t)routes * d->hidden * 2u, stream)) {
             return false;
         }
     } else {

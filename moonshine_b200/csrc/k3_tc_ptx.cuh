@@ -86,6 +86,12 @@ K3_DEVINL void tma_load_2d(void *dst, const void *map, uint64_t *bar, int32_t x,
         : "memory");
 }
 
+// 2-D tiled prefetch global -> L2 only (no shared-memory destination, no barrier).
+K3_DEVINL void tma_prefetch_2d(const void *map, int32_t x, int32_t y) {
+    asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];" ::"l"(map), "r"(x), "r"(y)
+                 : "memory");
+}
+
 // -------------------------------------------------------------- tensor memory
 K3_DEVINL void tmem_alloc(uint32_t *dst_smem, uint32_t columns) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
