@@ -126,6 +126,24 @@ bool k3_moe_experts_grouped(const k3_moe_layer_desc *desc, void *rows_out,
                             void *act, const void *rows_in,
                             const void *offsets, uint32_t rows, void *stream);
 
+/* The same products on the block-scaled tensor-core path, which needs device
+ * scratch for the two-term E4M3 form of the rows and of the activation:
+ * k3_moe_experts_workspace_bytes(desc, rows, source_rows) bytes (0 when the
+ * layer shape or row count does not suit the path).  `index` (u32 per row on
+ * the device, or NULL) gathers rows_in: product row r reads rows_in[index[r]]
+ * and rows_in has source_rows rows, which folds gather_rows_bf16
+ * (k3_engine_prefill.inc:1203) into the conversion; with index NULL pass
+ * source_rows 0.  `act` may be NULL on this path.  Falls back to
+ * k3_moe_experts_grouped when workspace is NULL or too small, index is NULL
+ * and act is given; fails otherwise. */
+size_t k3_moe_experts_workspace_bytes(const k3_moe_layer_desc *desc, uint32_t rows,
+                                      uint32_t source_rows);
+bool k3_moe_experts_grouped_ws(const k3_moe_layer_desc *desc, void *rows_out,
+                               void *act, const void *rows_in, const void *index,
+                               uint32_t source_rows, const void *offsets,
+                               uint32_t rows, void *workspace,
+                               size_t workspace_bytes, void *stream);
+
 /* Shared expert for `tokens` rows: out bf16 [tokens, d]; gate/up/act are
  * scratch bf16 [tokens, S] (k3_engine_prefill.inc:1530-1551). */
 bool k3_moe_shared_expert(const k3_moe_layer_desc *desc, void *out, void *gate,

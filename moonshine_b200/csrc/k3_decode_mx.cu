@@ -33,7 +33,6 @@
 #include <cuda_fp8.h>
 
 #include <algorithm>
-#include <cstdlib>
 #include <mutex>
 
 using namespace k3;
@@ -115,7 +114,6 @@ struct MxArgs {
     const uint16_t *q8_gate, *q8_up;
     uint32_t q8_rows, q8_cols, q8_block;
     int q8_scale_f16;
-    uint32_t exp_flags;         // timing experiments only
 };
 
 // value -> (hi, lo) E4M3 pair and block scale of a 32-element block held one
@@ -224,14 +222,9 @@ decode_mx_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_consta
                         if ((turn++ & 1u) == mine) {
                             if (!mbar_wait(&empty[s], ph ^ 1u, abort_flag)) { ok = false; break; }
                             unsigned char *dst = base + s * kStageBytes;
-                            if (a.exp_flags & 2u) {
-                                mbar_arrive_expect_tx(&full[s], kATx);
-                                tma_load_2d(dst, map_a, &full[s], (int32_t)(st * 128u), y);
-                            } else {
                             mbar_arrive_expect_tx(&full[s], kATx + kBTile);
                             tma_load_2d(dst, map_a, &full[s], (int32_t)(st * 128u), y);
                             tma_load_2d(dst + kATile, &map_b, &full[s], (int32_t)(st * 128u), yb);
-                            }
                         }
                         if (++s == kStages) { s = 0; ph ^= 1u; }
                     }
@@ -252,7 +245,7 @@ decode_mx_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_consta
                     const uint32_t d = tmem + kAccCol + buf * 32u + p * 16u;
                     for (uint32_t st = 0; st < steps; st++) {
                         if (!mbar_wait(&full[s], ph, abort_flag) ||
-                            ((st & 3u) == 0u && !(a.exp_flags & 4u) && !mbar_wait(&sf_full[sb], sph, abort_flag))) {
+                            ((st & 3u) == 0u && !mbar_wait(&sf_full[sb], sph, abort_flag))) {
                             ok = false;
                             break;
                         }
@@ -262,8 +255,6 @@ decode_mx_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_consta
                         const uint64_t db = make_desc_sw128(smem_u32(src + kATile));
 #pragma unroll
                         for (uint32_t j = 0; j < 4u; j++) {
-                            if ((a.exp_flags & 1u) && j != 0u) break;
-                            if ((a.exp_flags & 8u)) break;
                             const uint32_t sfs = sb * 4u + (st & 3u);
                             mma_mx(d, da + 2u * j, db + 2u * j, make_idesc_mx(j), tmem + kSfaCol + sfs * 4u,
                                    tmem + kSfbCol + sfs * 4u, (st | j) != 0u ? 1u : 0u);
@@ -521,8 +512,7 @@ bool k3_decode_mx_experts(const k3_moe_layer_desc *d, const void *x, const void 
     a.w_rows = I;
     a.k = H;
     a.shared_vector = 1u;
-    const bool side = S != 0 && getenv("K3_MX_NOSIDE") == nullptr;
-    a.exp_flags = getenv("K3_MX_EXP") ? (uint32_t)atoi(getenv("K3_MX_EXP")) : 0u;
+    const bool side = S != 0;
     if (side) {
         a.q8_q0 = (const int8_t *)d->shared_gate_q; a.q8_s0 = d->shared_gate_s; a.q8_out0 = (uint16_t *)sh_gate;
         a.q8_q1 = (const int8_t *)d->shared_up_q;   a.q8_s1 = d->shared_up_s;   a.q8_out1 = (uint16_t *)sh_up;

@@ -41,3 +41,15 @@ bool k3_decode_mx_experts(const k3_moe_layer_desc *desc, const void *x, const vo
                           void *rows_out, void *sh_gate, void *sh_up, void *sh_out, void *scratch,
                           cudaStream_t stream);
 uint32_t k3_decode_mx_status();
+
+// Block-scaled tensor-core grouped expert products for many rows
+// (k3_grouped_mx.cu).  `index` (u32 per row, or null) gathers rows_in, which then
+// has source_rows rows; `act` may be null.
+bool k3_grouped_mx_supported(const k3_moe_layer_desc *desc, uint32_t rows);
+size_t k3_grouped_mx_workspace_bytes(const k3_moe_layer_desc *desc, uint32_t rows,
+                                     uint32_t source_rows);
+bool k3_grouped_mx_experts(const k3_moe_layer_desc *desc, void *rows_out, void *act,
+                           const void *rows_in, const void *index, uint32_t source_rows,
+                           const void *offsets, uint32_t rows, void *workspace,
+                           cudaStream_t stream);
+uint32_t k3_grouped_mx_status();

@@ -70,16 +70,21 @@ struct TcArgs {
 
 template <int kA>
 struct Cfg {
-    static constexpr uint32_t kPackedRowBytes = kA == kAMxfp4 ? BK / 2 : (kA == kAQ8 ? BK : 0);
-    static constexpr uint32_t kPackedTile = kPackedRowBytes * BM;          // 4096 / 8192 / 0
-    static constexpr uint32_t kATile = BM * BK * 2;                        // 16384
-    static constexpr uint32_t kBTile = BN * BK * 2;                        // 16384
     static constexpr bool kDequant = kA != kABf16;
-    // TMA ring stage: [packed0 | packed1 | B] (dequant) or [A0 | A1 | B] (bf16)
-    static constexpr uint32_t kStageBytes = kDequant ? 2 * kPackedTile + kBTile : 2 * kATile + kBTile;
-    static constexpr uint32_t kStages = kA == kAQ8 ? 3 : 4;
-    static constexpr uint32_t kAStages = kDequant ? 3 : 0;
-    static constexpr uint32_t kRingBytes = kStages * kStageBytes + kAStages * 2 * kATile;
+    static constexpr uint32_t kATile = BM * BK * 2;                        // 16384 (bf16, one K step)
+    static constexpr uint32_t kBTile = BN * BK * 2;                        // 16384
+    // Packed weights travel in 128-byte rows (the TMA engine spends about the same
+    // time on a box row whatever its length), i.e. several K steps per packed stage:
+    // 256 columns of MXFP4 or 128 of int8.
+    static constexpr uint32_t kPackSteps = kA == kAMxfp4 ? 4 : (kA == kAQ8 ? 2 : 1);
+    static constexpr uint32_t kPackedTile = kDequant ? BM * 128u : 0u;     // 16384
+    static constexpr uint32_t kPStages = kDequant ? 2 : 0;                 // packed ring: [tile0 | tile1]
+    // token ring stage: [B] (dequant) or [A0 | A1 | B] (bf16, everything by TMA)
+    static constexpr uint32_t kStageBytes = kDequant ? kBTile : 2 * kATile + kBTile;
+    static constexpr uint32_t kStages = 4;
+    static constexpr uint32_t kAStages = kDequant ? 2 : 0;                 // dequantised ring: [A0 | A1]
+    static constexpr uint32_t kRingBytes =
+        kStages * kStageBytes + kPStages * 2 * kPackedTile + kAStages * 2 * kATile;
     static constexpr uint32_t kSmemBytes = kRingBytes + 1024 /*align*/ + 512 /*barriers*/ +
                                            (kMaxGroups + 1) * 4;
 };
@@ -155,14 +160,17 @@ grouped_tc_kernel(const __grid_constant__ CUtensorMap map_a0,
     extern __shared__ unsigned char smem_raw[];
     const uint32_t raw_addr = smem_u32(smem_raw);
     unsigned char *base = smem_raw + ((1024u - (raw_addr & 1023u)) & 1023u);
-    unsigned char *ring = base;                                     // TMA ring
-    unsigned char *aring = base + C::kStages * C::kStageBytes;      // dequantised A ring
+    unsigned char *ring = base;                                     // token (or all-TMA) ring
+    unsigned char *pring = base + C::kStages * C::kStageBytes;      // packed weight ring
+    unsigned char *aring = pring + C::kPStages * 2u * C::kPackedTile;   // dequantised A ring
     uint64_t *bars = reinterpret_cast<uint64_t *>(base + C::kRingBytes);
     uint64_t *full = bars;                         // [kStages]
     uint64_t *empty = full + C::kStages;           // [kStages]
     uint64_t *a_full = empty + C::kStages;         // [kAStages]
     uint64_t *a_empty = a_full + 4;                // [kAStages]
-    uint64_t *acc_full = a_empty + 4;              // [2]
+    uint64_t *p_full = a_empty + 4;                // [kPStages]
+    uint64_t *p_empty = p_full + 2;                // [kPStages]
+    uint64_t *acc_full = p_empty + 2;              // [2]
     uint64_t *acc_empty = acc_full + 2;            // [2]
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(acc_empty + 2);
     volatile uint32_t *abort_flag = tmem_slot + 1;
@@ -177,7 +185,11 @@ grouped_tc_kernel(const __grid_constant__ CUtensorMap map_a0,
         *abort_flag = 0u;
         for (uint32_t s = 0; s < C::kStages; s++) {
             mbar_init(&full[s], 1);
-            mbar_init(&empty[s], C::kDequant ? kDequantWarps + 1 : 1);
+            mbar_init(&empty[s], 1);
+        }
+        for (uint32_t s = 0; s < C::kPStages; s++) {
+            mbar_init(&p_full[s], 1);
+            mbar_init(&p_empty[s], kDequantWarps);
         }
         for (uint32_t s = 0; s < C::kAStages; s++) {
             mbar_init(&a_full[s], kDequantWarps);
@@ -240,22 +252,27 @@ grouped_tc_kernel(const __grid_constant__ CUtensorMap map_a0,
             prefetch_tensormap(&map_a0);
             prefetch_tensormap(&map_a1);
             prefetch_tensormap(&map_b);
-            uint32_t s = 0, ph = 0;
+            uint32_t s = 0, ph = 0, ps = 0, pph = 0;
             bool ok = true;
             for (uint32_t w = blockIdx.x; ok && w < total_items; w += gridDim.x) {
                 const Item it = decode_item(w, prefix, a);
                 const int32_t y0 = (int32_t)(it.group * a.w_rows + it.m_item * (kE == kEAct ? BM : 2u * BM));
                 const int32_t y1 = kE == kEAct ? y0 : y0 + (int32_t)BM;
                 for (uint32_t ks = 0; ks < ksteps; ks++) {
+                    if (C::kDequant && (ks % C::kPackSteps) == 0u) {
+                        if (!mbar_wait(&p_empty[ps], pph ^ 1u, abort_flag)) { ok = false; break; }
+                        unsigned char *pt = pring + ps * 2u * C::kPackedTile;
+                        mbar_arrive_expect_tx(&p_full[ps], 2u * C::kPackedTile);
+                        const int32_t xb = (int32_t)((ks / C::kPackSteps) * 128u);      // bytes
+                        tma_load_2d(pt, &map_a0, &p_full[ps], xb, y0);
+                        tma_load_2d(pt + C::kPackedTile, &map_a1, &p_full[ps], xb, y1);
+                        if (++ps == C::kPStages) { ps = 0; pph ^= 1u; }
+                    }
                     if (!mbar_wait(&empty[s], ph ^ 1u, abort_flag)) { ok = false; break; }
                     unsigned char *st = ring + s * C::kStageBytes;
                     mbar_arrive_expect_tx(&full[s], C::kStageBytes);
                     if (C::kDequant) {
-                        const int32_t xb = (int32_t)(ks * C::kPackedRowBytes);
-                        tma_load_2d(st, &map_a0, &full[s], xb, y0);
-                        tma_load_2d(st + C::kPackedTile, &map_a1, &full[s], xb, y1);
-                        tma_load_2d(st + 2 * C::kPackedTile, &map_b, &full[s], (int32_t)(ks * BK),
-                                    (int32_t)it.row_start);
+                        tma_load_2d(st, &map_b, &full[s], (int32_t)(ks * BK), (int32_t)it.row_start);
                     } else {
                         tma_load_2d(st, &map_a0, &full[s], (int32_t)(ks * BK), y0);
                         tma_load_2d(st + C::kATile, &map_a1, &full[s], (int32_t)(ks * BK), y1);
@@ -287,7 +304,7 @@ grouped_tc_kernel(const __grid_constant__ CUtensorMap map_a0,
                         if (!mbar_wait(&a_full[sa], pha, abort_flag)) { ok = false; break; }
                         a0_addr = smem_u32(aring + sa * 2u * C::kATile);
                         a1_addr = a0_addr + C::kATile;
-                        b_addr = smem_u32(st + 2 * C::kPackedTile);
+                        b_addr = smem_u32(st);
                     } else {
                         a0_addr = smem_u32(st);
                         a1_addr = a0_addr + C::kATile;
@@ -365,7 +382,7 @@ grouped_tc_kernel(const __grid_constant__ CUtensorMap map_a0,
         // ====================================================== dequantisers
         const uint32_t t = threadIdx.x - 8u * kWarp;     // 0..255
         const uint32_t row = t & 127u, half = t >> 7;    // weight row in tile, 32-column half
-        uint32_t s = 0, ph = 0, sa = 0, pha = 0;
+        uint32_t ps = 0, pph = 0, sa = 0, pha = 0;
         bool ok = true;
         const uint64_t total_w_rows = (uint64_t)a.groups * a.w_rows;
         for (uint32_t w = blockIdx.x; ok && w < total_items; w += gridDim.x) {
@@ -384,12 +401,17 @@ grouped_tc_kernel(const __grid_constant__ CUtensorMap map_a0,
                     sc0 = *reinterpret_cast<const uint4 *>(srow0 + (ks >> 3) * 16u);
                     sc1 = *reinterpret_cast<const uint4 *>(srow1 + (ks >> 3) * 16u);
                 }
-                if (!mbar_wait(&full[s], ph, abort_flag)) { ok = false; break; }
-                const unsigned char *st = ring + s * C::kStageBytes;
+                const uint32_t sub = ks % C::kPackSteps;
+                if (sub == 0u && !mbar_wait(&p_full[ps], pph, abort_flag)) { ok = false; break; }
+                // packed tiles are 128-byte rows written with the 128-byte swizzle: 16-byte
+                // chunk c of row r sits at chunk position c ^ (r % 8)
+                const unsigned char *pt0 = pring + ps * 2u * C::kPackedTile + row * 128u;
+                const unsigned char *pt1 = pt0 + C::kPackedTile;
                 uint32_t o0[16], o1[16];          // 32 bf16 per tile
                 if (kA == kAMxfp4) {
-                    const uint4 p0 = *reinterpret_cast<const uint4 *>(st + row * 32u + half * 16u);
-                    const uint4 p1 = *reinterpret_cast<const uint4 *>(st + C::kPackedTile + row * 32u + half * 16u);
+                    const uint32_t chunk = ((sub * 2u + half) ^ (row & 7u)) * 16u;
+                    const uint4 p0 = *reinterpret_cast<const uint4 *>(pt0 + chunk);
+                    const uint4 p1 = *reinterpret_cast<const uint4 *>(pt1 + chunk);
                     const uint32_t bi = (ks & 7u) * 2u + half;        // byte inside the 16-byte scale chunk
                     const uint32_t wi = bi >> 2;
                     const uint32_t ws0 = wi == 0u ? sc0.x : (wi == 1u ? sc0.y : (wi == 2u ? sc0.z : sc0.w));
@@ -418,11 +440,11 @@ grouped_tc_kernel(const __grid_constant__ CUtensorMap map_a0,
                         f0 = reinterpret_cast<const float *>(a.scales0)[yc0 * pitch + sidx];
                         f1 = reinterpret_cast<const float *>(a.scales1)[yc1 * pitch + sidx];
                     }
-                    const uint4 *q0 = reinterpret_cast<const uint4 *>(st + row * 64u + half * 32u);
-                    const uint4 *q1 = reinterpret_cast<const uint4 *>(st + C::kPackedTile + row * 64u + half * 32u);
 #pragma unroll
                     for (int h = 0; h < 2; h++) {
-                        const uint4 a4 = q0[h], b4 = q1[h];
+                        const uint32_t chunk = ((sub * 4u + half * 2u + (uint32_t)h) ^ (row & 7u)) * 16u;
+                        const uint4 a4 = *reinterpret_cast<const uint4 *>(pt0 + chunk);
+                        const uint4 b4 = *reinterpret_cast<const uint4 *>(pt1 + chunk);
                         const uint32_t aw[4] = {a4.x, a4.y, a4.z, a4.w};
                         const uint32_t bw[4] = {b4.x, b4.y, b4.z, b4.w};
 #pragma unroll
@@ -439,10 +461,12 @@ grouped_tc_kernel(const __grid_constant__ CUtensorMap map_a0,
                         }
                     }
                 }
-                // packed stage consumed (it is in registers now)
-                __syncwarp();
-                if (lane == 0) mbar_arrive(&empty[s]);
-                if (++s == C::kStages) { s = 0; ph ^= 1u; }
+                if (sub == C::kPackSteps - 1u) {
+                    // last quarter of the packed stage is in registers now
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&p_empty[ps]);
+                    if (++ps == C::kPStages) { ps = 0; pph ^= 1u; }
+                }
 
                 if (!mbar_wait(&a_empty[sa], pha ^ 1u, abort_flag)) { ok = false; break; }
                 // row `row` of the tile: 128 bytes at atom (row/8), line (row%8); 16-byte
@@ -515,15 +539,15 @@ bool launch_tc(const void *a0, const void *a1, const TcArgs &args, const void *b
     const uint64_t w_total = (uint64_t)args.groups * args.w_rows;
     bool ok;
     if (kA == kAMxfp4) {
-        ok = make_map(&ma0, a0, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, w_total, args.k / 2u, BK / 2u, BM,
-                      CU_TENSOR_MAP_SWIZZLE_NONE) &&
-             make_map(&ma1, a1, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, w_total, args.k / 2u, BK / 2u, BM,
-                      CU_TENSOR_MAP_SWIZZLE_NONE);
+        ok = make_map(&ma0, a0, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, w_total, args.k / 2u, 128u, BM,
+                      CU_TENSOR_MAP_SWIZZLE_128B) &&
+             make_map(&ma1, a1, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, w_total, args.k / 2u, 128u, BM,
+                      CU_TENSOR_MAP_SWIZZLE_128B);
     } else if (kA == kAQ8) {
-        ok = make_map(&ma0, a0, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, w_total, args.k, BK, BM,
-                      CU_TENSOR_MAP_SWIZZLE_NONE) &&
-             make_map(&ma1, a1, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, w_total, args.k, BK, BM,
-                      CU_TENSOR_MAP_SWIZZLE_NONE);
+        ok = make_map(&ma0, a0, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, w_total, args.k, 128u, BM,
+                      CU_TENSOR_MAP_SWIZZLE_128B) &&
+             make_map(&ma1, a1, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, w_total, args.k, 128u, BM,
+                      CU_TENSOR_MAP_SWIZZLE_128B);
     } else {
         ok = make_map(&ma0, a0, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, w_total, args.k, BK, BM,
                       CU_TENSOR_MAP_SWIZZLE_128B) &&
@@ -556,7 +580,7 @@ bool tc_shape_ok(uint32_t k, uint32_t rows) {
 extern "C" uint32_t k3_moe_device_status(void) {
     uint32_t v = 0xffffffffu;
     if (cudaMemcpyFromSymbol(&v, g_tc_status, sizeof(v)) != cudaSuccess) (void)cudaGetLastError();
-    return v | k3_decode_mx_status();
+    return v | k3_decode_mx_status() | k3_grouped_mx_status();
 }
 
 bool k3_grouped_dense_bf16_f32(void *out, const void *weights, const void *x, uint32_t tokens,

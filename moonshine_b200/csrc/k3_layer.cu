@@ -168,6 +168,8 @@ struct Workspace {
     uint32_t *offsets, *sorted_route, *sorted_token, *inv_perm;
     void *dispatch_ws;
     size_t dispatch_bytes;
+    void *mx_ws;
+    size_t mx_bytes;
     uint16_t *rows_in, *act, *rows_out, *sh_gate, *sh_up, *sh_act, *sh_out;
     size_t total;
 };
@@ -194,6 +196,9 @@ Workspace carve(const k3_moe_layer_desc *d, uint32_t tokens, void *base) {
     w.rows_in = (uint16_t *)take(routes * d->hidden * 2u);
     w.act = (uint16_t *)take(routes * d->expert_hidden * 2u);
     w.rows_out = (uint16_t *)take(routes * d->hidden * 2u);
+    w.mx_bytes = k3_grouped_mx_supported(d, (uint32_t)routes)
+                     ? k3_grouped_mx_workspace_bytes(d, (uint32_t)routes, tokens) : 0;
+    w.mx_ws = take(w.mx_bytes);
     if (d->shared_hidden) {
         w.sh_gate = (uint16_t *)take((size_t)tokens * d->shared_hidden * 2u);
         w.sh_up = (uint16_t *)take((size_t)tokens * d->shared_hidden * 2u);
@@ -326,6 +331,30 @@ extern "C" bool k3_moe_experts_grouped(const k3_moe_layer_desc *d, void *rows_ou
                                d->local_expert_count, false, (cudaStream_t)stream);
 }
 
+extern "C" size_t k3_moe_experts_workspace_bytes(const k3_moe_layer_desc *d, uint32_t rows,
+                                                 uint32_t source_rows) {
+    if (!desc_ok(d) || rows == 0 || !slot_pointers_aligned(d) || !k3_grouped_mx_supported(d, rows)) return 0;
+    return k3_grouped_mx_workspace_bytes(d, rows, source_rows);
+}
+
+extern "C" bool k3_moe_experts_grouped_ws(const k3_moe_layer_desc *d, void *rows_out, void *act,
+                                          const void *rows_in, const void *index,
+                                          uint32_t source_rows, const void *offsets,
+                                          uint32_t rows, void *workspace, size_t workspace_bytes,
+                                          void *stream) {
+    if (!desc_ok(d) || !rows_out || !rows_in || !offsets || rows == 0 || !slot_pointers_aligned(d) ||
+        (index != nullptr && source_rows == 0)) {
+        return false;
+    }
+    const size_t need = k3_moe_experts_workspace_bytes(d, rows, index ? source_rows : 0u);
+    if (need != 0 && workspace && workspace_bytes >= need) {
+        return k3_grouped_mx_experts(d, rows_out, act, rows_in, index, source_rows, offsets, rows,
+                                     workspace, (cudaStream_t)stream);
+    }
+    if (index || !act) return false;
+    return k3_moe_experts_grouped(d, rows_out, act, rows_in, offsets, rows, stream);
+}
+
 extern "C" bool k3_moe_shared_expert(const k3_moe_layer_desc *d, void *out, void *gate, void *up,
                                      void *act, const void *x, uint32_t tokens, void *stream) {
     if (!desc_ok(d) || d->shared_hidden == 0 || !out || !gate || !up || !act || !x ||
@@ -408,13 +437,24 @@ bool layer_forward_impl(const k3_moe_layer_desc *d, void *out, const void *x, ui
         } else {
             if (!k3_moe_dispatch_build(w.offsets, w.sorted_route, w.sorted_token, w.inv_perm, w.ids,
                                        tokens, d->top_k, d->expert_count, w.dispatch_ws,
-                                       w.dispatch_bytes, stream) ||
-                !k3_rocm_gather_rows_bf16(w.rows_in, x, w.sorted_token, routes, d->hidden, stream)) {
+                                       w.dispatch_bytes, stream)) {
                 return false;
             }
-            if (!mark(events, 3, stream)) return false;
-            if (!k3_moe_experts_grouped(d, w.rows_out, w.act, w.rows_in, w.offsets, routes, stream)) {
-                return false;
+            if (w.mx_bytes != 0) {
+                // block-scaled path: tokens are converted once, then gathered as bytes
+                if (!mark(events, 3, stream)) return false;
+                if (!k3_grouped_mx_experts(d, w.rows_out, nullptr, x, w.sorted_token, tokens, w.offsets,
+                                           routes, w.mx_ws, stream)) {
+                    return false;
+                }
+            } else {
+                if (!k3_rocm_gather_rows_bf16(w.rows_in, x, w.sorted_token, routes, d->hidden, stream)) {
+                    return false;
+                }
+                if (!mark(events, 3, stream)) return false;
+                if (!k3_moe_experts_grouped(d, w.rows_out, w.act, w.rows_in, w.offsets, routes, stream)) {
+                    return false;
+                }
             }
             index = w.inv_perm;
         }

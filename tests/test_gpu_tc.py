@@ -102,3 +102,83 @@ def test_grouped_expert_products(oracle, counts):
         down = oracle.mxfp4_gemm(w["w2_packed"][ex], w["w2_scales"][ex], got_act[lo:hi], d, i)
         ref = oracle.mxfp4_gemm_f64(w["w2_packed"][ex], w["w2_scales"][ex], got_act[lo:hi], d, i)
         G.check_mxfp4_envelope(got_out[lo:hi], down, ref)
+
+
+@pytest.mark.parametrize("counts,gathered", [
+    ([0, 5, 130, 128, 1, 300, 17, 64], False),
+    ([0, 5, 130, 128, 1, 300, 17, 64], True),
+    ([33, 0, 0, 0, 0, 0, 0, 0], True),
+    ([0, 0, 0, 700, 0, 0, 0, 1], False),
+])
+def test_grouped_expert_products_block_scaled(oracle, counts, gathered):
+    """Block-scaled tensor-core path (packed E2M1 weights and E8M0 scales consumed
+    as they are, rows as two E4M3 terms): gate/up/activation and down against the
+    oracle, with and without the fused row gather."""
+    d, i, e = 1024, 512, 8
+    cfg = synth.baseline_config(hidden=d, expert_hidden=i, experts=e, top_k=2, shared_hidden=0)
+    w = synth.make_layer(cfg, seed=23)
+    rows = int(sum(counts))
+    x = synth.activations(23, rows, d)
+    offsets = np.concatenate([[0], np.cumsum(counts)]).astype(np.uint32)
+    desc = _native.LayerDesc(hidden=d, expert_hidden=i, expert_count=e, top_k=2, shared_hidden=0,
+                             activation=cfg["activation"], route_scale=1.0, local_expert_count=e)
+    keep = {k: G.dev(w[k]) for k in w if k.startswith("w")}
+    for k, v in keep.items():
+        setattr(desc, k, v.data_ptr())
+    out = G.empty((rows, d), np.uint16)
+    act = G.empty((rows, i), np.uint16)
+    need = ops.k3_moe_experts_workspace_bytes(desc, rows, rows if gathered else 0)
+    assert need > 0
+    ws = torch.empty(need, dtype=torch.uint8, device="cuda")
+    if gathered:
+        perm = np.random.default_rng(5).permutation(rows).astype(np.uint32)
+        index = np.argsort(perm).astype(np.uint32)          # x[perm][index] == x
+        ok = ops.k3_moe_experts_grouped_ws(desc, out, act, G.dev(np.ascontiguousarray(x[perm])),
+                                           G.dev(index), rows, G.dev(offsets), rows, ws, need)
+    else:
+        ok = ops.k3_moe_experts_grouped_ws(desc, out, act, G.dev(x), None, 0, G.dev(offsets), rows,
+                                           ws, need)
+    assert ok
+    status_ok()
+    got_act, got_out = G.host(act, np.uint16), G.host(out, np.uint16)
+    for ex in range(e):
+        lo, hi = int(offsets[ex]), int(offsets[ex + 1])
+        if lo == hi:
+            continue
+        xe = x[lo:hi]
+        gate = oracle.mxfp4_gemm(w["w1_packed"][ex], w["w1_scales"][ex], xe, i, d)
+        up = oracle.mxfp4_gemm(w["w3_packed"][ex], w["w3_scales"][ex], xe, i, d)
+        a = oracle.activation(gate, up, cfg["activation"])
+        # gate and up are rounded to bf16 before the activation on both sides; a last-bit
+        # difference there moves the activation by one bf16 step
+        assert G.rel_l2(got_act[lo:hi], a) <= 1e-3, ex
+        down = oracle.mxfp4_gemm(w["w2_packed"][ex], w["w2_scales"][ex], got_act[lo:hi], d, i)
+        ref = oracle.mxfp4_gemm_f64(w["w2_packed"][ex], w["w2_scales"][ex], got_act[lo:hi], d, i)
+        G.check_mxfp4_envelope(got_out[lo:hi], down, ref)
+
+
+def test_block_scaled_workspace_rules():
+    """Too-small or missing scratch falls back to the bf16 tensor-core path when that
+    is possible (no gather, act given) and fails otherwise."""
+    d, i, e = 1024, 512, 4
+    cfg = synth.baseline_config(hidden=d, expert_hidden=i, experts=e, top_k=2, shared_hidden=0)
+    w = synth.make_layer(cfg, seed=3)
+    rows = 64
+    x = synth.activations(3, rows, d)
+    offsets = np.array([0, 16, 16, 40, 64], np.uint32)
+    desc = _native.LayerDesc(hidden=d, expert_hidden=i, expert_count=e, top_k=2, shared_hidden=0,
+                             activation=cfg["activation"], route_scale=1.0, local_expert_count=e)
+    keep = {k: G.dev(w[k]) for k in w if k.startswith("w")}
+    for k, v in keep.items():
+        setattr(desc, k, v.data_ptr())
+    out, out2 = G.empty((rows, d), np.uint16), G.empty((rows, d), np.uint16)
+    act, act2 = G.empty((rows, i), np.uint16), G.empty((rows, i), np.uint16)
+    xd, od = G.dev(x), G.dev(offsets)
+    index = G.dev(np.arange(rows, dtype=np.uint32))
+    assert ops.k3_moe_experts_grouped_ws(desc, out, act, xd, None, 0, od, rows, None, 0)
+    assert ops.k3_moe_experts_grouped(desc, out2, act2, xd, od, rows)
+    status_ok()
+    assert np.array_equal(G.host(out, np.uint16), G.host(out2, np.uint16))
+    assert not ops.k3_moe_experts_grouped_ws(desc, out, act, xd, index, rows, od, rows, None, 0)
+    assert not ops.k3_moe_experts_grouped_ws(desc, out, None, xd, None, 0, od, rows, None, 0)
+    assert ops.k3_moe_experts_workspace_bytes(desc, 8, 0) == 0        # too few rows for the path
