@@ -18,6 +18,13 @@ bool k3_grouped_q8_bf16(void *out, const void *q, const void *scales, const void
                         uint32_t tokens, uint32_t rows, uint32_t cols, uint32_t block,
                         int scale_type, void *stream);
 
+// Shared expert with its Q8 tables converted to bf16 once per call in `workspace`
+// (k3_grouped_shared_workspace_bytes, 0 when the shape does not suit the path).
+// act bf16 [tokens, S] is scratch, out bf16 [tokens, H].
+size_t k3_grouped_shared_workspace_bytes(const k3_moe_layer_desc *desc, uint32_t tokens);
+bool k3_grouped_shared_expert(const k3_moe_layer_desc *desc, void *out, void *act, const void *x,
+                              uint32_t tokens, void *workspace, cudaStream_t stream);
+
 // true when the grouped tensor-core path can run this layer / row count
 bool k3_grouped_tc_supported(const k3_moe_layer_desc *desc, uint32_t rows);
 

@@ -571,6 +571,33 @@ bool launch_tc(const void *a0, const void *a1, const TcArgs &args, const void *b
     return launch_ok();
 }
 
+// Q8 weights -> bf16 (each product q * scale rounded once, as the in-kernel
+// conversion of the Q8 mode does); 16 elements per thread, block % 16 == 0.
+__global__ void __launch_bounds__(256)
+q8_to_bf16_kernel(uint4 *__restrict__ w, const uint4 *__restrict__ q, const void *__restrict__ scales,
+                  uint64_t units, uint32_t block, int scale_f16) {
+    const uint64_t stride = (uint64_t)gridDim.x * blockDim.x;
+    for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < units; i += stride) {
+        const uint64_t b = i * 16u / block;
+        const float s = scale_f16 ? __half2float(reinterpret_cast<const __half *>(scales)[b])
+                                  : reinterpret_cast<const float *>(scales)[b];
+        const uint4 v = q[i];
+        const uint32_t in[4] = {v.x, v.y, v.z, v.w};
+        uint32_t o[8];
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+#pragma unroll
+            for (int p = 0; p < 2; p++) {
+                const float lo = __fmul_rn((float)(int8_t)(in[j] >> (16 * p)), s);
+                const float hi = __fmul_rn((float)(int8_t)(in[j] >> (16 * p + 8)), s);
+                o[2 * j + p] = pack_bf16x2(lo, hi);
+            }
+        }
+        w[2 * i] = make_uint4(o[0], o[1], o[2], o[3]);
+        w[2 * i + 1] = make_uint4(o[4], o[5], o[6], o[7]);
+    }
+}
+
 bool tc_shape_ok(uint32_t k, uint32_t rows) {
     return k % 512u == 0 && k >= 512u && rows >= 1u;
 }
@@ -619,6 +646,53 @@ bool k3_grouped_q8_bf16(void *out, const void *q, const void *scales, const void
         return launch_tc<kAQ8, kEBf16>(q, q, a, x, (cudaStream_t)stream);
     }
     return k3_moe_q8_gemm_bf16(out, q, scales, x, tokens, rows, cols, block, scale_type, stream);
+}
+
+size_t k3_grouped_shared_workspace_bytes(const k3_moe_layer_desc *d, uint32_t tokens) {
+    if (d->shared_hidden == 0 || tokens < 32u || !tc_shape_ok(d->hidden, tokens) ||
+        !tc_shape_ok(d->shared_hidden, tokens) || d->q8_block % 16u != 0 || !encode_fn()) {
+        return 0;
+    }
+    return (size_t)3u * d->shared_hidden * d->hidden * 2u + 256u;
+}
+
+// Shared expert for many tokens: the three Q8 tables are converted to bf16 once
+// per call (tens of microseconds at memory speed) and the products run as plain
+// bf16 tensor-core GEMMs with the activation fused into the gate/up epilogue.
+bool k3_grouped_shared_expert(const k3_moe_layer_desc *d, void *out, void *act, const void *x,
+                              uint32_t tokens, void *workspace, cudaStream_t stream) {
+    const uint32_t S = d->shared_hidden, H = d->hidden;
+    const uint64_t units = (uint64_t)S * H / 16u;
+    uint16_t *wg = (uint16_t *)(((uintptr_t)workspace + 255u) & ~(uintptr_t)255u);
+    uint16_t *wu = wg + (size_t)S * H, *wd = wu + (size_t)S * H;
+    const void *q[3] = {d->shared_gate_q, d->shared_up_q, d->shared_down_q};
+    const void *sc[3] = {d->shared_gate_s, d->shared_up_s, d->shared_down_s};
+    uint16_t *dst[3] = {wg, wu, wd};
+    const uint32_t blocks = (uint32_t)std::min<uint64_t>((units + 255u) / 256u, (uint64_t)sm_count() * 16u);
+    for (int t = 0; t < 3; t++) {
+        if ((((uintptr_t)q[t]) & 15u) != 0) return false;
+        q8_to_bf16_kernel<<<blocks, 256, 0, stream>>>((uint4 *)dst[t], (const uint4 *)q[t], sc[t], units,
+                                                      d->q8_block, d->q8_scale_type);
+    }
+    if (!launch_ok()) return false;
+    TcArgs a{};
+    a.groups = 1;
+    a.rows = tokens;
+    a.activation = d->activation;
+    a.beta = d->beta;
+    a.linear_beta = d->linear_beta;
+    a.out = act;
+    a.w_rows = S;
+    a.k = H;
+    a.out_width = S;
+    a.m_items = (S + BM - 1u) / BM;
+    if (!launch_tc<kABf16, kEAct>(wg, wu, a, x, stream)) return false;
+    a.out = out;
+    a.w_rows = H;
+    a.k = S;
+    a.out_width = H;
+    a.m_items = (H + 2u * BM - 1u) / (2u * BM);
+    return launch_tc<kABf16, kEBf16>(wd, wd, a, act, stream);
 }
 
 bool k3_grouped_tc_supported(const k3_moe_layer_desc *d, uint32_t rows) {

@@ -168,8 +168,8 @@ struct Workspace {
     uint32_t *offsets, *sorted_route, *sorted_token, *inv_perm;
     void *dispatch_ws;
     size_t dispatch_bytes;
-    void *mx_ws;
-    size_t mx_bytes;
+    void *mx_ws, *sh_ws;
+    size_t mx_bytes, sh_bytes;
     uint16_t *rows_in, *act, *rows_out, *sh_gate, *sh_up, *sh_act, *sh_out;
     size_t total;
 };
@@ -199,6 +199,8 @@ Workspace carve(const k3_moe_layer_desc *d, uint32_t tokens, void *base) {
     w.mx_bytes = k3_grouped_mx_supported(d, (uint32_t)routes)
                      ? k3_grouped_mx_workspace_bytes(d, (uint32_t)routes, tokens) : 0;
     w.mx_ws = take(w.mx_bytes);
+    w.sh_bytes = k3_grouped_shared_workspace_bytes(d, tokens);
+    w.sh_ws = take(w.sh_bytes);
     if (d->shared_hidden) {
         w.sh_gate = (uint16_t *)take((size_t)tokens * d->shared_hidden * 2u);
         w.sh_up = (uint16_t *)take((size_t)tokens * d->shared_hidden * 2u);
@@ -425,7 +427,9 @@ bool layer_forward_impl(const k3_moe_layer_desc *d, void *out, const void *x, ui
         if (!k3_moe_route(d, w.ids, w.weights, w.logits, x, tokens, stream)) return false;
         if (!mark(events, 1, stream)) return false;
         if (d->shared_hidden &&
-            !k3_moe_shared_expert(d, w.sh_out, w.sh_gate, w.sh_up, w.sh_act, x, tokens, stream)) {
+            !(w.sh_bytes != 0
+                  ? k3_grouped_shared_expert(d, w.sh_out, w.sh_act, x, tokens, w.sh_ws, stream)
+                  : k3_moe_shared_expert(d, w.sh_out, w.sh_gate, w.sh_up, w.sh_act, x, tokens, stream))) {
             return false;
         }
         if (!mark(events, 2, stream)) return false;
