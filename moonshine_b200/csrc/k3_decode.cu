@@ -1,11 +1,12 @@
-// One-token (decode) routed-MoE layer: five launches, no host round trip.
+// One-token (decode) routed-MoE layer: four launches, no host round trip.
 //
-//   front    router logits (896 BF16 rows) + shared-expert gate/up rows (Q8),
-//            one warp per weight row, reference reduction order
-//   route    sigmoid + bias top-k (8-warp tournament), routing weights, shared
-//            activation
+//   front    router logits (896 BF16 rows), shared-expert gate/up rows (Q8), one
+//            warp per weight row in the reference reduction order, and the
+//            token's two-term E4M3 form; the last block to finish routes the
+//            token (sigmoid + bias top-k) and applies the shared activation
 //   gate/up  the top_k selected experts' gate and up rows + activation
-//   down     the selected experts' down rows + the shared expert's down rows
+//            (+ the shared expert's down rows on spare warps)
+//   down     the selected experts' down rows
 //   combine  weighted sum in rank order + shared output
 //
 // It replaces the per-token sequence of the reference's decode_routed_layer
@@ -26,6 +27,9 @@
 #include "k3_moe_ops.h"
 
 #include <algorithm>
+#include <atomic>
+
+#include <cuda_fp8.h>
 
 using namespace k3;
 
@@ -44,117 +48,148 @@ struct DecodeArgs {
     uint16_t *sh_gate, *sh_up, *sh_act, *sh_out;   // shared expert buffers
     uint16_t *act;            // [top_k, I]
     uint16_t *rows_out;       // [top_k, hidden]
-    uint32_t shared_only;     // down kernel: only the shared expert's rows
-    uint32_t skip_shared;     // front/route: the shared expert is computed elsewhere
+    uint32_t skip_shared;     // down kernel: the shared expert's rows are computed elsewhere
+    uint8_t *x_hl, *x_sf;     // front: two-term E4M3 form of x ([2, hidden], [hidden/32]) or null
+    unsigned int *ticket;     // front: completion counter of this call
 };
 
 // ------------------------------------------------------------------- front
+// Tickets of the "last block finishes the job" step of the front kernel.  A call
+// takes the next slot round-robin, the last block of the grid resets it, so calls
+// running at once on different streams do not share a counter unless more than
+// kTicketSlots of them are in flight.
+constexpr uint32_t kTicketSlots = 64;
+__device__ unsigned int g_front_tickets[kTicketSlots];
+
+// float -> unsigned key with the same order (-0 is folded into +0 first)
+K3_DEVINL uint32_t order_key(float f) {
+    const uint32_t b = __float_as_uint(f + 0.0f);
+    return b ^ ((b >> 31) ? 0xffffffffu : 0x80000000u);
+}
+
+// Block of 32 values (one per lane) -> two E4M3 terms and the E8M0 block scale:
+// value = 2^(scale - 127) * (hi + lo).
+K3_DEVINL void split_block(float val, uint8_t &hi, uint8_t &lo, uint8_t &scale_byte) {
+    const float mx = warp_max(fabsf(val));
+    int e = 0;
+    if (mx > 0.f && mx < 3.0e38f) e = (int)((__float_as_uint(mx) >> 23) & 0xffu) - 127 - 7;
+    e = max(-127, min(127, e));
+    const float scaled = val * __uint_as_float((uint32_t)(127 - e) << 23);      // |scaled| < 256
+    hi = __nv_cvt_float_to_fp8(scaled, __NV_SATFINITE, __NV_E4M3);
+    const float hi_f = __half2float(__half(__nv_cvt_fp8_to_halfraw(hi, __NV_E4M3)));
+    lo = __nv_cvt_float_to_fp8(scaled - hi_f, __NV_SATFINITE, __NV_E4M3);
+    scale_byte = (uint8_t)(e + 127);
+}
+
+// One warp per task: router rows, shared-expert gate and up rows (reference
+// reduction order), and the 32-column blocks of the token's two-term E4M3 form.
+// The last block to finish then routes the token (sigmoid + bias top-k in the
+// reference's order: larger choice first, lower expert id on ties) and applies the
+// shared expert's activation.
 __global__ void __launch_bounds__(256)
 decode_front_kernel(DecodeArgs a) {
-    const uint32_t lane = threadIdx.x % kWarp;
+    __shared__ float choice_s[1024], score_s[1024];
+    __shared__ float top_score[32];
+    __shared__ uint32_t top_id[32];
+    __shared__ uint32_t is_last;
+    const uint32_t warp = threadIdx.x / kWarp, lane = threadIdx.x % kWarp;
     const uint32_t warps = (gridDim.x * blockDim.x) / kWarp;
-    const uint32_t E = a.d.expert_count, S = a.d.shared_hidden, H = a.d.hidden;
-    const uint32_t tasks = E + (a.skip_shared ? 0u : 2u * S);
-    const uint32_t blocks_per_row = H / a.d.q8_block;
+    const uint32_t E = a.d.expert_count, S = a.d.shared_hidden, H = a.d.hidden, k = a.d.top_k;
+    const uint32_t split_tasks = a.x_hl ? H / 32u : 0u;
+    const uint32_t tasks = E + 2u * S + split_tasks;
+    const uint32_t blocks_per_row = S ? H / a.d.q8_block : 0u;
     for (uint32_t task = (blockIdx.x * blockDim.x + threadIdx.x) / kWarp; task < tasks; task += warps) {
         if (task < E) {
             const float v = bf16_row_dot_exact((const uint16_t *)a.d.router_weight + (uint64_t)task * H,
                                                a.x, H, lane);
             if (lane == 0) a.logits[task] = v;
-        } else {
+        } else if (task < E + 2u * S) {
             const uint32_t r = task - E;
             const bool up = r >= S;
             const uint32_t row = up ? r - S : r;
             const int8_t *q = (const int8_t *)(up ? a.d.shared_up_q : a.d.shared_gate_q);
-            const void *s = up ? a.d.shared_up_s : a.d.shared_gate_s;
-            const float v = q8_row_dot_exact(q + (uint64_t)row * H, s, (uint64_t)row * blocks_per_row,
+            const void *sc = up ? a.d.shared_up_s : a.d.shared_gate_s;
+            const float v = q8_row_dot_exact(q + (uint64_t)row * H, sc, (uint64_t)row * blocks_per_row,
                                              a.x, H, a.d.q8_block, a.d.q8_scale_type, lane);
             if (lane == 0) (up ? a.sh_up : a.sh_gate)[row] = float_to_bf16_bits(v);
-        }
-    }
-}
-
-// ------------------------------------------------------------------- route
-// 8 warps: each finds the top_k of its 1/8 of the experts, warp 0 merges.
-K3_DEVINL bool better(float c, uint32_t id, float oc, uint32_t oid) {
-    return id != 0xffffffffu && (oid == 0xffffffffu || c > oc || (c == oc && id < oid));
-}
-
-template <int kPer>
-K3_DEVINL void warp_topk(float (&choice)[kPer], float (&score)[kPer], uint32_t (&ids)[kPer],
-                         uint32_t top_k, uint32_t lane, float *out_choice, float *out_score,
-                         uint32_t *out_id) {
-    uint32_t taken = 0u;
-    for (uint32_t rank = 0; rank < top_k; rank++) {
-        float best = 0.f, best_s = 0.f;
-        uint32_t best_id = 0xffffffffu;
-        int best_i = -1;
-#pragma unroll
-        for (int i = 0; i < kPer; i++) {
-            if (((taken >> i) & 1u) == 0u && better(choice[i], ids[i], best, best_id)) {
-                best = choice[i]; best_s = score[i]; best_id = ids[i]; best_i = i;
-            }
-        }
-        float win = best, win_s = best_s;
-        uint32_t win_id = best_id;
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) {
-            const float oc = __shfl_xor_sync(0xffffffffu, win, o);
-            const float os = __shfl_xor_sync(0xffffffffu, win_s, o);
-            const uint32_t oid = __shfl_xor_sync(0xffffffffu, win_id, o);
-            if (better(oc, oid, win, win_id)) { win = oc; win_s = os; win_id = oid; }
-        }
-        if (best_i >= 0 && win_id == best_id) taken |= 1u << best_i;
-        if (lane == 0) { out_choice[rank] = win; out_score[rank] = win_s; out_id[rank] = win_id; }
-    }
-}
-
-__global__ void __launch_bounds__(256)
-decode_route_kernel(DecodeArgs a) {
-    __shared__ float c_s[8 * 32], s_s[8 * 32];
-    __shared__ uint32_t i_s[8 * 32];
-    const uint32_t warp = threadIdx.x / kWarp, lane = threadIdx.x % kWarp;
-    const uint32_t E = a.d.expert_count, k = a.d.top_k;
-    // shared-expert activation
-    for (uint32_t i = threadIdx.x; i < (a.skip_shared ? 0u : a.d.shared_hidden); i += blockDim.x) {
-        a.sh_act[i] = float_to_bf16_bits(activation(bf16_bits_to_float(a.sh_gate[i]),
-                                                    bf16_bits_to_float(a.sh_up[i]), a.d.activation,
-                                                    a.d.beta, a.d.linear_beta));
-    }
-    // local candidates: warp w owns experts e with (e / 32) % 8 == w
-    float choice[4], score[4];
-    uint32_t ids[4];
-#pragma unroll
-    for (int i = 0; i < 4; i++) {
-        const uint32_t e = (warp + 8u * i) * 32u + lane;
-        if (e < E) {
-            const float s = sigmoid_exact(a.logits[e]);
-            score[i] = s;
-            choice[i] = s + ((const float *)a.d.router_bias)[e];
-            ids[i] = e;
         } else {
-            score[i] = 0.f; choice[i] = 0.f; ids[i] = 0xffffffffu;
+            const uint32_t blk = task - E - 2u * S;
+            uint8_t hi, lo, sb;
+            split_block(bf16_bits_to_float(a.x[blk * 32u + lane]), hi, lo, sb);
+            a.x_hl[blk * 32u + lane] = hi;
+            a.x_hl[H + blk * 32u + lane] = lo;
+            if (lane == 0) a.x_sf[blk] = sb;
         }
     }
-    warp_topk<4>(choice, score, ids, k, lane, c_s + warp * 32, s_s + warp * 32, i_s + warp * 32);
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const unsigned int ticket = atomicAdd(a.ticket, 1u);
+        is_last = ticket == gridDim.x - 1u ? 1u : 0u;
+    }
+    __syncthreads();
+    if (is_last == 0u) return;
+    __threadfence();
+    if (threadIdx.x == 0) *a.ticket = 0u;
+    // ---- routing and shared activation: results of the other blocks come from L2
+    for (uint32_t e = threadIdx.x; e < 1024u; e += blockDim.x) {
+        float sc = 0.f, ch = 0.f;
+        if (e < E) {
+            sc = sigmoid_exact(__ldcg(a.logits + e));
+            ch = sc + ((const float *)a.d.router_bias)[e];
+        }
+        score_s[e] = sc;
+        choice_s[e] = ch;
+    }
     __syncthreads();
     if (warp == 0) {
-        float mc[8], ms[8];
-        uint32_t mi[8];
-#pragma unroll
-        for (int i = 0; i < 8; i++) {
-            const bool ok = lane < k;
-            mc[i] = ok ? c_s[i * 32 + lane] : 0.f;
-            ms[i] = ok ? s_s[i * 32 + lane] : 0.f;
-            mi[i] = ok ? i_s[i * 32 + lane] : 0xffffffffu;
+        // lane owns experts lane, lane + 32, ...; its best candidate is cached
+        const uint32_t slots = (E + 31u) / 32u;
+        uint32_t best_key = 0u, best_id = 0xffffffffu;
+        for (uint32_t i = 0; i < slots; i++) {
+            const uint32_t e = i * 32u + lane;
+            if (e < E) {
+                const uint32_t key = order_key(choice_s[e]);
+                if (best_id == 0xffffffffu || key > best_key) { best_key = key; best_id = e; }
+            }
         }
-        warp_topk<8>(mc, ms, mi, k, lane, c_s, s_s, i_s);
+        for (uint32_t rank = 0; rank < k; rank++) {
+            const uint32_t has = best_id != 0xffffffffu ? 1u : 0u;
+            const uint32_t top = __reduce_max_sync(0xffffffffu, has ? best_key : 0u);
+            const uint32_t any = __reduce_max_sync(0xffffffffu, has);
+            const uint32_t cand = (has && best_key == top) ? best_id : 0xffffffffu;
+            const uint32_t win = any ? __reduce_min_sync(0xffffffffu, cand) : 0xffffffffu;
+            if (lane == 0) {
+                top_id[rank] = win;
+                top_score[rank] = win != 0xffffffffu ? score_s[win] : 0.f;
+            }
+            if (win != 0xffffffffu && (win & 31u) == lane) {
+                // winner leaves the pool; rescan this lane's candidates
+                choice_s[win] = __uint_as_float(0x7fc00000u);       // marks "taken"
+                best_key = 0u;
+                best_id = 0xffffffffu;
+                for (uint32_t i = 0; i < slots; i++) {
+                    const uint32_t e = i * 32u + lane;
+                    if (e >= E) continue;
+                    const float c = choice_s[e];
+                    if (__float_as_uint(c) == 0x7fc00000u) continue;
+                    const uint32_t key = order_key(c);
+                    if (best_id == 0xffffffffu || key > best_key) { best_key = key; best_id = e; }
+                }
+            }
+        }
         __syncwarp();
         float denominator = 1e-20f;
-        for (uint32_t r = 0; r < k; r++) denominator += s_s[r];
+        for (uint32_t r = 0; r < k; r++) denominator += top_score[r];
         if (lane < k) {
-            a.ids[lane] = i_s[lane];
-            a.weights[lane] = __fmul_rn(__fdiv_rn(s_s[lane], denominator), a.d.route_scale);
+            a.ids[lane] = top_id[lane];
+            a.weights[lane] = __fmul_rn(__fdiv_rn(top_score[lane], denominator), a.d.route_scale);
+        }
+    } else {
+        for (uint32_t i = threadIdx.x - kWarp; i < S; i += blockDim.x - kWarp) {
+            a.sh_act[i] = float_to_bf16_bits(activation(bf16_bits_to_float(__ldcg(a.sh_gate + i)),
+                                                        bf16_bits_to_float(__ldcg(a.sh_up + i)),
+                                                        a.d.activation, a.d.beta, a.d.linear_beta));
         }
     }
 }
@@ -287,7 +322,7 @@ decode_down_kernel(DecodeArgs a) {
     __half *xs = reinterpret_cast<__half *>(smem_raw);                       // [k][I]
     float *inv_scale = reinterpret_cast<float *>(smem_raw + (size_t)(k + 1u) * I * sizeof(__half));  // [k+1]
     float *scratch = inv_scale + 34;
-    for (uint32_t r = 0; r < (a.shared_only ? 0u : k); r += 2u) {
+    for (uint32_t r = 0; r < k; r += 2u) {
         __syncthreads();
         stage_vectors_f16(xs + (size_t)r * I, inv_scale + r, a.act + (uint64_t)r * I,
                           r + 1u < k ? a.act + (uint64_t)(r + 1u) * I : nullptr, I, I, scratch);
@@ -297,8 +332,8 @@ decode_down_kernel(DecodeArgs a) {
     const uint32_t lane = threadIdx.x % kWarp;
     const uint32_t blocks = H / 16u;
     const uint64_t pstride = (uint64_t)H * (I / 2u), sstride = (uint64_t)H * (I / 32u);
-    const uint32_t expert_tasks = a.shared_only ? 0u : k * blocks;
-    const uint32_t shared_tasks = S ? H : 0u;            // one warp per shared down row
+    const uint32_t expert_tasks = k * blocks;
+    const uint32_t shared_tasks = (S && !a.skip_shared) ? H : 0u;            // one warp per shared down row
     for (uint32_t task = warp_global; task < expert_tasks + shared_tasks; task += warps) {
         if (task < expert_tasks) {
             const uint32_t rank = task % k, rb = task / k;
@@ -366,14 +401,19 @@ bool k3_decode_layer(const k3_moe_layer_desc *d, const void *x, void *logits, vo
     const int sms = sm_count();
     const bool mx = scratch != nullptr && k3_decode_mx_supported(d) &&
                     scratch_bytes >= k3_decode_mx_scratch_bytes(d);
-    a.skip_shared = mx ? 1u : 0u;
-    const uint32_t front_tasks = d->expert_count + (mx ? 0u : 2u * d->shared_hidden);
+    if (mx) k3_decode_mx_vector_scratch(d, scratch, (void **)&a.x_hl, (void **)&a.x_sf);
+    static std::atomic<uint32_t> next_ticket{0};
+    unsigned int *tickets = nullptr;
+    if (cudaGetSymbolAddress((void **)&tickets, g_front_tickets) != cudaSuccess) {
+        (void)cudaGetLastError();
+        return false;
+    }
+    a.ticket = tickets + next_ticket.fetch_add(1u) % kTicketSlots;
+    const uint32_t front_tasks = d->expert_count + 2u * d->shared_hidden + (mx ? d->hidden / 32u : 0u);
     decode_front_kernel<<<std::min<uint32_t>((front_tasks + 7u) / 8u, (uint32_t)sms * 8u), 256, 0, stream>>>(a);
     if (!launch_ok()) return false;
-    decode_route_kernel<<<1, 256, 0, stream>>>(a);
-    if (!launch_ok()) return false;
     if (mx) {
-        return k3_decode_mx_experts(d, x, ids, act, rows_out, sh_gate, sh_up, sh_out, scratch, stream);
+        return k3_decode_mx_experts(d, ids, act, rows_out, sh_act, sh_out, scratch, stream);
     }
     size_t smem = (size_t)2 * d->hidden * sizeof(__half) + (2 + 2 * kDecodeWarps) * sizeof(float);
     if (!set_smem((const void *)decode_gateup_kernel, smem)) return false;

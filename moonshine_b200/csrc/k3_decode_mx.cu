@@ -40,21 +40,25 @@ using namespace k3::tc;
 
 namespace {
 
-constexpr uint32_t kStages = 12;            // TMA ring (multiple of 4)
-constexpr uint32_t kSfBatches = 6;          // scale ring: batches of 4 steps
+constexpr uint32_t kStages = 10;            // TMA ring of weight / vector tiles
+constexpr uint32_t kSfBatches = 6;          // scale ring in tensor memory: batches of 4 steps
+constexpr uint32_t kSfSlots = 8;            // scale ring in shared memory (one batch per slot)
+constexpr uint32_t kSfaBytes = 128 * 16;    // 128 rows x 16 scale bytes (4 steps)
+constexpr uint32_t kSfSlotBytes = kSfaBytes + 128;   // + the vector's 16 scale bytes
 constexpr uint32_t kSfStages = 4 * kSfBatches;
 constexpr uint32_t kATile = 128 * 128;     // bytes in shared memory (8-bit containers)
 constexpr uint32_t kATx = 128 * 64;        // bytes the TMA transaction counts (packed)
 constexpr uint32_t kBTile = 16 * 128;
 constexpr uint32_t kStageBytes = kATile + kBTile;
 constexpr uint32_t kThreads = 512;
-constexpr uint32_t kSideWarps = 5;          // warps 11..15 (warp 10 is the second TMA producer)
-constexpr uint32_t kTmemCols = 256;
-constexpr uint32_t kAccCol = 0;            // 2 buffers x 32 columns
-constexpr uint32_t kSfaCol = 64;           // kSfStages x 4 columns
-constexpr uint32_t kSfbCol = 64 + 4 * kSfStages;   // kSfStages x 4 columns
+constexpr uint32_t kSideWarps = 4;          // warps 12..15 (10: scale producer, 11: second MMA issuer)
+constexpr uint32_t kTmemCols = 512;
+constexpr uint32_t kAccCol = 0;            // 2 buffers x 2 issuers x 2 phases x 16 columns
+constexpr uint32_t kSfaCol = 128;          // kSfStages x 4 columns
+constexpr uint32_t kSfbCol = 128 + 4 * kSfStages;  // kSfStages x 4 columns
 constexpr uint32_t kBarrierBytes = 512;
-constexpr uint32_t kSmemBytes = kStages * kStageBytes + 1024 + kBarrierBytes;   // + shared activation vector
+constexpr uint32_t kSmemBytes =
+    kStages * kStageBytes + kSfSlots * kSfSlotBytes + 1024 + kBarrierBytes;   // + shared activation vector
 
 __device__ uint32_t g_mx_status = 0;
 
@@ -93,9 +97,6 @@ K3_DEVINL uint32_t make_idesc_mx(uint32_t sf) {
 }
 
 struct MxArgs {
-    const uint8_t *scales_a0;   // E8M0 table of phase 0 (gate / down)
-    const uint8_t *scales_a1;   // E8M0 table of phase 1 (up), gate/up mode only
-    const uint8_t *sfb;         // activation block scales [vectors, K/32]
     const uint32_t *ids;        // expert id per rank
     uint16_t *out;              // [ranks, out_width] bf16
     uint32_t ranks, first_local, local_count;
@@ -107,11 +108,10 @@ struct MxArgs {
     uint8_t *act_hl;            // gate/up: E4M3 split of the produced activation [2*ranks, w_rows]
     uint8_t *act_sf;            //          and its block scales [ranks, w_rows/32]
     // shared-expert side work (Q8 rows, one warp per row)
-    const int8_t *q8_q0, *q8_q1;
-    const void *q8_s0, *q8_s1;
-    uint16_t *q8_out0, *q8_out1;
-    const uint16_t *q8_x;       // input vector in global memory, or nullptr: act(q8_gate, q8_up)
-    const uint16_t *q8_gate, *q8_up;
+    const int8_t *q8_q;
+    const void *q8_s;
+    uint16_t *q8_out;
+    const uint16_t *q8_x;       // input vector [q8_cols] bf16
     uint32_t q8_rows, q8_cols, q8_block;
     int q8_scale_f16;
 };
@@ -130,22 +130,31 @@ K3_DEVINL void split_block_e4m3(float val, uint8_t &hi, uint8_t &lo, uint8_t &sc
     scale_byte = (uint8_t)(e + 127);
 }
 
+struct MxMaps {
+    CUtensorMap a0, a1;        // packed E2M1 weights of phase 0 / phase 1
+    CUtensorMap b;             // vector terms (E4M3), rows 2v = hi, 2v+1 = lo
+    CUtensorMap sfa0, sfa1;    // weight block scales [rows, K/32]
+    CUtensorMap sfb;           // vector block scales [vectors, K/32]
+};
+
 // kGateUp: two phases (w1 then w3) into accumulator columns [0,16) and [16,32),
 // fused activation.  Otherwise one phase, plain bf16 output.
 template <bool kGateUp>
 __global__ void __launch_bounds__(kThreads, 1)
-decode_mx_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_constant__ CUtensorMap map_a1,
-                 const __grid_constant__ CUtensorMap map_b, MxArgs a) {
+decode_mx_kernel(const __grid_constant__ MxMaps maps, MxArgs a) {
     extern __shared__ unsigned char smem_raw[];
     unsigned char *base = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
-    uint64_t *bars = reinterpret_cast<uint64_t *>(base + kStages * kStageBytes);
+    unsigned char *sf_smem = base + kStages * kStageBytes;
+    uint64_t *bars = reinterpret_cast<uint64_t *>(sf_smem + kSfSlots * kSfSlotBytes);
     uint64_t *full = bars, *empty = bars + kStages;
     uint64_t *sf_full = bars + 2 * kStages;            // [kSfBatches]
     uint64_t *sf_empty = sf_full + kSfBatches;         // [kSfBatches]
-    uint64_t *acc_full = sf_empty + kSfBatches, *acc_empty = acc_full + 2;
+    uint64_t *sfs_full = sf_empty + kSfBatches;        // [kSfSlots]
+    uint64_t *sfs_empty = sfs_full + kSfSlots;         // [kSfSlots]
+    uint64_t *acc_full = sfs_empty + kSfSlots, *acc_empty = acc_full + 2;
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(acc_empty + 2);
     volatile uint32_t *abort_flag = tmem_slot + 1;
-    uint16_t *side_x = reinterpret_cast<uint16_t *>(base + kStages * kStageBytes + kBarrierBytes);
+    uint16_t *side_x = reinterpret_cast<uint16_t *>(reinterpret_cast<unsigned char *>(bars) + kBarrierBytes);
     const uint32_t warp = threadIdx.x / kWarp, lane = threadIdx.x % kWarp;
     const uint32_t steps = a.k / 128u;
     const uint32_t phases = kGateUp ? 2u : 1u;
@@ -160,10 +169,14 @@ decode_mx_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_consta
         }
         for (uint32_t b = 0; b < kSfBatches; b++) {
             mbar_init(&sf_full[b], 4);
-            mbar_init(&sf_empty[b], 1);
+            mbar_init(&sf_empty[b], 2);
+        }
+        for (uint32_t b = 0; b < kSfSlots; b++) {
+            mbar_init(&sfs_full[b], 1);
+            mbar_init(&sfs_empty[b], 4);
         }
         for (uint32_t b = 0; b < 2; b++) {
-            mbar_init(&acc_full[b], 1);
+            mbar_init(&acc_full[b], 2);
             mbar_init(&acc_empty[b], 4);
         }
         fence_barrier_init();
@@ -172,42 +185,35 @@ decode_mx_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_consta
         tmem_alloc(tmem_slot, kTmemCols);
         tmem_relinquish();
     }
-    if (a.q8_rows != 0u && a.q8_x == nullptr) {
-        for (uint32_t i = threadIdx.x; i < a.q8_cols; i += blockDim.x) {
-            side_x[i] = float_to_bf16_bits(activation(bf16_bits_to_float(a.q8_gate[i]),
-                                                      bf16_bits_to_float(a.q8_up[i]), a.activation,
-                                                      a.beta, a.linear_beta));
-        }
-    }
+    for (uint32_t i = threadIdx.x; i < (a.q8_rows != 0u ? a.q8_cols : 0u); i += blockDim.x) side_x[i] = a.q8_x[i];
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = *tmem_slot;
 
-    if (warp >= 11) {
+    if (warp >= 12) {
         // ---- shared-expert rows (SIMT), independent of the tensor pipeline
-        const uint16_t *xin = a.q8_x ? a.q8_x : side_x;
-        const uint32_t side = blockIdx.x * kSideWarps + (warp - 11u);
+        // two rows per pass so that twice the loads are in flight
+        const uint32_t side = blockIdx.x * kSideWarps + (warp - 12u);
         const uint32_t side_total = gridDim.x * kSideWarps;
-        const uint32_t mats = a.q8_q1 ? 2u : 1u;
         const uint32_t bpr = a.q8_cols / (a.q8_block ? a.q8_block : 1u);
-        for (uint32_t task = side; task < a.q8_rows * mats; task += side_total) {
-            const bool second = task >= a.q8_rows;
-            const uint32_t row = second ? task - a.q8_rows : task;
-            const float v = q8_row_dot_exact((second ? a.q8_q1 : a.q8_q0) + (uint64_t)row * a.q8_cols,
-                                             second ? a.q8_s1 : a.q8_s0, (uint64_t)row * bpr, xin,
-                                             a.q8_cols, a.q8_block, a.q8_scale_f16, lane);
-            if (lane == 0) (second ? a.q8_out1 : a.q8_out0)[row] = float_to_bf16_bits(v);
+        for (uint32_t row = 2u * side; row < a.q8_rows; row += 2u * side_total) {
+            const uint32_t row1 = min(row + 1u, a.q8_rows - 1u);
+            const float v0 = q8_row_dot_exact(a.q8_q + (uint64_t)row * a.q8_cols, a.q8_s, (uint64_t)row * bpr,
+                                              side_x, a.q8_cols, a.q8_block, a.q8_scale_f16, lane);
+            const float v1 = q8_row_dot_exact(a.q8_q + (uint64_t)row1 * a.q8_cols, a.q8_s, (uint64_t)row1 * bpr,
+                                              side_x, a.q8_cols, a.q8_block, a.q8_scale_f16, lane);
+            if (lane == 0) {
+                a.q8_out[row] = float_to_bf16_bits(v0);
+                a.q8_out[row1] = float_to_bf16_bits(v1);
+            }
         }
-    } else if (warp == 0 || warp == 10) {
-        // two producers issue alternate K steps (a TMA issue occupies its thread for
-        // a few hundred cycles)
+    } else if (warp == 0) {
+        // weight tile + vector tile of every K step
         if (lane == 0) {
-            const uint32_t mine = warp == 0 ? 0u : 1u;
-            uint32_t turn = 0u;
-            prefetch_tensormap(&map_a0);
-            prefetch_tensormap(&map_a1);
-            prefetch_tensormap(&map_b);
+            prefetch_tensormap(&maps.a0);
+            prefetch_tensormap(&maps.a1);
+            prefetch_tensormap(&maps.b);
             uint32_t s = 0, ph = 0;
             bool ok = true;
             for (uint32_t it = blockIdx.x; ok && it < items; it += gridDim.x) {
@@ -217,23 +223,53 @@ decode_mx_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_consta
                 const int32_t y = (int32_t)((id - a.first_local) * a.w_rows + tile * 128u);
                 const int32_t yb = a.shared_vector ? 0 : (int32_t)(2u * rank);
                 for (uint32_t p = 0; ok && p < phases; p++) {
-                    const void *map_a = p == 0 ? (const void *)&map_a0 : (const void *)&map_a1;
+                    const void *map_a = p == 0 ? (const void *)&maps.a0 : (const void *)&maps.a1;
                     for (uint32_t st = 0; st < steps; st++) {
-                        if ((turn++ & 1u) == mine) {
-                            if (!mbar_wait(&empty[s], ph ^ 1u, abort_flag)) { ok = false; break; }
-                            unsigned char *dst = base + s * kStageBytes;
-                            mbar_arrive_expect_tx(&full[s], kATx + kBTile);
-                            tma_load_2d(dst, map_a, &full[s], (int32_t)(st * 128u), y);
-                            tma_load_2d(dst + kATile, &map_b, &full[s], (int32_t)(st * 128u), yb);
-                        }
+                        if (!mbar_wait(&empty[s], ph ^ 1u, abort_flag)) { ok = false; break; }
+                        unsigned char *dst = base + s * kStageBytes;
+                        mbar_arrive_expect_tx(&full[s], kATx + kBTile);
+                        tma_load_2d(dst, map_a, &full[s], (int32_t)(st * 128u), y);
+                        tma_load_2d(dst + kATile, &maps.b, &full[s], (int32_t)(st * 128u), yb);
                         if (++s == kStages) { s = 0; ph ^= 1u; }
                     }
                 }
             }
         }
-    } else if (warp == 1) {
+    } else if (warp == 10) {
+        // block scales of four K steps at a time: 128 weight rows x 16 bytes and the
+        // vector's 16 bytes, into the shared-memory scale ring
         if (lane == 0) {
-            uint32_t s = 0, ph = 0, buf = 0, pacc = 0, sb = 0, sph = 0;
+            prefetch_tensormap(&maps.sfa0);
+            prefetch_tensormap(&maps.sfa1);
+            prefetch_tensormap(&maps.sfb);
+            uint32_t s = 0, ph = 0;
+            bool ok = true;
+            for (uint32_t it = blockIdx.x; ok && it < items; it += gridDim.x) {
+                const uint32_t rank = it / tiles, tile = it % tiles;
+                const uint32_t id = a.ids[rank];
+                if (id < a.first_local || id >= a.first_local + a.local_count) continue;
+                const int32_t y = (int32_t)((id - a.first_local) * a.w_rows + tile * 128u);
+                const int32_t yb = a.shared_vector ? 0 : (int32_t)rank;
+                for (uint32_t p = 0; ok && p < phases; p++) {
+                    const void *map_s = p == 0 ? (const void *)&maps.sfa0 : (const void *)&maps.sfa1;
+                    for (uint32_t st = 0; st < steps; st += 4u) {
+                        if (!mbar_wait(&sfs_empty[s], ph ^ 1u, abort_flag)) { ok = false; break; }
+                        unsigned char *dst = sf_smem + s * kSfSlotBytes;
+                        mbar_arrive_expect_tx(&sfs_full[s], kSfaBytes + 16u);
+                        tma_load_2d(dst, map_s, &sfs_full[s], (int32_t)(st * 4u), y);
+                        tma_load_2d(dst + kSfaBytes, &maps.sfb, &sfs_full[s], (int32_t)(st * 4u), yb);
+                        if (++s == kSfSlots) { s = 0; ph ^= 1u; }
+                    }
+                }
+            }
+        }
+    } else if (warp == 1 || warp == 11) {
+        // Two MMA issuers: the issue loop of one thread, not the tensor pipe, bounds
+        // the rate of these small MMAs, so warp 1 takes the even K steps and warp 11
+        // the odd ones, each into its own accumulator columns (summed in the epilogue).
+        if (lane == 0) {
+            const uint32_t q = warp == 1 ? 0u : 1u;
+            uint32_t s = q, ph = 0, buf = 0, pacc = 0, sb = 0, sph = 0;
             bool ok = true;
             for (uint32_t it = blockIdx.x; ok && it < items; it += gridDim.x) {
                 const uint32_t rank = it / tiles;
@@ -242,10 +278,10 @@ decode_mx_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_consta
                 if (!mbar_wait(&acc_empty[buf], pacc ^ 1u, abort_flag)) break;
                 tc_fence_after();
                 for (uint32_t p = 0; ok && p < phases; p++) {
-                    const uint32_t d = tmem + kAccCol + buf * 32u + p * 16u;
-                    for (uint32_t st = 0; st < steps; st++) {
+                    const uint32_t d = tmem + kAccCol + buf * 64u + q * 32u + p * 16u;
+                    for (uint32_t st = q; st < steps; st += 2u) {
                         if (!mbar_wait(&full[s], ph, abort_flag) ||
-                            ((st & 3u) == 0u && !mbar_wait(&sf_full[sb], sph, abort_flag))) {
+                            ((st & 3u) == q && !mbar_wait(&sf_full[sb], sph, abort_flag))) {
                             ok = false;
                             break;
                         }
@@ -253,15 +289,16 @@ decode_mx_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_consta
                         unsigned char *src = base + s * kStageBytes;
                         const uint64_t da = make_desc_sw128(smem_u32(src));
                         const uint64_t db = make_desc_sw128(smem_u32(src + kATile));
+                        const uint32_t sfs = (sb * 4u + (st & 3u)) * 4u;
 #pragma unroll
                         for (uint32_t j = 0; j < 4u; j++) {
-                            const uint32_t sfs = sb * 4u + (st & 3u);
-                            mma_mx(d, da + 2u * j, db + 2u * j, make_idesc_mx(j), tmem + kSfaCol + sfs * 4u,
-                                   tmem + kSfbCol + sfs * 4u, (st | j) != 0u ? 1u : 0u);
+                            mma_mx(d, da + 2u * j, db + 2u * j, make_idesc_mx(j), tmem + kSfaCol + sfs,
+                                   tmem + kSfbCol + sfs, (st != q || j != 0u) ? 1u : 0u);
                         }
                         mma_commit(&empty[s]);
-                        if (++s == kStages) { s = 0; ph ^= 1u; }
-                        if ((st & 3u) == 3u) {
+                        s += 2u;
+                        if (s >= kStages) { s -= kStages; ph ^= 1u; }
+                        if ((st & 3u) == q + 2u) {
                             mma_commit(&sf_empty[sb]);
                             if (++sb == kSfBatches) { sb = 0; sph ^= 1u; }
                         }
@@ -273,54 +310,40 @@ decode_mx_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_consta
             }
         }
     } else if (warp < 6) {
-        // scale writers: warp w fills lane quadrant w % 4
+        // scale writers: shared memory -> tensor memory, warp w fills lane quadrant w % 4
         const uint32_t quad = warp & 3u;
         const uint32_t lane_base = (32u * quad) << 16;
-        const uint32_t pitch = a.k / 32u;
-        uint32_t sb = 0, sph = 0;
+        uint32_t sb = 0, sph = 0, ss = 0, ssph = 0;
         bool ok = true;
         for (uint32_t it = blockIdx.x; ok && it < items; it += gridDim.x) {
-            const uint32_t rank = it / tiles, tile = it % tiles;
-            const uint32_t id = a.ids[rank];
+            const uint32_t id = a.ids[it / tiles];
             if (id < a.first_local || id >= a.first_local + a.local_count) continue;
-            const uint64_t row0 = (uint64_t)(id - a.first_local) * a.w_rows + tile * 128u;
-            const uint8_t *sfb_row = a.sfb + (uint64_t)(a.shared_vector ? 0u : rank) * pitch;
-            for (uint32_t p = 0; ok && p < phases; p++) {
-                const uint8_t *table = p == 0 ? a.scales_a0 : a.scales_a1;
-                const uint8_t *r0 = table + (row0 + lane) * pitch;
-                // 16 bytes per row = the scales of 4 steps; rows lane, lane+32, lane+64, lane+96
-                uint4 v[4], vb;
+            for (uint32_t st = 0; st < phases * steps; st += 4u) {
+                if (!mbar_wait(&sfs_full[ss], ssph, abort_flag)) { ok = false; break; }
+                const unsigned char *src = sf_smem + ss * kSfSlotBytes;
+                uint4 cur[4];
 #pragma unroll
-                for (uint32_t c = 0; c < 4u; c++) v[c] = *reinterpret_cast<const uint4 *>(r0 + (uint64_t)(32u * c) * pitch);
-                vb = *reinterpret_cast<const uint4 *>(sfb_row);
-                for (uint32_t st = 0; st < steps; st += 4u) {
-                    uint4 cur[4];
-#pragma unroll
-                    for (uint32_t c = 0; c < 4u; c++) cur[c] = v[c];
-                    const uint4 curb = vb;
-                    if (st + 4u < steps) {          // prefetch the next four steps
-#pragma unroll
-                        for (uint32_t c = 0; c < 4u; c++) {
-                            v[c] = *reinterpret_cast<const uint4 *>(r0 + (uint64_t)(32u * c) * pitch + (st + 4u) * 4u);
-                        }
-                        vb = *reinterpret_cast<const uint4 *>(sfb_row + (st + 4u) * 4u);
-                    }
-                    if (!mbar_wait(&sf_empty[sb], sph ^ 1u, abort_flag)) { ok = false; break; }
-                    tc_fence_after();
-                    // column (step q, row group c) = q * 4 + c of the batch's 16 columns
-                    const uint32_t va[16] = {cur[0].x, cur[1].x, cur[2].x, cur[3].x, cur[0].y, cur[1].y,
-                                             cur[2].y, cur[3].y, cur[0].z, cur[1].z, cur[2].z, cur[3].z,
-                                             cur[0].w, cur[1].w, cur[2].w, cur[3].w};
-                    const uint32_t vbb[16] = {curb.x, curb.x, curb.x, curb.x, curb.y, curb.y, curb.y, curb.y,
-                                              curb.z, curb.z, curb.z, curb.z, curb.w, curb.w, curb.w, curb.w};
-                    tmem_st_32x16(tmem + lane_base + kSfaCol + sb * 16u, va);
-                    tmem_st_32x16(tmem + lane_base + kSfbCol + sb * 16u, vbb);
-                    tmem_st_wait();
-                    tc_fence_before();
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(&sf_full[sb]);
-                    if (++sb == kSfBatches) { sb = 0; sph ^= 1u; }
-                }
+                for (uint32_t c = 0; c < 4u; c++)
+                    cur[c] = *reinterpret_cast<const uint4 *>(src + (32u * c + lane) * 16u);
+                const uint4 curb = *reinterpret_cast<const uint4 *>(src + kSfaBytes);
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&sfs_empty[ss]);
+                if (++ss == kSfSlots) { ss = 0; ssph ^= 1u; }
+                if (!mbar_wait(&sf_empty[sb], sph ^ 1u, abort_flag)) { ok = false; break; }
+                tc_fence_after();
+                // column (step q, row group c) = q * 4 + c of the batch's 16 columns
+                const uint32_t va[16] = {cur[0].x, cur[1].x, cur[2].x, cur[3].x, cur[0].y, cur[1].y,
+                                         cur[2].y, cur[3].y, cur[0].z, cur[1].z, cur[2].z, cur[3].z,
+                                         cur[0].w, cur[1].w, cur[2].w, cur[3].w};
+                const uint32_t vbb[16] = {curb.x, curb.x, curb.x, curb.x, curb.y, curb.y, curb.y, curb.y,
+                                          curb.z, curb.z, curb.z, curb.z, curb.w, curb.w, curb.w, curb.w};
+                tmem_st_32x16(tmem + lane_base + kSfaCol + sb * 16u, va);
+                tmem_st_32x16(tmem + lane_base + kSfbCol + sb * 16u, vbb);
+                tmem_st_wait();
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&sf_full[sb]);
+                if (++sb == kSfBatches) { sb = 0; sph ^= 1u; }
             }
         }
     } else if (warp < 10) {
@@ -334,19 +357,23 @@ decode_mx_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_consta
             if (id < a.first_local || id >= a.first_local + a.local_count) continue;
             if (!mbar_wait(&acc_full[buf], pacc, abort_flag)) break;
             tc_fence_after();
-            const uint32_t t0 = tmem + ((32u * quad) << 16) + kAccCol + buf * 32u;
-            uint32_t h0, l0, h1 = 0, l1 = 0;
-            tmem_ld_32x2(t0, h0, l0);
-            if (kGateUp) tmem_ld_32x2(t0 + 16u, h1, l1);
+            const uint32_t t0 = tmem + ((32u * quad) << 16) + kAccCol + buf * 64u;
+            uint32_t h0, l0, h1 = 0, l1 = 0, h2, l2, h3 = 0, l3 = 0;
+            tmem_ld_32x2(t0, h0, l0);                       // even K steps
+            tmem_ld_32x2(t0 + 32u, h2, l2);                 // odd K steps
+            if (kGateUp) {
+                tmem_ld_32x2(t0 + 16u, h1, l1);
+                tmem_ld_32x2(t0 + 48u, h3, l3);
+            }
             tmem_ld_wait();
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(&acc_empty[buf]);
             if (++buf == 2u) { buf = 0; pacc ^= 1u; }
-            const float v0 = __uint_as_float(h0) + __uint_as_float(l0);
+            const float v0 = (__uint_as_float(h0) + __uint_as_float(l0)) + (__uint_as_float(h2) + __uint_as_float(l2));
             uint16_t *dst = a.out + (uint64_t)rank * a.w_rows + tile * 128u + m;
             if (kGateUp) {
-                const float v1 = __uint_as_float(h1) + __uint_as_float(l1);
+                const float v1 = (__uint_as_float(h1) + __uint_as_float(l1)) + (__uint_as_float(h3) + __uint_as_float(l3));
                 const float g = bf16_bits_to_float(float_to_bf16_bits(v0));
                 const float u = bf16_bits_to_float(float_to_bf16_bits(v1));
                 const uint16_t act_bits = float_to_bf16_bits(activation(g, u, a.activation, a.beta, a.linear_beta));
@@ -371,32 +398,6 @@ decode_mx_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_consta
     if (warp == 1) {
         tc_fence_after();
         tmem_dealloc(tmem, kTmemCols);
-    }
-}
-
-// ---- activation split: bf16 rows -> interleaved E4M3 rows [2*vectors, K] (row 2v = hi,
-// 2v+1 = lo) and E8M0 block scales [vectors, K/32]; one warp per 32-element block.
-__global__ void __launch_bounds__(256)
-split_e4m3_kernel(uint8_t *__restrict__ hl, uint8_t *__restrict__ sf, const uint16_t *__restrict__ x,
-                  uint32_t vectors, uint32_t k) {
-    const uint32_t lane = threadIdx.x % kWarp;
-    const uint32_t blocks_per_row = k / 32u;
-    const uint32_t total = vectors * blocks_per_row;
-    const uint32_t warps = (gridDim.x * blockDim.x) / kWarp;
-    for (uint32_t b = (blockIdx.x * blockDim.x + threadIdx.x) / kWarp; b < total; b += warps) {
-        const uint32_t v = b / blocks_per_row, blk = b % blocks_per_row;
-        const float val = bf16_bits_to_float(x[(uint64_t)v * k + blk * 32u + lane]);
-        const float mx = warp_max(fabsf(val));
-        int e = 0;
-        if (mx > 0.f && mx < 3.0e38f) e = (int)((__float_as_uint(mx) >> 23) & 0xffu) - 127 - 7;
-        e = max(-127, min(127, e));
-        const float scaled = val * __uint_as_float((uint32_t)(127 - e) << 23);      // |scaled| < 256
-        const __nv_fp8_storage_t hi = __nv_cvt_float_to_fp8(scaled, __NV_SATFINITE, __NV_E4M3);
-        const float hi_f = __half2float(__half(__nv_cvt_fp8_to_halfraw(hi, __NV_E4M3)));
-        const __nv_fp8_storage_t lo = __nv_cvt_float_to_fp8(scaled - hi_f, __NV_SATFINITE, __NV_E4M3);
-        hl[(uint64_t)(2u * v) * k + blk * 32u + lane] = hi;
-        hl[(uint64_t)(2u * v + 1u) * k + blk * 32u + lane] = lo;
-        if (lane == 0) sf[(uint64_t)v * blocks_per_row + blk] = (uint8_t)(e + 127);
     }
 }
 
@@ -440,6 +441,19 @@ bool map_u8(CUtensorMap *map, const void *ptr, uint64_t rows, uint64_t k) {
               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+// block scales [rows, K/32] bytes, box = 16 bytes (four K steps) x box_rows rows
+bool map_sf(CUtensorMap *map, const void *ptr, uint64_t rows, uint64_t k, uint32_t box_rows) {
+    auto fn = encode_fn();
+    if (!fn || (((uintptr_t)ptr) & 15u) != 0) return false;
+    const cuuint64_t dims[2] = {k / 32u, rows};
+    const cuuint64_t strides[1] = {k / 32u};
+    const cuuint32_t box[2] = {16, box_rows};
+    const cuuint32_t es[2] = {1, 1};
+    return fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void *>(ptr), dims, strides, box, es,
+              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 }  // namespace
 
 uint32_t k3_decode_mx_status() {
@@ -460,17 +474,22 @@ bool k3_decode_mx_supported(const k3_moe_layer_desc *d) {
            ((((uintptr_t)d->w1_scales) | ((uintptr_t)d->w3_scales) | ((uintptr_t)d->w2_scales)) & 15u) == 0;
 }
 
+void k3_decode_mx_vector_scratch(const k3_moe_layer_desc *d, void *scratch, void **x_hl, void **x_sf) {
+    auto align = [](uint8_t *p) { return (uint8_t *)(((uintptr_t)p + 255u) & ~(uintptr_t)255u); };
+    uint8_t *hl = align((uint8_t *)scratch);
+    *x_hl = hl;
+    *x_sf = align(hl + (size_t)2 * d->hidden);
+}
+
 // Routed experts of one token: act [top_k, I] and rows_out [top_k, hidden] in rank
-// order (ids on the device), plus - riding along on spare warps - the shared
-// expert: sh_gate / sh_up [S] next to the gate/up products and sh_out [hidden]
-// next to the down products.
-bool k3_decode_mx_experts(const k3_moe_layer_desc *d, const void *x, const void *ids, void *act,
-                          void *rows_out, void *sh_gate, void *sh_up, void *sh_out, void *scratch,
-                          cudaStream_t stream) {
+// order (ids on the device) from the token's E4M3 form in `scratch`; the shared
+// expert's down rows ride along on spare warps of the gate/up kernel.
+bool k3_decode_mx_experts(const k3_moe_layer_desc *d, const void *ids, void *act, void *rows_out,
+                          const void *sh_act, void *sh_out, void *scratch, cudaStream_t stream) {
     const uint32_t H = d->hidden, I = d->expert_hidden, k = d->top_k, S = d->shared_hidden;
     auto align = [](uint8_t *p) { return (uint8_t *)(((uintptr_t)p + 255u) & ~(uintptr_t)255u); };
-    uint8_t *x_hl = align((uint8_t *)scratch);
-    uint8_t *x_sf = align(x_hl + (size_t)2 * H);
+    uint8_t *x_hl = nullptr, *x_sf = nullptr;
+    k3_decode_mx_vector_scratch(d, scratch, (void **)&x_hl, (void **)&x_sf);
     uint8_t *a_hl = align(x_sf + H / 32u);
     uint8_t *a_sf = align(a_hl + (size_t)2 * k * I);
     const size_t smem = kSmemBytes + (size_t)S * 2u;
@@ -484,12 +503,16 @@ bool k3_decode_mx_experts(const k3_moe_layer_desc *d, const void *x, const void 
         configured = smem;
     }
     const uint64_t total = (uint64_t)d->local_expert_count;
-    CUtensorMap m1, m3, m2, mbx, mba;
-    if (!map_fp4(&m1, d->w1_packed, total * I, H) || !map_fp4(&m3, d->w3_packed, total * I, H) ||
-        !map_fp4(&m2, d->w2_packed, total * H, I) || !map_u8(&mbx, x_hl, 2, H) ||
-        !map_u8(&mba, a_hl, 2ull * k, I)) {
+    MxMaps gu, dn;
+    if (!map_fp4(&gu.a0, d->w1_packed, total * I, H) || !map_fp4(&gu.a1, d->w3_packed, total * I, H) ||
+        !map_u8(&gu.b, x_hl, 2, H) || !map_sf(&gu.sfa0, d->w1_scales, total * I, H, 128) ||
+        !map_sf(&gu.sfa1, d->w3_scales, total * I, H, 128) || !map_sf(&gu.sfb, x_sf, 1, H, 1) ||
+        !map_fp4(&dn.a0, d->w2_packed, total * H, I) || !map_u8(&dn.b, a_hl, 2ull * k, I) ||
+        !map_sf(&dn.sfa0, d->w2_scales, total * H, I, 128) || !map_sf(&dn.sfb, a_sf, k, I, 1)) {
         return false;
     }
+    dn.a1 = dn.a0;
+    dn.sfa1 = dn.sfa0;
     MxArgs a{};
     a.ids = (const uint32_t *)ids;
     a.ranks = k;
@@ -498,48 +521,34 @@ bool k3_decode_mx_experts(const k3_moe_layer_desc *d, const void *x, const void 
     a.activation = d->activation;
     a.beta = d->beta;
     a.linear_beta = d->linear_beta;
-    a.q8_block = d->q8_block;
-    a.q8_scale_f16 = d->q8_scale_type;
     const int sms = sm_count();
-    // gate/up + activation (+ shared gate/up rows)
-    split_e4m3_kernel<<<(H / 32u + 7u) / 8u, 256, 0, stream>>>(x_hl, x_sf, (const uint16_t *)x, 1u, H);
-    a.scales_a0 = (const uint8_t *)d->w1_scales;
-    a.scales_a1 = (const uint8_t *)d->w3_scales;
-    a.sfb = x_sf;
+    // gate/up + activation (+ shared down rows)
     a.out = (uint16_t *)act;
     a.act_hl = a_hl;
     a.act_sf = a_sf;
     a.w_rows = I;
     a.k = H;
     a.shared_vector = 1u;
-    const bool side = S != 0;
-    if (side) {
-        a.q8_q0 = (const int8_t *)d->shared_gate_q; a.q8_s0 = d->shared_gate_s; a.q8_out0 = (uint16_t *)sh_gate;
-        a.q8_q1 = (const int8_t *)d->shared_up_q;   a.q8_s1 = d->shared_up_s;   a.q8_out1 = (uint16_t *)sh_up;
-        a.q8_x = (const uint16_t *)x;
-        a.q8_rows = S;
-        a.q8_cols = H;
+    if (S != 0) {
+        a.q8_q = (const int8_t *)d->shared_down_q;
+        a.q8_s = d->shared_down_s;
+        a.q8_out = (uint16_t *)sh_out;
+        a.q8_x = (const uint16_t *)sh_act;
+        a.q8_rows = H;
+        a.q8_cols = S;
+        a.q8_block = d->q8_block;
+        a.q8_scale_f16 = d->q8_scale_type;
     }
-    decode_mx_kernel<true><<<sms, kThreads, smem, stream>>>(m1, m3, mbx, a);
+    decode_mx_kernel<true><<<sms, kThreads, smem, stream>>>(gu, a);
     if (!launch_ok()) return false;
-    // down (+ shared down rows on act(sh_gate, sh_up))
-    a.scales_a0 = a.scales_a1 = (const uint8_t *)d->w2_scales;
-    a.sfb = a_sf;
+    // down
     a.out = (uint16_t *)rows_out;
     a.act_hl = nullptr;
     a.act_sf = nullptr;
     a.w_rows = H;
     a.k = I;
     a.shared_vector = 0u;
-    if (side) {
-        a.q8_q0 = (const int8_t *)d->shared_down_q; a.q8_s0 = d->shared_down_s; a.q8_out0 = (uint16_t *)sh_out;
-        a.q8_q1 = nullptr; a.q8_s1 = nullptr; a.q8_out1 = nullptr;
-        a.q8_x = nullptr;
-        a.q8_gate = (const uint16_t *)sh_gate;
-        a.q8_up = (const uint16_t *)sh_up;
-        a.q8_rows = H;
-        a.q8_cols = S;
-    }
-    decode_mx_kernel<false><<<sms, kThreads, smem, stream>>>(m2, m2, mba, a);
+    a.q8_rows = 0u;
+    decode_mx_kernel<false><<<sms, kThreads, smem, stream>>>(dn, a);
     return launch_ok();
 }

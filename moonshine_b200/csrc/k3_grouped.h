@@ -44,9 +44,13 @@ bool k3_decode_layer(const k3_moe_layer_desc *desc, const void *x, void *logits,
 // Block-scaled tensor-core expert products for one token (k3_decode_mx.cu).
 bool k3_decode_mx_supported(const k3_moe_layer_desc *desc);
 size_t k3_decode_mx_scratch_bytes(const k3_moe_layer_desc *desc);
-bool k3_decode_mx_experts(const k3_moe_layer_desc *desc, const void *x, const void *ids, void *act,
-                          void *rows_out, void *sh_gate, void *sh_up, void *sh_out, void *scratch,
-                          cudaStream_t stream);
+// where the token's two-term E4M3 form lives inside `scratch`: x_hl [2, hidden]
+// (row 0 = hi terms, row 1 = lo terms) and x_sf [hidden / 32] block scales
+void k3_decode_mx_vector_scratch(const k3_moe_layer_desc *desc, void *scratch, void **x_hl, void **x_sf);
+// Expert products of one token from its E4M3 form already in `scratch`; the
+// shared expert's down rows (input sh_act [S] bf16 -> sh_out [hidden]) ride along.
+bool k3_decode_mx_experts(const k3_moe_layer_desc *desc, const void *ids, void *act, void *rows_out,
+                          const void *sh_act, void *sh_out, void *scratch, cudaStream_t stream);
 uint32_t k3_decode_mx_status();
 
 // Block-scaled tensor-core grouped expert products for many rows
