@@ -5,9 +5,9 @@
 //            token's two-term E4M3 form; the last block to finish routes the
 //            token (sigmoid + bias top-k) and applies the shared activation
 //   gate/up  the top_k selected experts' gate and up rows + activation
-//            (+ the shared expert's down rows on spare warps)
 //   down     the selected experts' down rows
-//   combine  weighted sum in rank order + shared output
+//   tail     the shared expert's down rows (Q8) fused with the weighted sum in
+//            rank order (one block per output column)
 //
 // It replaces the per-token sequence of the reference's decode_routed_layer
 // (k3_engine.cu:1554-1563 router, :1668-1689 static projections, :1032-1066
@@ -81,56 +81,89 @@ K3_DEVINL void split_block(float val, uint8_t &hi, uint8_t &lo, uint8_t &scale_b
     scale_byte = (uint8_t)(e + 127);
 }
 
-// One warp per task: router rows, shared-expert gate and up rows (reference
-// reduction order), and the 32-column blocks of the token's two-term E4M3 form.
-// The last block to finish then routes the token (sigmoid + bias top-k in the
-// reference's order: larger choice first, lower expert id on ties) and applies the
-// shared expert's activation.
-__global__ void __launch_bounds__(256)
+// One 256-thread block per row task: router rows and the shared expert's gate
+// and up rows (reference reduction order, thread v = the reference's lane v, the
+// whole row in flight at once), plus the 32-column blocks of the token's two-term
+// E4M3 form.  The last block to finish then routes the token (sigmoid + bias
+// top-k in the reference's order: larger choice first, lower expert id on ties)
+// and applies the shared expert's activation.
+__global__ void __launch_bounds__(256, 2)
 decode_front_kernel(DecodeArgs a) {
+    extern __shared__ __align__(16) unsigned char front_smem[];
+    float *xf = reinterpret_cast<float *>(front_smem);                       // [hidden] as fp32
+    __half *xh = reinterpret_cast<__half *>(front_smem + (size_t)a.d.hidden * 4u);   // [2][hidden] f16, rescaled
+    __shared__ float inv_scale[2], stage_scratch[2 * 8], part[8][16];
     __shared__ float choice_s[1024], score_s[1024];
+    __shared__ float red[kRowBlock];
     __shared__ float top_score[32];
-    __shared__ uint32_t top_id[32];
+    __shared__ uint32_t top_id[32], list_key[8 * 32], list_id[8 * 32];
     __shared__ uint32_t is_last;
     const uint32_t warp = threadIdx.x / kWarp, lane = threadIdx.x % kWarp;
-    const uint32_t warps = (gridDim.x * blockDim.x) / kWarp;
     const uint32_t E = a.d.expert_count, S = a.d.shared_hidden, H = a.d.hidden, k = a.d.top_k;
-    const uint32_t split_tasks = a.x_hl ? H / 32u : 0u;
-    const uint32_t tasks = E + 2u * S + split_tasks;
-    const uint32_t blocks_per_row = S ? H / a.d.q8_block : 0u;
-    for (uint32_t task = (blockIdx.x * blockDim.x + threadIdx.x) / kWarp; task < tasks; task += warps) {
+    const uint32_t split_tasks = a.x_hl ? (H / 32u + 7u) / 8u : 0u;        // 8 blocks (one per warp) each
+    for (uint32_t i = threadIdx.x; i < H; i += blockDim.x) xf[i] = bf16_bits_to_float(a.x[i]);
+    stage_vectors_f16(xh, inv_scale, a.x, nullptr, H, H, stage_scratch);     // ends with a block barrier
+    // tasks: router rows one at a time, then blocks of 16 gate / up rows
+    const uint32_t groups = 2u * S / 16u;
+    const uint32_t tasks_total = E + groups + split_tasks;
+    // The extra last block of the grid takes no tasks: it runs the routing code once
+    // on stale data without storing anything, so that those instructions are already
+    // cached when the last worker block needs them - on its own they cost a chain of
+    // instruction fetches from memory several times longer than the arithmetic.
+    const bool warmer = blockIdx.x == gridDim.x - 1u;
+    const uint32_t workers = gridDim.x - 1u;
+    for (uint32_t task = blockIdx.x; !warmer && task < tasks_total; task += workers) {
         if (task < E) {
-            const float v = bf16_row_dot_exact((const uint16_t *)a.d.router_weight + (uint64_t)task * H,
-                                               a.x, H, lane);
-            if (lane == 0) a.logits[task] = v;
-        } else if (task < E + 2u * S) {
-            const uint32_t r = task - E;
-            const bool up = r >= S;
-            const uint32_t row = up ? r - S : r;
-            const int8_t *q = (const int8_t *)(up ? a.d.shared_up_q : a.d.shared_gate_q);
-            const void *sc = up ? a.d.shared_up_s : a.d.shared_gate_s;
-            const float v = q8_row_dot_exact(q + (uint64_t)row * H, sc, (uint64_t)row * blocks_per_row,
-                                             a.x, H, a.d.q8_block, a.d.q8_scale_type, lane);
-            if (lane == 0) (up ? a.sh_up : a.sh_gate)[row] = float_to_bf16_bits(v);
+            Bf16RowLoad p;
+            bf16_block_load(p, (const uint16_t *)a.d.router_weight + (uint64_t)task * H, H);
+            const float v = block_tree_256(bf16_block_lane_sum(p, xf, H), red);
+            if (threadIdx.x == 0) a.logits[task] = v;
+        } else if (task < E + groups) {
+            // 16 gate or up rows on the tensor-core Q8 scheme, the K extent split over the 8 warps
+            const uint32_t r0 = (task - E) * 16u;                     // S % 16 == 0
+            const bool up = r0 >= S;
+            const uint32_t row0 = up ? r0 - S : r0;
+            const uint32_t steps = H / 128u, per = (steps + 7u) / 8u;
+            float p0, p1;
+            q8_rows16_partial<3>(p0, p1, (const int8_t *)(up ? a.d.shared_up_q : a.d.shared_gate_q),
+                                 up ? a.d.shared_up_s : a.d.shared_gate_s, a.d.q8_scale_type, a.d.q8_block,
+                                 row0, H, min(steps, warp * per), min(steps, (warp + 1u) * per), xh);
+            if ((lane & 3u) == 0u) {
+                part[warp][lane >> 2] = p0;
+                part[warp][(lane >> 2) + 8u] = p1;
+            }
+            __syncthreads();
+            if (threadIdx.x < 16u) {
+                float v = 0.f;
+#pragma unroll
+                for (int w = 0; w < 8; w++) v += part[w][threadIdx.x];
+                (up ? a.sh_up : a.sh_gate)[row0 + threadIdx.x] = float_to_bf16_bits(v * inv_scale[0]);
+            }
         } else {
-            const uint32_t blk = task - E - 2u * S;
-            uint8_t hi, lo, sb;
-            split_block(bf16_bits_to_float(a.x[blk * 32u + lane]), hi, lo, sb);
-            a.x_hl[blk * 32u + lane] = hi;
-            a.x_hl[H + blk * 32u + lane] = lo;
-            if (lane == 0) a.x_sf[blk] = sb;
+            const uint32_t blk = (task - E - groups) * 8u + warp;
+            if (blk < H / 32u) {
+                uint8_t hi, lo, sb;
+                split_block(xf[blk * 32u + lane], hi, lo, sb);
+                a.x_hl[blk * 32u + lane] = hi;
+                a.x_hl[H + blk * 32u + lane] = lo;
+                if (lane == 0) a.x_sf[blk] = sb;
+            }
         }
+        __syncthreads();            // `red` is reused by the next task
     }
-    __threadfence();
-    __syncthreads();
-    if (threadIdx.x == 0) {
-        const unsigned int ticket = atomicAdd(a.ticket, 1u);
-        is_last = ticket == gridDim.x - 1u ? 1u : 0u;
+    if (!warmer) {
+        __threadfence();
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            const unsigned int ticket = atomicAdd(a.ticket, 1u);
+            is_last = ticket == workers - 1u ? 1u : 0u;
+        }
+        __syncthreads();
+        if (is_last == 0u) return;
+        __threadfence();
+        if (threadIdx.x == 0) *a.ticket = 0u;
     }
-    __syncthreads();
-    if (is_last == 0u) return;
-    __threadfence();
-    if (threadIdx.x == 0) *a.ticket = 0u;
+    const bool commit = !warmer;
     // ---- routing and shared activation: results of the other blocks come from L2
     for (uint32_t e = threadIdx.x; e < 1024u; e += blockDim.x) {
         float sc = 0.f, ch = 0.f;
@@ -142,54 +175,83 @@ decode_front_kernel(DecodeArgs a) {
         choice_s[e] = ch;
     }
     __syncthreads();
-    if (warp == 0) {
-        // lane owns experts lane, lane + 32, ...; its best candidate is cached
-        const uint32_t slots = (E + 31u) / 32u;
-        uint32_t best_key = 0u, best_id = 0xffffffffu;
-        for (uint32_t i = 0; i < slots; i++) {
-            const uint32_t e = i * 32u + lane;
-            if (e < E) {
-                const uint32_t key = order_key(choice_s[e]);
-                if (best_id == 0xffffffffu || key > best_key) { best_key = key; best_id = e; }
-            }
+    // Two levels of arg-max rounds on order keys (0 = none).  Level 1: warp w owns
+    // experts [128 w, 128 w + 128), four per lane, and lists its top_k best.  Level 2:
+    // warp 0 merges the eight lists.  Ties go to the lower expert id at both levels.
+    {
+        uint32_t key[4];
+#pragma unroll
+        for (uint32_t j = 0; j < 4u; j++) {
+            const uint32_t e = warp * 128u + j * 32u + lane;
+            key[j] = e < E ? order_key(choice_s[e]) : 0u;
         }
         for (uint32_t rank = 0; rank < k; rank++) {
-            const uint32_t has = best_id != 0xffffffffu ? 1u : 0u;
-            const uint32_t top = __reduce_max_sync(0xffffffffu, has ? best_key : 0u);
-            const uint32_t any = __reduce_max_sync(0xffffffffu, has);
-            const uint32_t cand = (has && best_key == top) ? best_id : 0xffffffffu;
-            const uint32_t win = any ? __reduce_min_sync(0xffffffffu, cand) : 0xffffffffu;
-            if (lane == 0) {
-                top_id[rank] = win;
-                top_score[rank] = win != 0xffffffffu ? score_s[win] : 0.f;
+            uint32_t best_key = key[0], best_slot = 0u;
+#pragma unroll
+            for (uint32_t j = 1; j < 4u; j++) {
+                if (key[j] > best_key) { best_key = key[j]; best_slot = j; }
             }
-            if (win != 0xffffffffu && (win & 31u) == lane) {
-                // winner leaves the pool; rescan this lane's candidates
-                choice_s[win] = __uint_as_float(0x7fc00000u);       // marks "taken"
-                best_key = 0u;
-                best_id = 0xffffffffu;
-                for (uint32_t i = 0; i < slots; i++) {
-                    const uint32_t e = i * 32u + lane;
-                    if (e >= E) continue;
-                    const float c = choice_s[e];
-                    if (__float_as_uint(c) == 0x7fc00000u) continue;
-                    const uint32_t key = order_key(c);
-                    if (best_id == 0xffffffffu || key > best_key) { best_key = key; best_id = e; }
+            const uint32_t top = __reduce_max_sync(0xffffffffu, best_key);
+            const uint32_t id = warp * 128u + best_slot * 32u + lane;
+            const uint32_t win = __reduce_min_sync(0xffffffffu, (top != 0u && best_key == top) ? id : 0xffffffffu);
+            if (lane == 0) {
+                list_key[warp * 32u + rank] = top;
+                list_id[warp * 32u + rank] = win;
+            }
+            if (win == id) {
+#pragma unroll
+                for (uint32_t j = 0; j < 4u; j++) {
+                    if (j == best_slot) key[j] = 0u;
                 }
             }
         }
+    }
+    __syncthreads();
+    // Level 2 by rank counting: candidate t of the 8 * top_k listed ones counts the
+    // candidates that beat it; ranks are unique because ids are.
+    if (threadIdx.x < 32u) { top_id[threadIdx.x] = 0xffffffffu; top_score[threadIdx.x] = 0.f; }
+    __syncthreads();
+    {
+        const uint32_t n = 8u * k;                                  // <= 256 = blockDim.x
+        // compact the eight lists (stride 32) into choice_s / red, which are free now
+        uint32_t *ckey = reinterpret_cast<uint32_t *>(choice_s), *cid = reinterpret_cast<uint32_t *>(red);
+        uint32_t my_key = 0u, my_id = 0xffffffffu;
+        if (threadIdx.x < n) {
+            const uint32_t src = (threadIdx.x / k) * 32u + threadIdx.x % k;
+            my_key = list_key[src];
+            my_id = list_id[src];
+        }
+        __syncthreads();                                            // choice_s was read by level 1
+        ckey[threadIdx.x] = my_key;
+        cid[threadIdx.x] = my_id;
+        __syncthreads();
+        uint32_t rank = 0u;
+#pragma unroll 8
+        for (uint32_t u = 0; u < n; u++) {
+            const uint32_t ok = ckey[u], oi = cid[u];
+            rank += (ok > my_key || (ok == my_key && oi < my_id)) ? 1u : 0u;
+        }
+        if (my_key != 0u && rank < k) {
+            top_id[rank] = my_id;
+            top_score[rank] = score_s[my_id];
+        }
+    }
+    __syncthreads();
+    if (warp == 0) {
         __syncwarp();
         float denominator = 1e-20f;
         for (uint32_t r = 0; r < k; r++) denominator += top_score[r];
-        if (lane < k) {
+        if (lane < k && commit) {
             a.ids[lane] = top_id[lane];
             a.weights[lane] = __fmul_rn(__fdiv_rn(top_score[lane], denominator), a.d.route_scale);
         }
     } else {
         for (uint32_t i = threadIdx.x - kWarp; i < S; i += blockDim.x - kWarp) {
-            a.sh_act[i] = float_to_bf16_bits(activation(bf16_bits_to_float(__ldcg(a.sh_gate + i)),
-                                                        bf16_bits_to_float(__ldcg(a.sh_up + i)),
-                                                        a.d.activation, a.d.beta, a.d.linear_beta));
+            const uint16_t bits =
+                float_to_bf16_bits(activation(bf16_bits_to_float(__ldcg(a.sh_gate + i)),
+                                              bf16_bits_to_float(__ldcg(a.sh_up + i)), a.d.activation,
+                                              a.d.beta, a.d.linear_beta));
+            if (commit) a.sh_act[i] = bits;
         }
     }
 }
@@ -361,6 +423,56 @@ decode_down_kernel(DecodeArgs a) {
     }
 }
 
+// ------------------------------------------------------------------- tail
+// One 128-thread block per 16 output columns: the shared expert's down rows (Q8 on
+// the tensor-core scheme, K split over the 4 warps) and the weighted sum of the
+// selected experts' rows in rank order,
+//   out[c] = bf16( bf16(sum_r w[r] * rows[r][c]) + shared_down[c] ).
+__global__ void __launch_bounds__(128, 4)
+decode_tail_kernel(DecodeArgs a, uint16_t *__restrict__ out) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    __half *act_h = reinterpret_cast<__half *>(smem_raw);                   // [2][S] f16, rescaled
+    __shared__ float terms[32][16], w_s[32], part[4][16];
+    __shared__ float inv_scale[2], stage_scratch[2 * 4];
+    const uint32_t H = a.d.hidden, S = a.d.shared_hidden, k = a.d.top_k;
+    const uint32_t warp = threadIdx.x / kWarp, lane = threadIdx.x % kWarp;
+    if (S != 0u) stage_vectors_f16(act_h, inv_scale, a.sh_act, nullptr, S, S, stage_scratch);
+    if (threadIdx.x < k) w_s[threadIdx.x] = a.weights[threadIdx.x];
+    for (uint32_t c0 = blockIdx.x * 16u; c0 < H; c0 += gridDim.x * 16u) {           // H % 16 == 0
+        // experts' values of these columns: thread (rank, column)
+        for (uint32_t i = threadIdx.x; i < k * 16u; i += blockDim.x) {
+            const uint32_t r = i / 16u, j = i % 16u;
+            terms[r][j] = bf16_bits_to_float(a.rows_out[(uint64_t)r * H + c0 + j]);
+        }
+        if (S != 0u) {
+            const uint32_t steps = S / 128u, per = (steps + 3u) / 4u;
+            float p0, p1;
+            q8_rows16_partial<2>(p0, p1, (const int8_t *)a.d.shared_down_q, a.d.shared_down_s,
+                                 a.d.q8_scale_type, a.d.q8_block, c0, S, min(steps, warp * per),
+                                 min(steps, (warp + 1u) * per), act_h);
+            if ((lane & 3u) == 0u) {
+                part[warp][lane >> 2] = p0;
+                part[warp][(lane >> 2) + 8u] = p1;
+            }
+        }
+        __syncthreads();
+        if (threadIdx.x < 16u) {
+            float acc = 0.f;
+            for (uint32_t r = 0; r < k; r++) acc = fmaf(w_s[r], terms[r][threadIdx.x], acc);
+            uint32_t bits = float_to_bf16_bits(acc);
+            if (S != 0u) {
+                float v = 0.f;
+#pragma unroll
+                for (int w = 0; w < 4; w++) v += part[w][threadIdx.x];
+                bits = float_to_bf16_bits(bf16_bits_to_float(bits) +
+                                          bf16_bits_to_float(float_to_bf16_bits(v * inv_scale[0])));
+            }
+            out[c0 + threadIdx.x] = (uint16_t)bits;
+        }
+        __syncthreads();
+    }
+}
+
 bool set_smem(const void *kernel, size_t smem) {
     if (smem <= 48 * 1024) return true;
     if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
@@ -375,8 +487,8 @@ bool set_smem(const void *kernel, size_t smem) {
 // Shapes the persistent one-token kernels handle; anything else takes the generic path.
 bool k3_decode_supported(const k3_moe_layer_desc *d) {
     return d->hidden % 256u == 0 && d->expert_hidden % 128u == 0 && d->hidden % 128u == 0 &&
-           d->expert_count <= 1024u && d->top_k <= 32u &&
-           (d->shared_hidden == 0 || (d->shared_hidden % 8u == 0 && d->q8_block % 8u == 0)) &&
+           d->expert_count <= 1024u && d->top_k <= 32u && d->hidden <= 8192u && d->shared_hidden <= 8192u &&
+           (d->shared_hidden == 0 || (d->shared_hidden % 128u == 0 && d->q8_block % 32u == 0)) &&
            (size_t)(d->top_k + 1u) * d->expert_hidden * 2u + 512u <= 200u * 1024u &&
            ((d->hidden / 32u) % 2u == 0) && ((d->expert_hidden / 32u) % 2u == 0);
 }
@@ -384,7 +496,7 @@ bool k3_decode_supported(const k3_moe_layer_desc *d) {
 // buffers: see DecodeArgs; all caller-owned scratch carved from the layer workspace
 bool k3_decode_layer(const k3_moe_layer_desc *d, const void *x, void *logits, void *ids,
                      void *weights, void *sh_gate, void *sh_up, void *sh_act, void *sh_out,
-                     void *act, void *rows_out, void *scratch, size_t scratch_bytes,
+                     void *act, void *rows_out, void *out, void *scratch, size_t scratch_bytes,
                      cudaStream_t stream) {
     DecodeArgs a{};
     a.d = *d;
@@ -399,7 +511,7 @@ bool k3_decode_layer(const k3_moe_layer_desc *d, const void *x, void *logits, vo
     a.act = (uint16_t *)act;
     a.rows_out = (uint16_t *)rows_out;
     const int sms = sm_count();
-    const bool mx = scratch != nullptr && k3_decode_mx_supported(d) &&
+    const bool mx = scratch != nullptr && k3_decode_mx_supported(d) && d->top_k < 32u &&
                     scratch_bytes >= k3_decode_mx_scratch_bytes(d);
     if (mx) k3_decode_mx_vector_scratch(d, scratch, (void **)&a.x_hl, (void **)&a.x_sf);
     static std::atomic<uint32_t> next_ticket{0};
@@ -409,11 +521,19 @@ bool k3_decode_layer(const k3_moe_layer_desc *d, const void *x, void *logits, vo
         return false;
     }
     a.ticket = tickets + next_ticket.fetch_add(1u) % kTicketSlots;
-    const uint32_t front_tasks = d->expert_count + 2u * d->shared_hidden + (mx ? d->hidden / 32u : 0u);
-    decode_front_kernel<<<std::min<uint32_t>((front_tasks + 7u) / 8u, (uint32_t)sms * 8u), 256, 0, stream>>>(a);
+    const uint32_t front_tasks = d->expert_count + 2u * d->shared_hidden / 16u +
+                                 (mx ? (d->hidden / 32u + 7u) / 8u : 0u);
+    const size_t front_smem = (size_t)d->hidden * 8u;      // fp32 copy + two f16 slots (the second stays zero)
+    if (!set_smem((const void *)decode_front_kernel, front_smem)) return false;
+    decode_front_kernel<<<std::min<uint32_t>(front_tasks, (uint32_t)sms * 2u - 1u) + 1u, 256, front_smem, stream>>>(a);
     if (!launch_ok()) return false;
     if (mx) {
-        return k3_decode_mx_experts(d, ids, act, rows_out, sh_act, sh_out, scratch, stream);
+        if (!k3_decode_mx_experts(d, ids, act, rows_out, scratch, stream)) return false;
+        const size_t tail_smem = (size_t)d->shared_hidden * 4u;   // two f16 slots (the second stays zero)
+        if (!set_smem((const void *)decode_tail_kernel, tail_smem)) return false;
+        decode_tail_kernel<<<std::min<uint32_t>(d->hidden / 16u, (uint32_t)sms * 4u), 128, tail_smem, stream>>>(
+            a, (uint16_t *)out);
+        return launch_ok();
     }
     size_t smem = (size_t)2 * d->hidden * sizeof(__half) + (2 + 2 * kDecodeWarps) * sizeof(float);
     if (!set_smem((const void *)decode_gateup_kernel, smem)) return false;
@@ -422,5 +542,7 @@ bool k3_decode_layer(const k3_moe_layer_desc *d, const void *x, void *logits, vo
     smem = (size_t)(d->top_k + 1u) * d->expert_hidden * sizeof(__half) + (34 + 2 * kDecodeWarps) * sizeof(float);
     if (!set_smem((const void *)decode_down_kernel, smem)) return false;
     decode_down_kernel<<<sms, kDecodeThreads, smem, stream>>>(a);
-    return launch_ok();
+    if (!launch_ok()) return false;
+    return k3_moe_combine(out, rows_out, nullptr, weights, d->shared_hidden ? sh_out : nullptr, 1u,
+                          d->top_k, d->hidden, stream);
 }

@@ -482,17 +482,16 @@ void k3_decode_mx_vector_scratch(const k3_moe_layer_desc *d, void *scratch, void
 }
 
 // Routed experts of one token: act [top_k, I] and rows_out [top_k, hidden] in rank
-// order (ids on the device) from the token's E4M3 form in `scratch`; the shared
-// expert's down rows ride along on spare warps of the gate/up kernel.
+// order (ids on the device) from the token's E4M3 form in `scratch`.
 bool k3_decode_mx_experts(const k3_moe_layer_desc *d, const void *ids, void *act, void *rows_out,
-                          const void *sh_act, void *sh_out, void *scratch, cudaStream_t stream) {
-    const uint32_t H = d->hidden, I = d->expert_hidden, k = d->top_k, S = d->shared_hidden;
+                          void *scratch, cudaStream_t stream) {
+    const uint32_t H = d->hidden, I = d->expert_hidden, k = d->top_k;
     auto align = [](uint8_t *p) { return (uint8_t *)(((uintptr_t)p + 255u) & ~(uintptr_t)255u); };
     uint8_t *x_hl = nullptr, *x_sf = nullptr;
     k3_decode_mx_vector_scratch(d, scratch, (void **)&x_hl, (void **)&x_sf);
     uint8_t *a_hl = align(x_sf + H / 32u);
     uint8_t *a_sf = align(a_hl + (size_t)2 * k * I);
-    const size_t smem = kSmemBytes + (size_t)S * 2u;
+    const size_t smem = kSmemBytes;
     static size_t configured = 0;
     if (configured < smem) {
         if (cudaFuncSetAttribute(decode_mx_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess ||
@@ -522,23 +521,13 @@ bool k3_decode_mx_experts(const k3_moe_layer_desc *d, const void *ids, void *act
     a.beta = d->beta;
     a.linear_beta = d->linear_beta;
     const int sms = sm_count();
-    // gate/up + activation (+ shared down rows)
+    // gate/up + activation
     a.out = (uint16_t *)act;
     a.act_hl = a_hl;
     a.act_sf = a_sf;
     a.w_rows = I;
     a.k = H;
     a.shared_vector = 1u;
-    if (S != 0) {
-        a.q8_q = (const int8_t *)d->shared_down_q;
-        a.q8_s = d->shared_down_s;
-        a.q8_out = (uint16_t *)sh_out;
-        a.q8_x = (const uint16_t *)sh_act;
-        a.q8_rows = H;
-        a.q8_cols = S;
-        a.q8_block = d->q8_block;
-        a.q8_scale_f16 = d->q8_scale_type;
-    }
     decode_mx_kernel<true><<<sms, kThreads, smem, stream>>>(gu, a);
     if (!launch_ok()) return false;
     // down
@@ -548,7 +537,6 @@ bool k3_decode_mx_experts(const k3_moe_layer_desc *d, const void *ids, void *act
     a.w_rows = H;
     a.k = I;
     a.shared_vector = 0u;
-    a.q8_rows = 0u;
     decode_mx_kernel<false><<<sms, kThreads, smem, stream>>>(dn, a);
     return launch_ok();
 }

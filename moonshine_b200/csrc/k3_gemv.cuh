@@ -21,6 +21,8 @@
 
 #include "k3_common.cuh"
 
+#include <cuda_fp16.h>
+
 namespace k3 {
 
 constexpr int kGemvWarps = 8;               // warps per CTA
@@ -102,6 +104,117 @@ K3_DEVINL void stage_vectors_f16(__half *xs, float *inv_scale, const uint16_t *x
         }
     }
     __syncthreads();
+}
+
+// ---------------------------------------------------------------------------
+// Q8 rows on the same tensor-core scheme.  A lane streams the 32 int8 of one
+// scale-width group (32 columns) of rows g and g+8 per 128-column step, converts
+// them to f16 exactly (byte spliced under the mantissa of 1024.0, then 1152.0
+// subtracted, two elements per instruction) and feeds mma.sync with the
+// block-diagonal B operand, so accumulator column n is the fp32 dot product of
+// group n alone; the block scale (fp16 or fp32, block % 32 == 0) is applied with
+// one fp32 FMA per group.  Products are exact, sums are fp32; only the order of
+// the fp32 additions differs from the reference's Q8 kernel.
+
+// four int8 (one word) -> f16x2 pairs (e0, e1) and (e2, e3)
+K3_DEVINL void int8x4_to_f16(uint32_t w, uint32_t &p01, uint32_t &p23) {
+    const uint32_t u = w ^ 0x80808080u;
+    const uint32_t h01 = __byte_perm(u, 0x64646464u, 0x4140u);
+    const uint32_t h23 = __byte_perm(u, 0x64646464u, 0x4342u);
+    const __half2 bias = __halves2half2(__ushort_as_half((unsigned short)0x6480u),
+                                        __ushort_as_half((unsigned short)0x6480u));
+    const __half2 a = __hsub2(*reinterpret_cast<const __half2 *>(&h01), bias);
+    const __half2 b = __hsub2(*reinterpret_cast<const __half2 *>(&h23), bias);
+    p01 = *reinterpret_cast<const uint32_t *>(&a);
+    p23 = *reinterpret_cast<const uint32_t *>(&b);
+}
+
+struct Q8Step {
+    uint4 a0, a1, b0, b1;      // 32 int8 of row g (a) and row g+8 (b)
+    float sa0, sa1, sb0, sb1;  // scales of the two groups this lane accumulates
+};
+
+K3_DEVINL float q8_scale_at(const void *scales, uint64_t index, int scale_f16) {
+    return scale_f16 ? __half2float(reinterpret_cast<const __half *>(scales)[index])
+                     : reinterpret_cast<const float *>(scales)[index];
+}
+
+// One warp: partial dot products of 16 consecutive Q8 rows [row0, row0+16) of a
+// [rows, k] matrix (k % 128 == 0, block % 32 == 0) with the f16 vector xs over the
+// 128-column steps [step_begin, step_end).  After the call lanes with t == 0 hold
+// the partial sums of rows g (r0) and g + 8 (r1), g = lane / 4.
+template <int kDepth>
+K3_DEVINL void q8_rows16_partial(float &r0, float &r1, const int8_t *q, const void *scales,
+                                 int scale_f16, uint32_t block, uint32_t row0, uint32_t k,
+                                 uint32_t step_begin, uint32_t step_end, const __half *xs) {
+    const uint32_t lane = threadIdx.x % kWarp;
+    const uint32_t g = lane >> 2, t = lane & 3u;
+    const int8_t *pa = q + (uint64_t)(row0 + g) * k;
+    const int8_t *pb = q + (uint64_t)(row0 + g + 8u) * k;
+    const uint64_t sa = (uint64_t)(row0 + g) * (k / block), sb = (uint64_t)(row0 + g + 8u) * (k / block);
+    const bool b_active = g == t;                 // column g carries group t of the vector
+    const __half *xv = xs + 32u * t;
+    const uint32_t sgrp = 2u * (t & 1u);
+    auto fetch = [&](uint32_t step) {
+        Q8Step p;
+        const uint32_t col = 128u * step + 32u * t;
+        p.a0 = ld_stream_16(pa + col);
+        p.a1 = ld_stream_16(pa + col + 16u);
+        p.b0 = ld_stream_16(pb + col);
+        p.b1 = ld_stream_16(pb + col + 16u);
+        const uint32_t c0 = 128u * step + 32u * sgrp;
+        p.sa0 = q8_scale_at(scales, sa + c0 / block, scale_f16);
+        p.sa1 = q8_scale_at(scales, sa + (c0 + 32u) / block, scale_f16);
+        p.sb0 = q8_scale_at(scales, sb + c0 / block, scale_f16);
+        p.sb1 = q8_scale_at(scales, sb + (c0 + 32u) / block, scale_f16);
+        return p;
+    };
+    Q8Step pf[kDepth];
+#pragma unroll
+    for (int i = 0; i < kDepth; i++) {
+        if (step_begin + i < step_end) pf[i] = fetch(step_begin + i);
+    }
+    float acc_a = 0.f, acc_b = 0.f;
+    for (uint32_t step0 = step_begin; step0 < step_end; step0 += kDepth) {
+#pragma unroll
+        for (int i = 0; i < kDepth; i++) {
+            const uint32_t step = step0 + i;
+            if (step >= step_end) break;
+            const Q8Step cur = pf[i];
+            if (step + kDepth < step_end) pf[i] = fetch(step + kDepth);
+            uint32_t xr[16];
+            if (b_active) {
+                const uint4 *p = reinterpret_cast<const uint4 *>(xv + 128u * step);
+#pragma unroll
+                for (int w = 0; w < 4; w++) {
+                    const uint4 v = p[w];
+                    xr[4 * w] = v.x; xr[4 * w + 1] = v.y; xr[4 * w + 2] = v.z; xr[4 * w + 3] = v.w;
+                }
+            } else {
+#pragma unroll
+                for (int w = 0; w < 16; w++) xr[w] = 0u;
+            }
+            float c[4] = {0.f, 0.f, 0.f, 0.f};
+            const uint32_t wa[8] = {cur.a0.x, cur.a0.y, cur.a0.z, cur.a0.w, cur.a1.x, cur.a1.y, cur.a1.z, cur.a1.w};
+            const uint32_t wb[8] = {cur.b0.x, cur.b0.y, cur.b0.z, cur.b0.w, cur.b1.x, cur.b1.y, cur.b1.z, cur.b1.w};
+#pragma unroll
+            for (int w = 0; w < 8; w++) {
+                uint32_t a01, a23, b01, b23;
+                int8x4_to_f16(wa[w], a01, a23);
+                int8x4_to_f16(wb[w], b01, b23);
+                mma_f16_m16n8k16(c, a01, b01, a23, b23, xr[2 * w], xr[2 * w + 1]);
+            }
+            acc_a = fmaf(cur.sa0, c[0], acc_a);
+            acc_a = fmaf(cur.sa1, c[1], acc_a);
+            acc_b = fmaf(cur.sb0, c[2], acc_b);
+            acc_b = fmaf(cur.sb1, c[3], acc_b);
+        }
+    }
+    // lanes t = 0 and 1 hold the two halves (groups 0,1 and 2,3) of every step
+    acc_a += __shfl_xor_sync(0xffffffffu, acc_a, 1);
+    acc_b += __shfl_xor_sync(0xffffffffu, acc_b, 1);
+    r0 = acc_a;
+    r1 = acc_b;
 }
 
 // Partial sums of one 16-row block over 128-column steps [step_begin, step_end).

@@ -33,12 +33,12 @@ bool k3_grouped_tc_experts(const k3_moe_layer_desc *desc, void *rows_out, void *
                            const void *rows_in, const void *offsets, uint32_t rows, void *stream);
 
 // One-token layer on persistent matrix-vector kernels (router, routing, expert
-// gate/up/down and shared-expert rows; the caller runs the combine).  All
-// buffers are caller-owned scratch.
+// gate/up/down, shared expert and the weighted combine into `out` bf16 [hidden]).
+// All other buffers are caller-owned scratch.
 bool k3_decode_supported(const k3_moe_layer_desc *desc);
 bool k3_decode_layer(const k3_moe_layer_desc *desc, const void *x, void *logits, void *ids,
                      void *weights, void *sh_gate, void *sh_up, void *sh_act, void *sh_out,
-                     void *act, void *rows_out, void *scratch, size_t scratch_bytes,
+                     void *act, void *rows_out, void *out, void *scratch, size_t scratch_bytes,
                      cudaStream_t stream);
 
 // Block-scaled tensor-core expert products for one token (k3_decode_mx.cu).
@@ -47,10 +47,9 @@ size_t k3_decode_mx_scratch_bytes(const k3_moe_layer_desc *desc);
 // where the token's two-term E4M3 form lives inside `scratch`: x_hl [2, hidden]
 // (row 0 = hi terms, row 1 = lo terms) and x_sf [hidden / 32] block scales
 void k3_decode_mx_vector_scratch(const k3_moe_layer_desc *desc, void *scratch, void **x_hl, void **x_sf);
-// Expert products of one token from its E4M3 form already in `scratch`; the
-// shared expert's down rows (input sh_act [S] bf16 -> sh_out [hidden]) ride along.
+// Expert products of one token from its E4M3 form already in `scratch`.
 bool k3_decode_mx_experts(const k3_moe_layer_desc *desc, const void *ids, void *act, void *rows_out,
-                          const void *sh_act, void *sh_out, void *scratch, cudaStream_t stream);
+                          void *scratch, cudaStream_t stream);
 uint32_t k3_decode_mx_status();
 
 // Block-scaled tensor-core grouped expert products for many rows

@@ -415,11 +415,13 @@ bool layer_forward_impl(const k3_moe_layer_desc *d, void *out, const void *x, ui
 
     if (!mark(events, 0, stream)) return false;
     const uint32_t *index = nullptr;
-    if (tokens == 1u && k3_decode_supported(d)) {
-        // one token: persistent matrix-vector kernels, rows stay in rank order
+    const bool one_token = tokens == 1u && k3_decode_supported(d);
+    if (one_token) {
+        // one token: persistent matrix-vector kernels, rows stay in rank order, the
+        // combine is part of the sequence
         if (!mark(events, 1, stream) || !mark(events, 2, stream) || !mark(events, 3, stream)) return false;
         if (!k3_decode_layer(d, x, w.logits, w.ids, w.weights, w.sh_gate, w.sh_up, w.sh_act,
-                             w.sh_out, w.act, w.rows_out, w.rows_in,
+                             w.sh_out, w.act, w.rows_out, out, w.rows_in,
                              (size_t)routes * d->hidden * 2u, stream)) {
             return false;
         }
@@ -464,7 +466,8 @@ bool layer_forward_impl(const k3_moe_layer_desc *d, void *out, const void *x, ui
         }
     }
     if (!mark(events, 4, stream)) return false;
-    if (!k3_moe_combine(out, w.rows_out, index, w.weights, d->shared_hidden ? w.sh_out : nullptr,
+    if (!one_token &&
+        !k3_moe_combine(out, w.rows_out, index, w.weights, d->shared_hidden ? w.sh_out : nullptr,
                         tokens, d->top_k, d->hidden, stream)) {
         return false;
     }
