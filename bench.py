@@ -213,10 +213,12 @@ def run_reference(args):
 
 # --------------------------------------------------------------- native arm
 def launches_per_step(tokens: int, shared: bool) -> int:
-    route, shared_k, combine = 2, (4 if shared else 0), 1
+    """Kernels of this library one layer pass launches (baseline shapes)."""
     if tokens == 1:
-        return route + shared_k + 2 + combine
-    return route + shared_k + 3 + 1 + 2 + combine      # dispatch(3) gather(1) grouped(2)
+        return 4                                   # front, gate/up, down, tail
+    route, shared_k, dispatch, combine = 2, (5 if shared else 0), 3, 1
+    experts = 1 + 3 + 2                            # row split, 3 gathers, gate/up and down GEMMs
+    return route + shared_k + dispatch + experts + combine
 
 
 def time_decode(layer, cfg, torch, iters: int = 40):
@@ -228,17 +230,23 @@ def time_decode(layer, cfg, torch, iters: int = 40):
     flush = torch.empty(2 * L2_BYTES, dtype=torch.uint8, device=layer.device)
     for i in range(5):
         layer.forward(xs[i % 8:i % 8 + 1])
-    times = []
+    # every iteration has its own pair of events; the host does not wait inside the
+    # loop, so launch overhead overlaps the previous iteration's flush and layer
+    starts = [torch.cuda.Event(enable_timing=True) for _ in range(iters)]
+    stops = [torch.cuda.Event(enable_timing=True) for _ in range(iters)]
     for i in range(iters):
         flush.fill_(i & 0xFF)
-        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        a.record()
+        starts[i].record()
         layer.forward(xs[i % 8:i % 8 + 1])
-        b.record()
-        b.synchronize()
-        times.append(a.elapsed_time(b))
+        stops[i].record()
+    torch.cuda.synchronize()
+    times = [a.elapsed_time(b) for a, b in zip(starts, stops)]
     ms = statistics.median(times)
-    return ms, min(times)
+    # per-kernel times from events the library records between its launches
+    ph = layer.phase_times(xs[0:1], 10)
+    kernels = {"front_ms": ph["router_ms"] + ph["shared_ms"], "gate_up_ms": ph["dispatch_ms"],
+               "down_ms": ph["experts_ms"], "tail_ms": ph["combine_ms"]}
+    return ms, min(times), kernels
 
 
 def run_native(args):
@@ -367,13 +375,14 @@ def run_native(args):
             if args.workload == "prefill8k":
                 del layer
                 torch.cuda.empty_cache()
-            dms, dmin = time_decode(dlayer, dcfg, torch)
+            dms, dmin, dkernels = time_decode(dlayer, dcfg, torch)
             nbytes = synth.decode_bytes_per_token(dcfg)
             gbs = nbytes / (dms * 1e-3) / 1e9
             decode = {"tokens_per_s": 1e3 / dms, "ms_per_token": dms, "ms_min": dmin,
                       "roofline": {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"],
                                    "unit": "GB/s", "frac": gbs / peaks["hbm_gbs"],
                                    "bytes_per_token": nbytes, "peak_source": peaks["source"]},
+                      "kernels_ms": dkernels,
                       "l2": "flushed between iterations (252 MiB buffer rewritten), 8 tokens round-robin",
                       "gpu_launches_per_token": launches_per_step(1, bool(dcfg["shared_hidden"]))}
         cpu = cpu_baseline(cfg, tokens) if world == 1 else None

@@ -28,6 +28,8 @@
 
 #include <algorithm>
 #include <atomic>
+#include <map>
+#include <mutex>
 
 #include <cuda_fp8.h>
 
@@ -473,12 +475,22 @@ decode_tail_kernel(DecodeArgs a, uint16_t *__restrict__ out) {
     }
 }
 
+// (attribute changes are remembered per kernel: the call costs microseconds of host time)
 bool set_smem(const void *kernel, size_t smem) {
     if (smem <= 48 * 1024) return true;
+    static std::mutex lock;
+    static std::map<std::pair<int, const void *>, size_t> done;      // (device, kernel) -> bytes set
+    int device = 0;
+    (void)cudaGetDevice(&device);
+    std::lock_guard<std::mutex> guard(lock);
+    const auto key = std::make_pair(device, kernel);
+    auto it = done.find(key);
+    if (it != done.end() && it->second >= smem) return true;
     if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
         (void)cudaGetLastError();
         return false;
     }
+    done[key] = smem;
     return true;
 }
 
@@ -497,7 +509,13 @@ bool k3_decode_supported(const k3_moe_layer_desc *d) {
 bool k3_decode_layer(const k3_moe_layer_desc *d, const void *x, void *logits, void *ids,
                      void *weights, void *sh_gate, void *sh_up, void *sh_act, void *sh_out,
                      void *act, void *rows_out, void *out, void *scratch, size_t scratch_bytes,
-                     cudaStream_t stream) {
+                     void *const *events, cudaStream_t stream) {
+    // optional phase events: [1], [2] after the front kernel, [3] after gate/up,
+    // [4] after down (the caller records [0] before and [5] after the call)
+    auto mark = [&](int index) {
+        return !events || !events[index] ||
+               cudaEventRecord((cudaEvent_t)events[index], stream) == cudaSuccess;
+    };
     DecodeArgs a{};
     a.d = *d;
     a.x = (const uint16_t *)x;
@@ -515,10 +533,24 @@ bool k3_decode_layer(const k3_moe_layer_desc *d, const void *x, void *logits, vo
                     scratch_bytes >= k3_decode_mx_scratch_bytes(d);
     if (mx) k3_decode_mx_vector_scratch(d, scratch, (void **)&a.x_hl, (void **)&a.x_sf);
     static std::atomic<uint32_t> next_ticket{0};
+    // address of the ticket array on the current device (looked up once per device)
+    static std::mutex ticket_lock;
+    static std::map<int, unsigned int *> ticket_base;
     unsigned int *tickets = nullptr;
-    if (cudaGetSymbolAddress((void **)&tickets, g_front_tickets) != cudaSuccess) {
-        (void)cudaGetLastError();
-        return false;
+    {
+        int device = 0;
+        (void)cudaGetDevice(&device);
+        std::lock_guard<std::mutex> guard(ticket_lock);
+        auto it = ticket_base.find(device);
+        if (it == ticket_base.end()) {
+            if (cudaGetSymbolAddress((void **)&tickets, g_front_tickets) != cudaSuccess) {
+                (void)cudaGetLastError();
+                return false;
+            }
+            ticket_base[device] = tickets;
+        } else {
+            tickets = it->second;
+        }
     }
     a.ticket = tickets + next_ticket.fetch_add(1u) % kTicketSlots;
     const uint32_t front_tasks = d->expert_count + 2u * d->shared_hidden / 16u +
@@ -526,9 +558,12 @@ bool k3_decode_layer(const k3_moe_layer_desc *d, const void *x, void *logits, vo
     const size_t front_smem = (size_t)d->hidden * 8u;      // fp32 copy + two f16 slots (the second stays zero)
     if (!set_smem((const void *)decode_front_kernel, front_smem)) return false;
     decode_front_kernel<<<std::min<uint32_t>(front_tasks, (uint32_t)sms * 2u - 1u) + 1u, 256, front_smem, stream>>>(a);
-    if (!launch_ok()) return false;
+    if (!launch_ok() || !mark(1) || !mark(2)) return false;
     if (mx) {
-        if (!k3_decode_mx_experts(d, ids, act, rows_out, scratch, stream)) return false;
+        if (!k3_decode_mx_experts(d, ids, act, rows_out, scratch, events ? events[3] : nullptr, stream) ||
+            !mark(4)) {
+            return false;
+        }
         const size_t tail_smem = (size_t)d->shared_hidden * 4u;   // two f16 slots (the second stays zero)
         if (!set_smem((const void *)decode_tail_kernel, tail_smem)) return false;
         decode_tail_kernel<<<std::min<uint32_t>(d->hidden / 16u, (uint32_t)sms * 4u), 128, tail_smem, stream>>>(
@@ -538,11 +573,11 @@ bool k3_decode_layer(const k3_moe_layer_desc *d, const void *x, void *logits, vo
     size_t smem = (size_t)2 * d->hidden * sizeof(__half) + (2 + 2 * kDecodeWarps) * sizeof(float);
     if (!set_smem((const void *)decode_gateup_kernel, smem)) return false;
     decode_gateup_kernel<<<sms, kDecodeThreads, smem, stream>>>(a);
-    if (!launch_ok()) return false;
+    if (!launch_ok() || !mark(3)) return false;
     smem = (size_t)(d->top_k + 1u) * d->expert_hidden * sizeof(__half) + (34 + 2 * kDecodeWarps) * sizeof(float);
     if (!set_smem((const void *)decode_down_kernel, smem)) return false;
     decode_down_kernel<<<sms, kDecodeThreads, smem, stream>>>(a);
-    if (!launch_ok()) return false;
+    if (!launch_ok() || !mark(4)) return false;
     return k3_moe_combine(out, rows_out, nullptr, weights, d->shared_hidden ? sh_out : nullptr, 1u,
                           d->top_k, d->hidden, stream);
 }

@@ -33,6 +33,7 @@
 #include <cuda_fp8.h>
 
 #include <algorithm>
+#include <cstring>
 #include <mutex>
 
 using namespace k3;
@@ -484,7 +485,7 @@ void k3_decode_mx_vector_scratch(const k3_moe_layer_desc *d, void *scratch, void
 // Routed experts of one token: act [top_k, I] and rows_out [top_k, hidden] in rank
 // order (ids on the device) from the token's E4M3 form in `scratch`.
 bool k3_decode_mx_experts(const k3_moe_layer_desc *d, const void *ids, void *act, void *rows_out,
-                          void *scratch, cudaStream_t stream) {
+                          void *scratch, void *between, cudaStream_t stream) {
     const uint32_t H = d->hidden, I = d->expert_hidden, k = d->top_k;
     auto align = [](uint8_t *p) { return (uint8_t *)(((uintptr_t)p + 255u) & ~(uintptr_t)255u); };
     uint8_t *x_hl = nullptr, *x_sf = nullptr;
@@ -501,17 +502,46 @@ bool k3_decode_mx_experts(const k3_moe_layer_desc *d, const void *ids, void *act
         }
         configured = smem;
     }
-    const uint64_t total = (uint64_t)d->local_expert_count;
+    // Tensor maps depend only on the tables, the scratch block and the shape: the
+    // last set is kept (encoding ten maps costs more host time than the launches).
+    struct MapKey {
+        int device;
+        const void *p[7];
+        uint32_t dims[4];
+        bool operator==(const MapKey &o) const {
+            return device == o.device && memcmp(p, o.p, sizeof(p)) == 0 && memcmp(dims, o.dims, sizeof(dims)) == 0;
+        }
+    };
+    static std::mutex map_lock;
+    static MapKey cached_key{-1, {}, {}};
+    static MxMaps cached_gu, cached_dn;
+    MapKey key{};
+    (void)cudaGetDevice(&key.device);
+    const void *ptrs[7] = {d->w1_packed, d->w3_packed, d->w2_packed, d->w1_scales, d->w3_scales, d->w2_scales, scratch};
+    memcpy(key.p, ptrs, sizeof(ptrs));
+    key.dims[0] = H; key.dims[1] = I; key.dims[2] = k; key.dims[3] = d->local_expert_count;
     MxMaps gu, dn;
-    if (!map_fp4(&gu.a0, d->w1_packed, total * I, H) || !map_fp4(&gu.a1, d->w3_packed, total * I, H) ||
-        !map_u8(&gu.b, x_hl, 2, H) || !map_sf(&gu.sfa0, d->w1_scales, total * I, H, 128) ||
-        !map_sf(&gu.sfa1, d->w3_scales, total * I, H, 128) || !map_sf(&gu.sfb, x_sf, 1, H, 1) ||
-        !map_fp4(&dn.a0, d->w2_packed, total * H, I) || !map_u8(&dn.b, a_hl, 2ull * k, I) ||
-        !map_sf(&dn.sfa0, d->w2_scales, total * H, I, 128) || !map_sf(&dn.sfb, a_sf, k, I, 1)) {
-        return false;
+    {
+        std::lock_guard<std::mutex> guard(map_lock);
+        if (!(cached_key == key)) {
+            const uint64_t total = (uint64_t)d->local_expert_count;
+            if (!map_fp4(&gu.a0, d->w1_packed, total * I, H) || !map_fp4(&gu.a1, d->w3_packed, total * I, H) ||
+                !map_u8(&gu.b, x_hl, 2, H) || !map_sf(&gu.sfa0, d->w1_scales, total * I, H, 128) ||
+                !map_sf(&gu.sfa1, d->w3_scales, total * I, H, 128) || !map_sf(&gu.sfb, x_sf, 1, H, 1) ||
+                !map_fp4(&dn.a0, d->w2_packed, total * H, I) || !map_u8(&dn.b, a_hl, 2ull * k, I) ||
+                !map_sf(&dn.sfa0, d->w2_scales, total * H, I, 128) || !map_sf(&dn.sfb, a_sf, k, I, 1)) {
+                return false;
+            }
+            dn.a1 = dn.a0;
+            dn.sfa1 = dn.sfa0;
+            cached_gu = gu;
+            cached_dn = dn;
+            cached_key = key;
+        } else {
+            gu = cached_gu;
+            dn = cached_dn;
+        }
     }
-    dn.a1 = dn.a0;
-    dn.sfa1 = dn.sfa0;
     MxArgs a{};
     a.ids = (const uint32_t *)ids;
     a.ranks = k;
@@ -530,6 +560,7 @@ bool k3_decode_mx_experts(const k3_moe_layer_desc *d, const void *ids, void *act
     a.shared_vector = 1u;
     decode_mx_kernel<true><<<sms, kThreads, smem, stream>>>(gu, a);
     if (!launch_ok()) return false;
+    if (between && cudaEventRecord((cudaEvent_t)between, stream) != cudaSuccess) return false;
     // down
     a.out = (uint16_t *)rows_out;
     a.act_hl = nullptr;

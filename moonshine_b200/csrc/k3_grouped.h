@@ -39,7 +39,7 @@ bool k3_decode_supported(const k3_moe_layer_desc *desc);
 bool k3_decode_layer(const k3_moe_layer_desc *desc, const void *x, void *logits, void *ids,
                      void *weights, void *sh_gate, void *sh_up, void *sh_act, void *sh_out,
                      void *act, void *rows_out, void *out, void *scratch, size_t scratch_bytes,
-                     cudaStream_t stream);
+                     void *const *events, cudaStream_t stream);
 
 // Block-scaled tensor-core expert products for one token (k3_decode_mx.cu).
 bool k3_decode_mx_supported(const k3_moe_layer_desc *desc);
@@ -47,9 +47,10 @@ size_t k3_decode_mx_scratch_bytes(const k3_moe_layer_desc *desc);
 // where the token's two-term E4M3 form lives inside `scratch`: x_hl [2, hidden]
 // (row 0 = hi terms, row 1 = lo terms) and x_sf [hidden / 32] block scales
 void k3_decode_mx_vector_scratch(const k3_moe_layer_desc *desc, void *scratch, void **x_hl, void **x_sf);
-// Expert products of one token from its E4M3 form already in `scratch`.
+// Expert products of one token from its E4M3 form already in `scratch`;
+// `between` (a CUDA event or null) is recorded between gate/up and down.
 bool k3_decode_mx_experts(const k3_moe_layer_desc *desc, const void *ids, void *act, void *rows_out,
-                          void *scratch, cudaStream_t stream);
+                          void *scratch, void *between, cudaStream_t stream);
 uint32_t k3_decode_mx_status();
 
 // Block-scaled tensor-core grouped expert products for many rows

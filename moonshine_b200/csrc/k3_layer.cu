@@ -419,10 +419,10 @@ bool layer_forward_impl(const k3_moe_layer_desc *d, void *out, const void *x, ui
     if (one_token) {
         // one token: persistent matrix-vector kernels, rows stay in rank order, the
         // combine is part of the sequence
-        if (!mark(events, 1, stream) || !mark(events, 2, stream) || !mark(events, 3, stream)) return false;
+        // (phase events there: front | gate/up | down | tail)
         if (!k3_decode_layer(d, x, w.logits, w.ids, w.weights, w.sh_gate, w.sh_up, w.sh_act,
                              w.sh_out, w.act, w.rows_out, out, w.rows_in,
-                             (size_t)routes * d->hidden * 2u, stream)) {
+                             (size_t)routes * d->hidden * 2u, events, stream)) {
             return false;
         }
     } else {
@@ -465,7 +465,7 @@ bool layer_forward_impl(const k3_moe_layer_desc *d, void *out, const void *x, ui
             index = w.inv_perm;
         }
     }
-    if (!mark(events, 4, stream)) return false;
+    if (!one_token && !mark(events, 4, stream)) return false;
     if (!one_token &&
         !k3_moe_combine(out, w.rows_out, index, w.weights, d->shared_hidden ? w.sh_out : nullptr,
                         tokens, d->top_k, d->hidden, stream)) {
