@@ -15,8 +15,9 @@
 // Work item = two 128-row weight tiles x up to 128 token rows of one group over
 // the whole K extent (gate+up with fused activation, or 256 rows of the down
 // projection).  One CTA per SM, persistent, item list derived in-kernel from the
-// group offsets.  Warps: 0 TMA producer (weights), 10 TMA producer (token
-// terms), 1 MMA issuer, 2-5 scale writers (one lane quadrant each), 6-9
+// group offsets.  Warps: 0 TMA producer (weights), 2 TMA producer (token terms),
+// 3 TMA producer (block scales), 1 and 16 MMA issuers (one per weight tile), 4-7
+// scale writers (shared memory -> tensor memory, one lane quadrant each), 8-15
 // epilogue.  All barrier waits are bounded.
 #include "k3_grouped.h"
 #include "k3_moe_ops.h"
@@ -42,7 +43,7 @@ constexpr uint32_t kATx = BM * 64u;                       // bytes the TMA trans
 constexpr uint32_t kBTile = BN * 128u;
 constexpr uint32_t kBBox = 32u;                           // token rows per TMA box
 constexpr uint32_t kStageBytes = 2u * kATile + 2u * kBTile;        // A0 | A1 | Bhi | Blo
-constexpr uint32_t kThreads = 512;                        // 16 warps
+constexpr uint32_t kThreads = 544;                        // 17 warps
 constexpr uint32_t kSfBatches = 3;                        // scale ring in tensor memory: batches of 4 stages
 constexpr uint32_t kSfSlots = 4;                          // scale ring in shared memory
 constexpr uint32_t kSfKind = BM * 16u;                    // one table's 128 rows x 16 scale bytes
@@ -170,17 +171,17 @@ grouped_mx_kernel(const __grid_constant__ GmxMaps maps, GmxArgs a) {
         *abort_flag = 0u;
         for (uint32_t s = 0; s < kStages; s++) {
             mbar_init(&full[s], 2);          // two producers arrive (weights, token terms)
-            mbar_init(&empty[s], 1);
+            mbar_init(&empty[s], 2);         // both MMA issuers release a stage
         }
         for (uint32_t b = 0; b < kSfBatches; b++) {
             mbar_init(&sf_full[b], 4);
-            mbar_init(&sf_empty[b], 1);
+            mbar_init(&sf_empty[b], 2);
         }
         for (uint32_t b = 0; b < kSfSlots; b++) {
             mbar_init(&sfs_full[b], 1);
             mbar_init(&sfs_empty[b], 4);
         }
-        mbar_init(acc_full, 1);
+        mbar_init(acc_full, 2);
         mbar_init(acc_empty, 8);
         fence_barrier_init();
     }
@@ -284,17 +285,25 @@ grouped_mx_kernel(const __grid_constant__ GmxMaps maps, GmxArgs a) {
                 }
             }
         }
-    } else if (warp == 1) {
-        // ===================================================== MMA issuer
+    } else if (warp == 1 || warp == 16) {
+        // ==================================================== MMA issuers
+        // One thread's issue loop cannot keep the tensor pipe fed with K = 32 MMAs, so
+        // warp 1 issues the MMAs of weight tile 0 and warp 16 those of tile 1.  Both
+        // commit to the same stage / scale / accumulator barriers (count 2).
         if (lane == 0) {
+            const uint32_t q = warp == 1 ? 0u : 1u;
             uint32_t s = 0, ph = 0, pacc = 0, sb = 0, sph = 0;
             bool ok = true;
             for (uint32_t w = blockIdx.x; ok && w < total_items; w += gridDim.x) {
                 const Item it = decode_item(w, prefix, a);
                 const uint32_t n_eff = max(16u, (it.rows_valid + 15u) & ~15u);
+                uint32_t idesc[4];
+#pragma unroll
+                for (uint32_t j = 0; j < 4u; j++) idesc[j] = make_idesc_mx(n_eff, j);
                 if (!mbar_wait(acc_empty, pacc ^ 1u, abort_flag)) break;
                 tc_fence_after();
-                const uint32_t d0 = tmem + kAccCol, d1 = d0 + BN;
+                const uint32_t d = tmem + kAccCol + q * BN;
+                const uint32_t sfa_col = tmem + (q == 0u ? kSfa0Col : kSfa1Col);
                 for (uint32_t st = 0; st < steps; st++) {
                     if (!mbar_wait(&full[s], ph, abort_flag) ||
                         ((st & 3u) == 0u && !mbar_wait(&sf_full[sb], sph, abort_flag))) {
@@ -303,19 +312,15 @@ grouped_mx_kernel(const __grid_constant__ GmxMaps maps, GmxArgs a) {
                     }
                     tc_fence_after();
                     unsigned char *src = base + s * kStageBytes;
-                    const uint64_t da0 = make_desc_sw128(smem_u32(src));
-                    const uint64_t da1 = make_desc_sw128(smem_u32(src + kATile));
+                    const uint64_t da = make_desc_sw128(smem_u32(src + q * kATile));
                     const uint64_t dbh = make_desc_sw128(smem_u32(src + 2u * kATile));
                     const uint64_t dbl = make_desc_sw128(smem_u32(src + 2u * kATile + kBTile));
                     const uint32_t sfs = sb * 16u + (st & 3u) * 4u;
 #pragma unroll
                     for (uint32_t j = 0; j < 4u; j++) {          // K blocks of 32 inside the stage
-                        const uint32_t idesc = make_idesc_mx(n_eff, j);
-                        const uint32_t first = (st | j) != 0u ? 1u : 0u;
-                        mma_mx(d0, da0 + 2u * j, dbh + 2u * j, idesc, tmem + kSfa0Col + sfs, tmem + kSfbCol + sfs, first);
-                        mma_mx(d1, da1 + 2u * j, dbh + 2u * j, idesc, tmem + kSfa1Col + sfs, tmem + kSfbCol + sfs, first);
-                        mma_mx(d0, da0 + 2u * j, dbl + 2u * j, idesc, tmem + kSfa0Col + sfs, tmem + kSfbCol + sfs, 1u);
-                        mma_mx(d1, da1 + 2u * j, dbl + 2u * j, idesc, tmem + kSfa1Col + sfs, tmem + kSfbCol + sfs, 1u);
+                        mma_mx(d, da + 2u * j, dbh + 2u * j, idesc[j], sfa_col + sfs, tmem + kSfbCol + sfs,
+                               (st | j) != 0u ? 1u : 0u);
+                        mma_mx(d, da + 2u * j, dbl + 2u * j, idesc[j], sfa_col + sfs, tmem + kSfbCol + sfs, 1u);
                     }
                     mma_commit(&empty[s]);
                     if (++s == kStages) { s = 0; ph ^= 1u; }
