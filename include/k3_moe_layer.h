@@ -150,6 +150,17 @@ bool k3_moe_shared_expert(const k3_moe_layer_desc *desc, void *out, void *gate,
                           void *up, void *act, const void *x, uint32_t tokens,
                           void *stream);
 
+/* The same with the three Q8 tables converted to bf16 once per call into device
+ * scratch (k3_moe_shared_workspace_bytes(desc, tokens) bytes, 0 when the shape
+ * or token count does not suit the path), so that the products run as plain bf16
+ * tensor-core GEMMs with the activation fused into the gate/up epilogue; `act`
+ * is scratch bf16 [tokens, S].  Fails when the workspace is missing or too
+ * small (k3_moe_shared_expert needs none). */
+size_t k3_moe_shared_workspace_bytes(const k3_moe_layer_desc *desc, uint32_t tokens);
+bool k3_moe_shared_expert_ws(const k3_moe_layer_desc *desc, void *out, void *act,
+                             const void *x, uint32_t tokens, void *workspace,
+                             size_t workspace_bytes, void *stream);
+
 /* Combine: out[t] = bf16( bf16(sum_r weights[t,r] * rows[index[t*top_k+r]])
  * + shared[t] ), r ascending; index == NULL means the identity; shared ==
  * NULL skips the add (k3_engine_prefill.inc:1575-1580, 1598-1603). */

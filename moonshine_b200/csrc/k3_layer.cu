@@ -374,6 +374,20 @@ extern "C" bool k3_moe_shared_expert(const k3_moe_layer_desc *d, void *out, void
                               d->q8_block, d->q8_scale_type, stream);
 }
 
+extern "C" size_t k3_moe_shared_workspace_bytes(const k3_moe_layer_desc *d, uint32_t tokens) {
+    if (!desc_ok(d) || tokens == 0) return 0;
+    return k3_grouped_shared_workspace_bytes(d, tokens);
+}
+
+extern "C" bool k3_moe_shared_expert_ws(const k3_moe_layer_desc *d, void *out, void *act, const void *x,
+                                        uint32_t tokens, void *workspace, size_t workspace_bytes,
+                                        void *stream) {
+    if (!desc_ok(d) || d->shared_hidden == 0 || !out || !act || !x || tokens == 0 || !workspace) return false;
+    const size_t need = k3_grouped_shared_workspace_bytes(d, tokens);
+    if (need == 0 || workspace_bytes < need) return false;
+    return k3_grouped_shared_expert(d, out, act, x, tokens, workspace, (cudaStream_t)stream);
+}
+
 extern "C" bool k3_moe_combine(void *out, const void *rows, const void *index,
                                const void *weights, const void *shared, uint32_t tokens,
                                uint32_t top_k, uint32_t hidden, void *stream) {

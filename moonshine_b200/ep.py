@@ -95,8 +95,14 @@ class NativeBackend:
         n, d, i = rows.shape[0], self.cfg["hidden"], self.cfg["expert_hidden"]
         out = self._buf("eo", (n, d), rows.dtype)
         act = self._buf("ea", (n, i), rows.dtype)
-        if n and not ops.k3_moe_experts_grouped(self.layer.desc, out, act, rows, offsets_local, n):
-            raise RuntimeError("k3_moe_experts_grouped failed")
+        if not n:
+            return out
+        # block-scaled path when the shape allows it (needs scratch), else the bf16 one
+        need = ops.k3_moe_experts_workspace_bytes(self.layer.desc, n, 0)
+        ws = self._buf("ews", (max(need, 1),), torch.uint8)
+        if not ops.k3_moe_experts_grouped_ws(self.layer.desc, out, act, rows, None, 0, offsets_local, n,
+                                             ws if need else None, need):
+            raise RuntimeError("k3_moe_experts_grouped_ws failed")
         return out
 
     def shared(self, x):
@@ -106,7 +112,13 @@ class NativeBackend:
         t, d = x.shape
         out = self._buf("so", (t, d), x.dtype)
         g, u, a = (self._buf("s" + n, (t, s), x.dtype) for n in "gua")
-        if not ops.k3_moe_shared_expert(self.layer.desc, out, g, u, a, x, t):
+        need = ops.k3_moe_shared_workspace_bytes(self.layer.desc, t)
+        if need:
+            ws = self._buf("sws", (need,), torch.uint8)
+            ok = ops.k3_moe_shared_expert_ws(self.layer.desc, out, a, x, t, ws, need)
+        else:
+            ok = ops.k3_moe_shared_expert(self.layer.desc, out, g, u, a, x, t)
+        if not ok:
             raise RuntimeError("k3_moe_shared_expert failed")
         return out
 
