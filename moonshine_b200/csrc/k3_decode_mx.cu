@@ -52,12 +52,11 @@ constexpr uint32_t kATx = 128 * 64;        // bytes the TMA transaction counts (
 constexpr uint32_t kBTile = 16 * 128;
 constexpr uint32_t kStageBytes = kATile + kBTile;
 constexpr uint32_t kThreads = 512;
-constexpr uint32_t kSideWarps = 2;          // warps 14, 15 (10: scale producer, 11-13: further MMA issuers)
+constexpr uint32_t kSideWarps = 4;          // warps 12..15 (10: scale producer, 11: second MMA issuer)
 constexpr uint32_t kTmemCols = 512;
-constexpr uint32_t kIssuers = 4;           // MMA-issuing warps (= K steps per scale batch)
-constexpr uint32_t kAccCol = 0;            // 2 buffers x kIssuers x 2 phases x 16 columns
-constexpr uint32_t kSfaCol = 64 * kIssuers; // kSfStages x 4 columns
-constexpr uint32_t kSfbCol = kSfaCol + 4 * kSfStages;  // kSfStages x 4 columns
+constexpr uint32_t kAccCol = 0;            // 2 buffers x 2 issuers x 2 phases x 16 columns
+constexpr uint32_t kSfaCol = 128;          // kSfStages x 4 columns
+constexpr uint32_t kSfbCol = 128 + 4 * kSfStages;  // kSfStages x 4 columns
 constexpr uint32_t kBarrierBytes = 512;
 constexpr uint32_t kSmemBytes =
     kStages * kStageBytes + kSfSlots * kSfSlotBytes + 1024 + kBarrierBytes;   // + shared activation vector
@@ -171,14 +170,14 @@ decode_mx_kernel(const __grid_constant__ MxMaps maps, MxArgs a) {
         }
         for (uint32_t b = 0; b < kSfBatches; b++) {
             mbar_init(&sf_full[b], 4);
-            mbar_init(&sf_empty[b], kIssuers);
+            mbar_init(&sf_empty[b], 2);
         }
         for (uint32_t b = 0; b < kSfSlots; b++) {
             mbar_init(&sfs_full[b], 1);
             mbar_init(&sfs_empty[b], 4);
         }
         for (uint32_t b = 0; b < 2; b++) {
-            mbar_init(&acc_full[b], kIssuers);
+            mbar_init(&acc_full[b], 2);
             mbar_init(&acc_empty[b], 4);
         }
         fence_barrier_init();
@@ -193,10 +192,10 @@ decode_mx_kernel(const __grid_constant__ MxMaps maps, MxArgs a) {
     tc_fence_after();
     const uint32_t tmem = *tmem_slot;
 
-    if (warp >= 14) {
+    if (warp >= 12) {
         // ---- shared-expert rows (SIMT), independent of the tensor pipeline
         // two rows per pass so that twice the loads are in flight
-        const uint32_t side = blockIdx.x * kSideWarps + (warp - 14u);
+        const uint32_t side = blockIdx.x * kSideWarps + (warp - 12u);
         const uint32_t side_total = gridDim.x * kSideWarps;
         const uint32_t bpr = a.q8_cols / (a.q8_block ? a.q8_block : 1u);
         for (uint32_t row = 2u * side; row < a.q8_rows; row += 2u * side_total) {
@@ -265,12 +264,12 @@ decode_mx_kernel(const __grid_constant__ MxMaps maps, MxArgs a) {
                 }
             }
         }
-    } else if (warp == 1 || (warp >= 11 && warp < 11 + kIssuers - 1)) {
-        // Several MMA issuers: the issue loop of one thread, not the tensor pipe, bounds
-        // the rate of these small MMAs, so issuer q takes the K steps with step % kIssuers
-        // == q, each into its own accumulator columns (summed in the epilogue).
+    } else if (warp == 1 || warp == 11) {
+        // Two MMA issuers: the issue loop of one thread, not the tensor pipe, bounds
+        // the rate of these small MMAs, so warp 1 takes the even K steps and warp 11
+        // the odd ones, each into its own accumulator columns (summed in the epilogue).
         if (lane == 0) {
-            const uint32_t q = warp == 1 ? 0u : warp - 10u;
+            const uint32_t q = warp == 1 ? 0u : 1u;
             uint32_t s = q, ph = 0, buf = 0, pacc = 0, sb = 0, sph = 0;
             bool ok = true;
             for (uint32_t it = blockIdx.x; ok && it < items; it += gridDim.x) {
@@ -280,9 +279,10 @@ decode_mx_kernel(const __grid_constant__ MxMaps maps, MxArgs a) {
                 if (!mbar_wait(&acc_empty[buf], pacc ^ 1u, abort_flag)) break;
                 tc_fence_after();
                 for (uint32_t p = 0; ok && p < phases; p++) {
-                    const uint32_t d = tmem + kAccCol + buf * (32u * kIssuers) + q * 32u + p * 16u;
-                    for (uint32_t st = q; st < steps; st += kIssuers) {       // one step of every scale batch
-                        if (!mbar_wait(&full[s], ph, abort_flag) || !mbar_wait(&sf_full[sb], sph, abort_flag)) {
+                    const uint32_t d = tmem + kAccCol + buf * 64u + q * 32u + p * 16u;
+                    for (uint32_t st = q; st < steps; st += 2u) {
+                        if (!mbar_wait(&full[s], ph, abort_flag) ||
+                            ((st & 3u) == q && !mbar_wait(&sf_full[sb], sph, abort_flag))) {
                             ok = false;
                             break;
                         }
@@ -290,17 +290,19 @@ decode_mx_kernel(const __grid_constant__ MxMaps maps, MxArgs a) {
                         unsigned char *src = base + s * kStageBytes;
                         const uint64_t da = make_desc_sw128(smem_u32(src));
                         const uint64_t db = make_desc_sw128(smem_u32(src + kATile));
-                        const uint32_t sfs = (sb * 4u + q) * 4u;
+                        const uint32_t sfs = (sb * 4u + (st & 3u)) * 4u;
 #pragma unroll
                         for (uint32_t j = 0; j < 4u; j++) {
                             mma_mx(d, da + 2u * j, db + 2u * j, make_idesc_mx(j), tmem + kSfaCol + sfs,
                                    tmem + kSfbCol + sfs, (st != q || j != 0u) ? 1u : 0u);
                         }
                         mma_commit(&empty[s]);
-                        s += kIssuers;
+                        s += 2u;
                         if (s >= kStages) { s -= kStages; ph ^= 1u; }
-                        mma_commit(&sf_empty[sb]);
-                        if (++sb == kSfBatches) { sb = 0; sph ^= 1u; }
+                        if ((st & 3u) == q + 2u) {
+                            mma_commit(&sf_empty[sb]);
+                            if (++sb == kSfBatches) { sb = 0; sph ^= 1u; }
+                        }
                     }
                 }
                 if (!ok) break;
@@ -356,28 +358,23 @@ decode_mx_kernel(const __grid_constant__ MxMaps maps, MxArgs a) {
             if (id < a.first_local || id >= a.first_local + a.local_count) continue;
             if (!mbar_wait(&acc_full[buf], pacc, abort_flag)) break;
             tc_fence_after();
-            const uint32_t t0 = tmem + ((32u * quad) << 16) + kAccCol + buf * (32u * kIssuers);
-            float part0[kIssuers], part1[kIssuers];
-            uint32_t h[kIssuers], l[kIssuers], hu[kIssuers], lu[kIssuers];
-#pragma unroll
-            for (uint32_t q = 0; q < kIssuers; q++) {
-                tmem_ld_32x2(t0 + q * 32u, h[q], l[q]);                 // issuer q's K steps: hi and lo term
-                if (kGateUp) tmem_ld_32x2(t0 + q * 32u + 16u, hu[q], lu[q]);
+            const uint32_t t0 = tmem + ((32u * quad) << 16) + kAccCol + buf * 64u;
+            uint32_t h0, l0, h1 = 0, l1 = 0, h2, l2, h3 = 0, l3 = 0;
+            tmem_ld_32x2(t0, h0, l0);                       // even K steps
+            tmem_ld_32x2(t0 + 32u, h2, l2);                 // odd K steps
+            if (kGateUp) {
+                tmem_ld_32x2(t0 + 16u, h1, l1);
+                tmem_ld_32x2(t0 + 48u, h3, l3);
             }
             tmem_ld_wait();
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(&acc_empty[buf]);
             if (++buf == 2u) { buf = 0; pacc ^= 1u; }
-#pragma unroll
-            for (uint32_t q = 0; q < kIssuers; q++) {
-                part0[q] = __uint_as_float(h[q]) + __uint_as_float(l[q]);
-                part1[q] = kGateUp ? __uint_as_float(hu[q]) + __uint_as_float(lu[q]) : 0.f;
-            }
-            const float v0 = (part0[0] + part0[1]) + (part0[2] + part0[3]);
+            const float v0 = (__uint_as_float(h0) + __uint_as_float(l0)) + (__uint_as_float(h2) + __uint_as_float(l2));
             uint16_t *dst = a.out + (uint64_t)rank * a.w_rows + tile * 128u + m;
             if (kGateUp) {
-                const float v1 = (part1[0] + part1[1]) + (part1[2] + part1[3]);
+                const float v1 = (__uint_as_float(h1) + __uint_as_float(l1)) + (__uint_as_float(h3) + __uint_as_float(l3));
                 const float g = bf16_bits_to_float(float_to_bf16_bits(v0));
                 const float u = bf16_bits_to_float(float_to_bf16_bits(v1));
                 const uint16_t act_bits = float_to_bf16_bits(activation(g, u, a.activation, a.beta, a.linear_beta));
