@@ -327,9 +327,6 @@ decode_mx_kernel(const __grid_constant__ MxMaps maps, MxArgs a) {
                 for (uint32_t c = 0; c < 4u; c++)
                     cur[c] = *reinterpret_cast<const uint4 *>(src + (32u * c + lane) * 16u);
                 const uint4 curb = *reinterpret_cast<const uint4 *>(src + kSfaBytes);
-                __syncwarp();
-                if (lane == 0) mbar_arrive(&sfs_empty[ss]);
-                if (++ss == kSfSlots) { ss = 0; ssph ^= 1u; }
                 if (!mbar_wait(&sf_empty[sb], sph ^ 1u, abort_flag)) { ok = false; break; }
                 tc_fence_after();
                 // column (step q, row group c) = q * 4 + c of the batch's 16 columns
@@ -340,6 +337,12 @@ decode_mx_kernel(const __grid_constant__ MxMaps maps, MxArgs a) {
                                           curb.z, curb.z, curb.z, curb.z, curb.w, curb.w, curb.w, curb.w};
                 tmem_st_32x16(tmem + lane_base + kSfaCol + sb * 16u, va);
                 tmem_st_32x16(tmem + lane_base + kSfbCol + sb * 16u, vbb);
+                // The shared-memory slot goes back to the TMA producer only now: the
+                // stores above consumed every loaded register, so the loads have
+                // completed (an arrive right after issuing them would not wait for that).
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&sfs_empty[ss]);
+                if (++ss == kSfSlots) { ss = 0; ssph ^= 1u; }
                 tmem_st_wait();
                 tc_fence_before();
                 __syncwarp();

@@ -353,9 +353,6 @@ grouped_mx_kernel(const __grid_constant__ GmxMaps maps, GmxArgs a) {
 #pragma unroll
                     for (uint32_t c = 0; c < 4u; c++)
                         v[t][c] = *reinterpret_cast<const uint4 *>(src + t * kSfKind + (32u * c + lane) * 16u);
-                __syncwarp();
-                if (lane == 0) mbar_arrive(&sfs_empty[ss]);
-                if (++ss == kSfSlots) { ss = 0; ssph ^= 1u; }
                 if (!mbar_wait(&sf_empty[sb], sph ^ 1u, abort_flag)) { ok = false; break; }
                 tc_fence_after();
 #pragma unroll
@@ -367,6 +364,12 @@ grouped_mx_kernel(const __grid_constant__ GmxMaps maps, GmxArgs a) {
                     const uint32_t col = (t == 0 ? kSfa0Col : t == 1 ? kSfa1Col : kSfbCol) + sb * 16u;
                     tmem_st_32x16(tmem + lane_base + col, cols);
                 }
+                // The shared-memory slot goes back to the TMA producer only now: the
+                // stores above consumed every loaded register, so the loads have
+                // completed (an arrive right after issuing them would not wait for that).
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&sfs_empty[ss]);
+                if (++ss == kSfSlots) { ss = 0; ssph ^= 1u; }
                 tmem_st_wait();
                 tc_fence_before();
                 __syncwarp();

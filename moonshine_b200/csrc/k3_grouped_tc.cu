@@ -461,13 +461,6 @@ grouped_tc_kernel(const __grid_constant__ CUtensorMap map_a0,
                         }
                     }
                 }
-                if (sub == C::kPackSteps - 1u) {
-                    // last quarter of the packed stage is in registers now
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(&p_empty[ps]);
-                    if (++ps == C::kPStages) { ps = 0; pph ^= 1u; }
-                }
-
                 if (!mbar_wait(&a_empty[sa], pha ^ 1u, abort_flag)) { ok = false; break; }
                 // row `row` of the tile: 128 bytes at atom (row/8), line (row%8); 16-byte
                 // chunk c is stored at chunk position c ^ (row % 8)
@@ -485,6 +478,13 @@ grouped_tc_kernel(const __grid_constant__ CUtensorMap map_a0,
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&a_full[sa]);
                 if (++sa == C::kAStages) { sa = 0; pha ^= 1u; }
+                if (sub == C::kPackSteps - 1u) {
+                    // The packed stage goes back to the TMA producer only here: the stores
+                    // above consumed every value loaded from it, so those loads have
+                    // completed (an arrive right after issuing them would not wait).
+                    if (lane == 0) mbar_arrive(&p_empty[ps]);
+                    if (++ps == C::kPStages) { ps = 0; pph ^= 1u; }
+                }
             }
         }
     }
