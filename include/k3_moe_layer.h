@@ -189,6 +189,40 @@ bool k3_moe_layer_forward_events(const k3_moe_layer_desc *desc, void *out,
                                  void *workspace, size_t workspace_bytes,
                                  void *const *events, void *stream);
 
+/* The routed layer at the model's real shape, where the experts work on a
+ * latent vector narrower than the model width (k3: hidden 7168, latent 3584):
+ *
+ *   ids, w      = router(x)                                   x: [T, hidden]
+ *   latent      = routed_expert_down_proj(x)                  Q8 [latent, hidden]
+ *   rows        = experts(latent rows grouped by expert)      MXFP4 tables of width latent
+ *   routed      = sum_r w[r] * rows[r]                        [T, latent]
+ *   routed_full = routed_expert_up_proj(rms_norm(routed))     Q8 [hidden, latent]
+ *   out         = routed_full + shared_expert(x)
+ *
+ * i.e. k3_engine.cu:1668-1671 (latent projection), :1851-1863 (weighted sum,
+ * routed_expert_norm, routed_expert_up_proj), :1889-1893 (add of the shared
+ * output) and k3_engine_prefill.inc:1525-1590, without the host round trips.
+ * `layer.hidden` is the model width (router weight [E, hidden], shared expert
+ * [S, hidden]); the six expert tables of `layer` are shaped with `latent` in
+ * place of hidden.  The two projections use layer.q8_block / q8_scale_type.
+ * No reference operator is replaced one to one: it is the composition. */
+typedef struct k3_moe_latent_desc {
+    k3_moe_layer_desc layer;
+    uint32_t latent;               /* width the experts work at                   */
+    float norm_epsilon;            /* routed_expert_norm epsilon (1e-5)           */
+    const void *down_q;            /* i8 [latent, hidden]                         */
+    const void *down_s;            /* scale [latent, hidden / q8_block]           */
+    const void *norm_weight;       /* bf16 [latent]                               */
+    const void *up_q;              /* i8 [hidden, latent]                         */
+    const void *up_s;              /* scale [hidden, latent / q8_block]           */
+} k3_moe_latent_desc;
+
+size_t k3_moe_latent_workspace_bytes(const k3_moe_latent_desc *desc, uint32_t tokens);
+bool k3_moe_latent_layer_forward(const k3_moe_latent_desc *desc, void *out,
+                                 const void *x, uint32_t tokens, void *workspace,
+                                 size_t workspace_bytes, void *ids_out,
+                                 void *weights_out, void *stream);
+
 /* Device-side status of the tensor-core kernels since the library was loaded:
  * 0 = ok, 1 = a bounded barrier wait gave up (the launch's output is then
  * undefined).  Synchronises with the device. */

@@ -28,6 +28,17 @@ class LayerDesc(C.Structure):
 
 _DP = C.POINTER(LayerDesc)
 
+
+class LatentDesc(C.Structure):
+    """Mirror of ``k3_moe_latent_desc`` (include/k3_moe_layer.h)."""
+    _fields_ = [
+        ("layer", LayerDesc), ("latent", u32), ("norm_epsilon", f32),
+        ("down_q", vp), ("down_s", vp), ("norm_weight", vp), ("up_q", vp), ("up_s", vp),
+    ]
+
+
+_LP = C.POINTER(LatentDesc)
+
 # name -> (restype, argtypes)
 SIGNATURES = {
     # legacy operator interface
@@ -73,6 +84,8 @@ SIGNATURES = {
     "k3_moe_shared_expert_ws": (C.c_bool, [_DP, vp, vp, vp, u32, vp, sz, vp]),
     "k3_moe_shared_expert": (C.c_bool, [_DP, vp, vp, vp, vp, vp, u32, vp]),
     "k3_moe_combine": (C.c_bool, [vp, vp, vp, vp, vp, u32, u32, u32, vp]),
+    "k3_moe_latent_workspace_bytes": (sz, [_LP, u32]),
+    "k3_moe_latent_layer_forward": (C.c_bool, [_LP, vp, vp, u32, vp, sz, vp, vp, vp]),
     "k3_moe_layer_forward": (C.c_bool, [_DP, vp, vp, u32, vp, sz, vp, vp, vp]),
     "k3_moe_layer_forward_events": (C.c_bool, [_DP, vp, vp, u32, vp, sz, C.POINTER(vp), vp]),
     "k3_moe_device_status": (u32, []),
