@@ -2,7 +2,7 @@
 """Benchmark of the routed-MoE layer (synthetic data, seeded).
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl native|reference]
-                    [--workload prefill8k|prefill512|decode]
+                    [--workload prefill8k|prefill512|decode|latent8k]
 
 One step = one pass of the layer over one batch.  Default workload: layer-major
 prefill of 8192 tokens with a Zipf-skewed router bias (the configuration the
@@ -44,6 +44,13 @@ def workload_config(name: str, args=None):
         cfg, tokens = synth.baseline_config(), 512
     elif name == "decode":
         cfg, tokens = synth.baseline_config(), 1
+    elif name == "latent8k":
+        # the reference's real layer shape: experts on a latent vector of width 3584,
+        # SiTU, Q8-128 static projections with f32 scales, routing scale 1
+        cfg = synth.baseline_config(bias_mode="zipf", expert_hidden=3072, activation=synth.ACT_SITU,
+                                    q8_block=128, q8_scale_type=synth.Q8_F32, route_scale=1.0)
+        cfg["latent"] = 3584
+        tokens = 8192
     else:
         raise SystemExit(f"unknown workload {name}")
     if args is not None:                      # reduced cases for profiler captures only
@@ -249,6 +256,43 @@ def time_decode(layer, cfg, torch, iters: int = 40):
     return ms, min(times), kernels
 
 
+def run_latent(args, cfg, tokens, device, peaks, torch):
+    """The latent-shape layer (k3_moe_latent_layer_forward): whole-step timing only."""
+    from moonshine_b200.layer import LatentMoELayer
+    latent = cfg.pop("latent")
+    layer = LatentMoELayer(cfg, latent, seed=0, device=device, max_tokens=tokens)
+    d, k, i, s, e = cfg["hidden"], cfg["top_k"], cfg["expert_hidden"], cfg["shared_hidden"], cfg["experts"]
+    x = torch.from_numpy(synth.activations(0, tokens, d).view(np.int16).copy()).view(torch.bfloat16).to(device)
+    for _ in range(max(args.warmup, 3)):
+        layer.forward(x)
+    torch.cuda.synchronize()
+    sampler = ClockSampler(0)
+    sampler.start()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for _ in range(args.steps):
+        layer.forward(x)
+    stop.record()
+    torch.cuda.synchronize()
+    clocks = sampler.stop()
+    ms = start.elapsed_time(stop) / args.steps
+    flops = tokens * (k * 6 * i * latent + 4 * latent * d + 6 * s * d + 2 * e * d)
+    achieved = flops / (ms * 1e-3) / 1e12
+    print(json.dumps({
+        "metric": METRIC, "value": tokens / (ms * 1e-3), "unit": UNIT, "n_gpus": 1, "steps": args.steps,
+        "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": args.workload, "tokens": tokens, "experts": e, "top_k": k, "hidden": d,
+                   "latent": latent, "expert_hidden": i, "shared_hidden": s, "router_bias": "zipf",
+                   "l2": "inputs larger than L2"},
+        "gpu_launches": (launches_per_step(tokens, bool(s)) + 4) * args.steps, "clocks": clocks,
+        "roofline": {"bound": "tensor", "kernel": "whole layer pass", "achieved": achieved,
+                     "peak": peaks["bf16_tflops_sustained"], "unit": "TFLOP/s",
+                     "frac": achieved / peaks["bf16_tflops_sustained"], "traffic": None,
+                     "peak_source": peaks["source"] + " bf16 sustained"},
+        "e2e": None, "cpu_baseline": None}))
+
+
 def run_native(args):
     import torch
     import torch.distributed as dist
@@ -275,6 +319,10 @@ def run_native(args):
     d, k = cfg["hidden"], cfg["top_k"]
     flops = synth.prefill_flops_per_token(cfg)
 
+    if "latent" in cfg:
+        if world > 1:
+            raise SystemExit("the latent workload runs on one GPU")
+        return run_latent(args, cfg, tokens, device, peaks, torch)
     if world > 1:
         from moonshine_b200.ep import ExpertParallelLayer
         layer = ExpertParallelLayer(cfg, seed=0, device=device, tokens=tokens)
@@ -414,7 +462,7 @@ def main():
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="native", choices=["native", "reference"])
-    ap.add_argument("--workload", default="prefill8k", choices=["prefill8k", "prefill512", "decode"])
+    ap.add_argument("--workload", default="prefill8k", choices=["prefill8k", "prefill512", "decode", "latent8k"])
     ap.add_argument("--lean", action="store_true", help="timed region only (for profiler captures)")
     ap.add_argument("--experts", type=int, default=0, help="override the expert count (profiler captures)")
     ap.add_argument("--tokens", type=int, default=0, help="override the token count (profiler captures)")

@@ -18,6 +18,13 @@ bool k3_grouped_q8_bf16(void *out, const void *q, const void *scales, const void
                         uint32_t tokens, uint32_t rows, uint32_t cols, uint32_t block,
                         int scale_type, void *stream);
 
+// One Q8 projection as a plain bf16 tensor-core GEMM: the table is converted to bf16
+// once into weight_scratch (rows * cols * 2 bytes).  False when the shape or the
+// token count does not suit the path (the caller then uses k3_grouped_q8_bf16).
+bool k3_grouped_q8_dense_bf16(void *out, const void *q, const void *scales, const void *x,
+                              uint32_t tokens, uint32_t rows, uint32_t cols, uint32_t block,
+                              int scale_type, void *weight_scratch, cudaStream_t stream);
+
 // Shared expert with its Q8 tables converted to bf16 once per call in `workspace`
 // (k3_grouped_shared_workspace_bytes, 0 when the shape does not suit the path).
 // act bf16 [tokens, S] is scratch, out bf16 [tokens, H].

@@ -648,6 +648,32 @@ bool k3_grouped_q8_bf16(void *out, const void *q, const void *scales, const void
     return k3_moe_q8_gemm_bf16(out, q, scales, x, tokens, rows, cols, block, scale_type, stream);
 }
 
+// out bf16 [tokens, rows] = x [tokens, cols] * dequant(q, scales)^T with the table
+// converted to bf16 once into weight_scratch (rows * cols * 2 bytes), then a plain
+// bf16 tensor-core GEMM.  False when the shape does not suit the path.
+bool k3_grouped_q8_dense_bf16(void *out, const void *q, const void *scales, const void *x, uint32_t tokens,
+                              uint32_t rows, uint32_t cols, uint32_t block, int scale_type,
+                              void *weight_scratch, cudaStream_t stream) {
+    if (tokens < 32u || !tc_shape_ok(cols, tokens) || block % 16u != 0 || !encode_fn() || !weight_scratch ||
+        ((((uintptr_t)q) | ((uintptr_t)x) | ((uintptr_t)weight_scratch)) & 15u) != 0) {
+        return false;
+    }
+    const uint64_t units = (uint64_t)rows * cols / 16u;
+    const uint32_t blocks = (uint32_t)std::min<uint64_t>((units + 255u) / 256u, (uint64_t)sm_count() * 16u);
+    q8_to_bf16_kernel<<<blocks, 256, 0, stream>>>((uint4 *)weight_scratch, (const uint4 *)q, scales, units, block,
+                                                  scale_type);
+    if (!launch_ok()) return false;
+    TcArgs a{};
+    a.out = out;
+    a.groups = 1;
+    a.rows = tokens;
+    a.w_rows = rows;
+    a.k = cols;
+    a.out_width = rows;
+    a.m_items = (rows + 2u * BM - 1u) / (2u * BM);
+    return launch_tc<kABf16, kEBf16>(weight_scratch, weight_scratch, a, x, stream);
+}
+
 size_t k3_grouped_shared_workspace_bytes(const k3_moe_layer_desc *d, uint32_t tokens) {
     if (d->shared_hidden == 0 || tokens < 32u || !tc_shape_ok(d->hidden, tokens) ||
         !tc_shape_ok(d->shared_hidden, tokens) || d->q8_block % 16u != 0 || !encode_fn()) {

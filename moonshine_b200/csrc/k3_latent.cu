@@ -32,7 +32,7 @@ struct LatentWorkspace {
     size_t dispatch_bytes;
     uint16_t *latent, *rows_in, *act, *rows_out, *routed, *routed_norm, *routed_full;
     uint16_t *sh_gate, *sh_up, *sh_act, *sh_out;
-    void *mx_ws, *sh_ws;
+    void *mx_ws, *sh_ws, *proj_w;
     size_t mx_bytes, sh_bytes, total;
 };
 
@@ -76,6 +76,7 @@ LatentWorkspace carve(const k3_moe_latent_desc *d, uint32_t tokens, void *base) 
     w.routed = (uint16_t *)take((size_t)tokens * L * 2u);
     w.routed_norm = (uint16_t *)take((size_t)tokens * L * 2u);
     w.routed_full = (uint16_t *)take((size_t)tokens * H * 2u);
+    w.proj_w = tokens >= 32u ? take(H * L * 2u) : nullptr;      // bf16 copy of one projection table
     w.mx_bytes = k3_grouped_mx_supported(&e, (uint32_t)routes)
                      ? k3_grouped_mx_workspace_bytes(&e, (uint32_t)routes, tokens) : 0;
     w.mx_ws = take(w.mx_bytes);
@@ -119,7 +120,9 @@ extern "C" bool k3_moe_latent_layer_forward(const k3_moe_latent_desc *d, void *o
 
     // router on the full-width token, experts on the latent projection
     if (!k3_moe_route(&l, w.ids, w.weights, w.logits, x, tokens, stream)) return false;
-    if (!k3_grouped_q8_bf16(w.latent, d->down_q, d->down_s, x, tokens, L, H, l.q8_block, l.q8_scale_type,
+    if (!(w.proj_w && k3_grouped_q8_dense_bf16(w.latent, d->down_q, d->down_s, x, tokens, L, H, l.q8_block,
+                                               l.q8_scale_type, w.proj_w, stream)) &&
+        !k3_grouped_q8_bf16(w.latent, d->down_q, d->down_s, x, tokens, L, H, l.q8_block, l.q8_scale_type,
                             stream)) {
         return false;
     }
@@ -150,7 +153,9 @@ extern "C" bool k3_moe_latent_layer_forward(const k3_moe_latent_desc *d, void *o
         return false;
     }
     void *full = l.shared_hidden ? (void *)w.routed_full : out;
-    if (!k3_grouped_q8_bf16(full, d->up_q, d->up_s, w.routed_norm, tokens, H, L, l.q8_block, l.q8_scale_type,
+    if (!(w.proj_w && k3_grouped_q8_dense_bf16(full, d->up_q, d->up_s, w.routed_norm, tokens, H, L, l.q8_block,
+                                               l.q8_scale_type, w.proj_w, stream)) &&
+        !k3_grouped_q8_bf16(full, d->up_q, d->up_s, w.routed_norm, tokens, H, L, l.q8_block, l.q8_scale_type,
                             stream)) {
         return false;
     }

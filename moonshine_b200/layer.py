@@ -151,3 +151,69 @@ class MoELayer:
 
     def weight_bytes(self) -> int:
         return sum(v.numel() * v.element_size() for v in self.t.values())
+
+
+class LatentMoELayer:
+    """The routed layer at the model's real shape: router and shared expert at the
+    model width ``cfg['hidden']``, experts on a latent projection of width
+    ``latent`` (``k3_moe_latent_layer_forward``).  Tensors are seeded synthetic."""
+
+    def __init__(self, cfg: dict, latent: int, seed: int = 0, device="cuda:0", max_tokens: int = 1,
+                 norm_epsilon: float = 1e-5):
+        self.cfg = dict(cfg)
+        self.latent = latent
+        self.device = torch.device(device)
+        h = cfg["hidden"]
+        # expert tables at the latent width (a MoELayer without shared expert owns them),
+        # router and shared expert at the model width
+        inner_cfg = dict(cfg, hidden=latent, shared_hidden=0)
+        self.inner = MoELayer(inner_cfg, None, seed=seed + 1, device=device, max_tokens=1)
+        outer = synth.make_layer(cfg, seed, experts=False)
+        self.t = {k: _dev(v, self.device) for k, v in outer.items() if k != "config"}
+        blk = cfg["q8_block"]
+        sdt = torch.float16 if cfg["q8_scale_type"] == synth.Q8_F16 else torch.float32
+        with torch.cuda.device(self.device):
+            for name, rows, cols, tag in (("down", latent, h, 911), ("up", h, latent, 913)):
+                q = torch.empty((rows, cols), dtype=torch.int8, device=self.device)
+                sc = torch.empty((rows, cols // blk), dtype=sdt, device=self.device)
+                if not ops.k3_synth_fill_int8(q, q.numel(), synth.stream_key(seed, tag), 0) or \
+                        not ops.k3_synth_fill_uniform(sc, sc.numel(), synth.stream_key(seed, tag + 1), 0,
+                                                      1e-4, 9e-4, 1 if sdt is torch.float16 else 0):
+                    raise RuntimeError("synthetic fill failed")
+                self.t[name + "_q"], self.t[name + "_s"] = q, sc
+            self.t["norm_w"] = torch.ones(latent, dtype=torch.bfloat16, device=self.device)
+        self.desc = _native.LatentDesc()
+        C.memmove(C.byref(self.desc.layer), C.byref(self.inner.desc), C.sizeof(_native.LayerDesc))
+        lay = self.desc.layer
+        lay.hidden, lay.shared_hidden = h, cfg["shared_hidden"]
+        for name in ("router_weight", "router_bias"):
+            setattr(lay, name, self.t[name].data_ptr())
+        if cfg["shared_hidden"]:
+            for name in synth.shared_tensor_specs(cfg):
+                setattr(lay, name + "_q", self.t[name + "_q"].data_ptr())
+                setattr(lay, name + "_s", self.t[name + "_s"].data_ptr())
+        self.desc.latent, self.desc.norm_epsilon = latent, norm_epsilon
+        self.desc.down_q, self.desc.down_s = self.t["down_q"].data_ptr(), self.t["down_s"].data_ptr()
+        self.desc.up_q, self.desc.up_s = self.t["up_q"].data_ptr(), self.t["up_s"].data_ptr()
+        self.desc.norm_weight = self.t["norm_w"].data_ptr()
+        self.max_tokens = 0
+        self.workspace = None
+        self.reserve(max_tokens)
+
+    def reserve(self, max_tokens: int) -> None:
+        if max_tokens <= self.max_tokens:
+            return
+        need = ops.k3_moe_latent_workspace_bytes(self.desc, max_tokens)
+        if need == 0:
+            raise RuntimeError("k3_moe_latent_workspace_bytes rejected the layer description")
+        self.workspace = torch.empty(need, dtype=torch.uint8, device=self.device)
+        self.max_tokens = max_tokens
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        tokens = x.shape[0]
+        self.reserve(tokens)
+        out = torch.empty_like(x)
+        if not ops.k3_moe_latent_layer_forward(self.desc, out, x, tokens, self.workspace,
+                                               self.workspace.numel(), None, None):
+            raise RuntimeError("k3_moe_latent_layer_forward failed")
+        return out
