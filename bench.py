@@ -218,6 +218,13 @@ def run_reference(args):
     print(json.dumps(line))
 
 
+# DRAM bytes per launch measured with ncu on these workloads (one-pass metrics,
+# profiles/dram_traffic_full_size.md): prefill = gate/up (28.81 GB) + down (11.73 GB)
+# launches of the grouped expert phase; decode = the four kernels of one token.
+PREFILL_TRAFFIC_BYTES = 40.54e9
+DECODE_TRAFFIC_BYTES = 434.8e6
+
+
 # --------------------------------------------------------------- native arm
 def launches_per_step(tokens: int, shared: bool) -> int:
     """Kernels of this library one layer pass launches (baseline shapes)."""
@@ -407,7 +414,10 @@ def run_native(args):
             roofline = {"bound": "tensor", "kernel": "grouped expert products (gate+up+act, down)",
                         "achieved": achieved, "peak": peaks["bf16_tflops_sustained"],
                         "unit": "TFLOP/s", "frac": achieved / peaks["bf16_tflops_sustained"],
-                        "traffic": None, "peak_source": peaks["source"] + " bf16 sustained",
+                        "traffic": PREFILL_TRAFFIC_BYTES if args.workload == "prefill8k" and world == 1 else None,
+                        "traffic_note": "DRAM read+write of the two grouped GEMM launches, ncu one-pass capture "
+                                        "of this workload (profiles/dram_traffic_full_size.md); algorithmic 26.2 GB",
+                        "peak_source": peaks["source"] + " bf16 sustained",
                         "launch_ms": experts_ms,
                         "hbm_floor_gbs": weight_bytes / (experts_ms * 1e-3) / 1e9}
         else:
@@ -415,7 +425,7 @@ def run_native(args):
             achieved = nbytes / (ms_step * 1e-3) / 1e9
             roofline = {"bound": "hbm", "kernel": "one-token layer", "achieved": achieved,
                         "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"],
-                        "traffic": None, "peak_source": peaks["source"]}
+                        "traffic": DECODE_TRAFFIC_BYTES, "peak_source": peaks["source"]}
         decode = None
         if world == 1:
             dcfg = synth.baseline_config()
@@ -429,7 +439,8 @@ def run_native(args):
             decode = {"tokens_per_s": 1e3 / dms, "ms_per_token": dms, "ms_min": dmin,
                       "roofline": {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"],
                                    "unit": "GB/s", "frac": gbs / peaks["hbm_gbs"],
-                                   "bytes_per_token": nbytes, "peak_source": peaks["source"]},
+                                   "bytes_per_token": nbytes, "traffic": DECODE_TRAFFIC_BYTES,
+                                   "peak_source": peaks["source"]},
                       "kernels_ms": dkernels,
                       "l2": "flushed between iterations (252 MiB buffer rewritten), 8 tokens round-robin",
                       "gpu_launches_per_token": launches_per_step(1, bool(dcfg["shared_hidden"]))}
