@@ -229,7 +229,7 @@ DECODE_TRAFFIC_BYTES = 434.8e6
 def launches_per_step(tokens: int, shared: bool) -> int:
     """Kernels of this library one layer pass launches (baseline shapes)."""
     if tokens == 1:
-        return 4                                   # front, gate/up, down, tail
+        return 6                                   # front, gate/up, down, combine + shared gate/up, shared down
     route, shared_k, dispatch, combine = 2, (5 if shared else 0), 3, 1
     experts = 1 + 3 + 2                            # row split, 3 gathers, gate/up and down GEMMs
     return route + shared_k + dispatch + experts + combine
@@ -259,7 +259,9 @@ def time_decode(layer, cfg, torch, iters: int = 40):
     # per-kernel times from events the library records between its launches
     ph = layer.phase_times(xs[0:1], 10)
     kernels = {"front_ms": ph["router_ms"] + ph["shared_ms"], "gate_up_ms": ph["dispatch_ms"],
-               "down_ms": ph["experts_ms"], "tail_ms": ph["combine_ms"]}
+               "down_ms": ph["experts_ms"], "combine_ms": ph["combine_ms"],
+               "note": "events between launches on the main stream; the shared expert runs beside them on a "
+                       "side stream; front includes host launch latency after an idle device"}
     return ms, min(times), kernels
 
 

@@ -1,25 +1,29 @@
-// One-token (decode) routed-MoE layer: four launches, no host round trip.
+// One-token (decode) routed-MoE layer: four launches on the caller's stream and two
+// on a side stream, no host round trip.
 //
-//   front    router logits (896 BF16 rows), shared-expert gate/up rows (Q8), one
-//            warp per weight row in the reference reduction order, and the
-//            token's two-term E4M3 form; the last block to finish routes the
-//            token (sigmoid + bias top-k) and applies the shared activation
+//   front    router logits (one 256-thread block per BF16 row, the reference's
+//            reduction order) and the token's two-term E4M3 form; the last block
+//            to finish routes the token (sigmoid + bias top-k).  On shapes the
+//            block-scaled expert kernels do not take it also carries the shared
+//            expert's gate/up rows and activation.
 //   gate/up  the top_k selected experts' gate and up rows + activation
 //   down     the selected experts' down rows
-//   tail     the shared expert's down rows (Q8) fused with the weighted sum in
-//            rank order (one block per output column)
+//   combine  weighted sum in rank order + shared output
+// and, on a low-priority side stream next to them (it depends only on the token):
+//   shared gate/up, shared activation + down (Q8 rows on mma.sync)
 //
 // It replaces the per-token sequence of the reference's decode_routed_layer
 // (k3_engine.cu:1554-1563 router, :1668-1689 static projections, :1032-1066
 // launch_expert x 16, :1851-1897 tail), which needs three host synchronisations
 // and ~70 launches per layer.
 //
-// The expert kernels are persistent: a CTA stages the activation vector(s) in
-// shared memory once (as f16 after an exact power-of-two rescale), then each
-// warp streams whole 16-row blocks of MXFP4 weights over the full K extent with
-// a three-deep register prefetch, converts nibbles to f16 with byte-permute
-// lookups and accumulates per 32-column scale group on mma.sync (see
-// k3_gemv.cuh for the fragment layout).  No cross-warp reduction is needed.
+// The expert kernels of the main path are the block-scaled tensor-core kernels of
+// k3_decode_mx.cu.  The ones in this file serve the remaining shapes: persistent,
+// a CTA stages the activation vector(s) in shared memory once (as f16 after an
+// exact power-of-two rescale), then each warp streams whole 16-row blocks of
+// MXFP4 weights over the full K extent with a three-deep register prefetch,
+// converts nibbles to f16 with byte-permute lookups and accumulates per 32-column
+// scale group on mma.sync (see k3_gemv.cuh for the fragment layout).
 #include "k3_gemv.cuh"
 #include "k3_grouped.h"
 #include "k3_rowdot.cuh"
@@ -53,6 +57,7 @@ struct DecodeArgs {
     uint32_t skip_shared;     // down kernel: the shared expert's rows are computed elsewhere
     uint8_t *x_hl, *x_sf;     // front: two-term E4M3 form of x ([2, hidden], [hidden/32]) or null
     unsigned int *ticket;     // front: completion counter of this call
+    uint32_t shared_elsewhere;  // front: the shared expert runs in its own kernels (side stream)
 };
 
 // ------------------------------------------------------------------- front
@@ -89,7 +94,8 @@ K3_DEVINL void split_block(float val, uint8_t &hi, uint8_t &lo, uint8_t &scale_b
 // E4M3 form.  The last block to finish then routes the token (sigmoid + bias
 // top-k in the reference's order: larger choice first, lower expert id on ties)
 // and applies the shared expert's activation.
-__global__ void __launch_bounds__(256, 2)
+template <bool kWithShared>
+__global__ void __launch_bounds__(256, kWithShared ? 2 : 4)
 decode_front_kernel(DecodeArgs a) {
     extern __shared__ __align__(16) unsigned char front_smem[];
     float *xf = reinterpret_cast<float *>(front_smem);                       // [hidden] as fp32
@@ -104,9 +110,13 @@ decode_front_kernel(DecodeArgs a) {
     const uint32_t E = a.d.expert_count, S = a.d.shared_hidden, H = a.d.hidden, k = a.d.top_k;
     const uint32_t split_tasks = a.x_hl ? (H / 32u + 7u) / 8u : 0u;        // 8 blocks (one per warp) each
     for (uint32_t i = threadIdx.x; i < H; i += blockDim.x) xf[i] = bf16_bits_to_float(a.x[i]);
-    stage_vectors_f16(xh, inv_scale, a.x, nullptr, H, H, stage_scratch);     // ends with a block barrier
+    if (kWithShared) {
+        stage_vectors_f16(xh, inv_scale, a.x, nullptr, H, H, stage_scratch);     // ends with a block barrier
+    } else {
+        __syncthreads();
+    }
     // tasks: router rows one at a time, then blocks of 16 gate / up rows
-    const uint32_t groups = 2u * S / 16u;
+    const uint32_t groups = kWithShared ? 2u * S / 16u : 0u;
     const uint32_t tasks_total = E + groups + split_tasks;
     // The extra last block of the grid takes no tasks: it runs the routing code once
     // on stale data without storing anything, so that those instructions are already
@@ -120,7 +130,7 @@ decode_front_kernel(DecodeArgs a) {
             bf16_block_load(p, (const uint16_t *)a.d.router_weight + (uint64_t)task * H, H);
             const float v = block_tree_256(bf16_block_lane_sum(p, xf, H), red);
             if (threadIdx.x == 0) a.logits[task] = v;
-        } else if (task < E + groups) {
+        } else if (kWithShared && task < E + groups) {
             // 16 gate or up rows on the tensor-core Q8 scheme, the K extent split over the 8 warps
             const uint32_t r0 = (task - E) * 16u;                     // S % 16 == 0
             const bool up = r0 >= S;
@@ -247,7 +257,7 @@ decode_front_kernel(DecodeArgs a) {
             a.ids[lane] = top_id[lane];
             a.weights[lane] = __fmul_rn(__fdiv_rn(top_score[lane], denominator), a.d.route_scale);
         }
-    } else {
+    } else if (kWithShared) {
         for (uint32_t i = threadIdx.x - kWarp; i < S; i += blockDim.x - kWarp) {
             const uint16_t bits =
                 float_to_bf16_bits(activation(bf16_bits_to_float(__ldcg(a.sh_gate + i)),
@@ -425,51 +435,74 @@ decode_down_kernel(DecodeArgs a) {
     }
 }
 
-// ------------------------------------------------------------------- tail
-// One 128-thread block per 16 output columns: the shared expert's down rows (Q8 on
-// the tensor-core scheme, K split over the 4 warps) and the weighted sum of the
-// selected experts' rows in rank order,
-//   out[c] = bf16( bf16(sum_r w[r] * rows[r][c]) + shared_down[c] ).
-__global__ void __launch_bounds__(128, 4)
-decode_tail_kernel(DecodeArgs a, uint16_t *__restrict__ out) {
+// ---------------------------------------------------- shared expert, on its own
+// The shared expert depends only on the token, not on the routing: these two
+// kernels run on a side stream next to the front and expert kernels.
+
+// gate and up rows: one 256-thread block per 16 rows, K split over the 8 warps
+__global__ void __launch_bounds__(256, 2)
+decode_shared_gateup_kernel(DecodeArgs a) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
-    __half *act_h = reinterpret_cast<__half *>(smem_raw);                   // [2][S] f16, rescaled
-    __shared__ float terms[32][16], w_s[32], part[4][16];
-    __shared__ float inv_scale[2], stage_scratch[2 * 4];
-    const uint32_t H = a.d.hidden, S = a.d.shared_hidden, k = a.d.top_k;
+    __half *xh = reinterpret_cast<__half *>(smem_raw);                       // [2][hidden] f16, rescaled
+    __shared__ float inv_scale[2], stage_scratch[2 * 8], part[8][16];
     const uint32_t warp = threadIdx.x / kWarp, lane = threadIdx.x % kWarp;
-    if (S != 0u) stage_vectors_f16(act_h, inv_scale, a.sh_act, nullptr, S, S, stage_scratch);
-    if (threadIdx.x < k) w_s[threadIdx.x] = a.weights[threadIdx.x];
-    for (uint32_t c0 = blockIdx.x * 16u; c0 < H; c0 += gridDim.x * 16u) {           // H % 16 == 0
-        // experts' values of these columns: thread (rank, column)
-        for (uint32_t i = threadIdx.x; i < k * 16u; i += blockDim.x) {
-            const uint32_t r = i / 16u, j = i % 16u;
-            terms[r][j] = bf16_bits_to_float(a.rows_out[(uint64_t)r * H + c0 + j]);
-        }
-        if (S != 0u) {
-            const uint32_t steps = S / 128u, per = (steps + 3u) / 4u;
-            float p0, p1;
-            q8_rows16_partial<2>(p0, p1, (const int8_t *)a.d.shared_down_q, a.d.shared_down_s,
-                                 a.d.q8_scale_type, a.d.q8_block, c0, S, min(steps, warp * per),
-                                 min(steps, (warp + 1u) * per), act_h);
-            if ((lane & 3u) == 0u) {
-                part[warp][lane >> 2] = p0;
-                part[warp][(lane >> 2) + 8u] = p1;
-            }
+    const uint32_t S = a.d.shared_hidden, H = a.d.hidden;
+    stage_vectors_f16(xh, inv_scale, a.x, nullptr, H, H, stage_scratch);
+    const uint32_t steps = H / 128u, per = (steps + 7u) / 8u;
+    for (uint32_t task = blockIdx.x; task < 2u * S / 16u; task += gridDim.x) {
+        const uint32_t r0 = task * 16u;
+        const bool up = r0 >= S;
+        const uint32_t row0 = up ? r0 - S : r0;
+        float p0, p1;
+        q8_rows16_partial<3>(p0, p1, (const int8_t *)(up ? a.d.shared_up_q : a.d.shared_gate_q),
+                             up ? a.d.shared_up_s : a.d.shared_gate_s, a.d.q8_scale_type, a.d.q8_block, row0, H,
+                             min(steps, warp * per), min(steps, (warp + 1u) * per), xh);
+        if ((lane & 3u) == 0u) {
+            part[warp][lane >> 2] = p0;
+            part[warp][(lane >> 2) + 8u] = p1;
         }
         __syncthreads();
         if (threadIdx.x < 16u) {
-            float acc = 0.f;
-            for (uint32_t r = 0; r < k; r++) acc = fmaf(w_s[r], terms[r][threadIdx.x], acc);
-            uint32_t bits = float_to_bf16_bits(acc);
-            if (S != 0u) {
-                float v = 0.f;
+            float v = 0.f;
 #pragma unroll
-                for (int w = 0; w < 4; w++) v += part[w][threadIdx.x];
-                bits = float_to_bf16_bits(bf16_bits_to_float(bits) +
-                                          bf16_bits_to_float(float_to_bf16_bits(v * inv_scale[0])));
-            }
-            out[c0 + threadIdx.x] = (uint16_t)bits;
+            for (int w = 0; w < 8; w++) v += part[w][threadIdx.x];
+            (up ? a.sh_up : a.sh_gate)[row0 + threadIdx.x] = float_to_bf16_bits(v * inv_scale[0]);
+        }
+        __syncthreads();
+    }
+}
+
+// activation of (gate, up) and the down rows: one 128-thread block per 16 rows
+__global__ void __launch_bounds__(128, 4)
+decode_shared_down_kernel(DecodeArgs a) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    __half *act_h = reinterpret_cast<__half *>(smem_raw);                   // [2][S] f16, rescaled
+    uint16_t *act_b = reinterpret_cast<uint16_t *>(smem_raw + (size_t)a.d.shared_hidden * 4u);   // [S] bf16
+    __shared__ float part[4][16];
+    __shared__ float inv_scale[2], stage_scratch[2 * 4];
+    const uint32_t H = a.d.hidden, S = a.d.shared_hidden;
+    const uint32_t warp = threadIdx.x / kWarp, lane = threadIdx.x % kWarp;
+    for (uint32_t i = threadIdx.x; i < S; i += blockDim.x) {
+        act_b[i] = float_to_bf16_bits(activation(bf16_bits_to_float(a.sh_gate[i]), bf16_bits_to_float(a.sh_up[i]),
+                                                 a.d.activation, a.d.beta, a.d.linear_beta));
+    }
+    __syncthreads();
+    stage_vectors_f16(act_h, inv_scale, act_b, nullptr, S, S, stage_scratch);
+    const uint32_t steps = S / 128u, per = (steps + 3u) / 4u;
+    for (uint32_t c0 = blockIdx.x * 16u; c0 < H; c0 += gridDim.x * 16u) {           // H % 16 == 0
+        float p0, p1;
+        q8_rows16_partial<2>(p0, p1, (const int8_t *)a.d.shared_down_q, a.d.shared_down_s, a.d.q8_scale_type,
+                             a.d.q8_block, c0, S, min(steps, warp * per), min(steps, (warp + 1u) * per), act_h);
+        if ((lane & 3u) == 0u) {
+            part[warp][lane >> 2] = p0;
+            part[warp][(lane >> 2) + 8u] = p1;
+        }
+        __syncthreads();
+        if (threadIdx.x < 16u) {
+            float v = 0.f;
+#pragma unroll
+            for (int w = 0; w < 4; w++) v += part[w][threadIdx.x];
+            a.sh_out[c0 + threadIdx.x] = float_to_bf16_bits(v * inv_scale[0]);
         }
         __syncthreads();
     }
@@ -492,6 +525,36 @@ bool set_smem(const void *kernel, size_t smem) {
     }
     done[key] = smem;
     return true;
+}
+
+// One side stream and a fork / join event pair per device, created on first use
+// (the one allocation-like step of the one-token path; never destroyed).
+struct SideStream {
+    cudaStream_t stream;
+    cudaEvent_t fork, join;
+};
+
+SideStream *side_stream() {
+    static std::mutex lock;
+    static std::map<int, SideStream> made;
+    int device = 0;
+    (void)cudaGetDevice(&device);
+    std::lock_guard<std::mutex> guard(lock);
+    auto it = made.find(device);
+    if (it != made.end()) return &it->second;
+    SideStream s{};
+    int least = 0, greatest = 0;
+    if (cudaDeviceGetStreamPriorityRange(&least, &greatest) != cudaSuccess) {
+        (void)cudaGetLastError();
+        return nullptr;
+    }
+    if (cudaStreamCreateWithPriority(&s.stream, cudaStreamNonBlocking, least) != cudaSuccess ||
+        cudaEventCreateWithFlags(&s.fork, cudaEventDisableTiming) != cudaSuccess ||
+        cudaEventCreateWithFlags(&s.join, cudaEventDisableTiming) != cudaSuccess) {
+        (void)cudaGetLastError();
+        return nullptr;
+    }
+    return &made.emplace(device, s).first->second;
 }
 
 }  // namespace
@@ -553,22 +616,64 @@ bool k3_decode_layer(const k3_moe_layer_desc *d, const void *x, void *logits, vo
         }
     }
     a.ticket = tickets + next_ticket.fetch_add(1u) % kTicketSlots;
-    const uint32_t front_tasks = d->expert_count + 2u * d->shared_hidden / 16u +
+    // Block-scaled path: the shared expert runs on a side stream next to everything
+    // that depends on the routing, and joins before the combine.
+    SideStream *side = nullptr;
+    if (mx && d->shared_hidden != 0) {
+        side = side_stream();
+        if (!side) return false;
+        a.shared_elsewhere = 1u;
+        // the side stream may start once everything queued before this call is done
+        if (cudaEventRecord(side->fork, stream) != cudaSuccess) {
+            (void)cudaGetLastError();
+            return false;
+        }
+    }
+    const uint32_t front_tasks = d->expert_count + (side ? 0u : 2u * d->shared_hidden / 16u) +
                                  (mx ? (d->hidden / 32u + 7u) / 8u : 0u);
     const size_t front_smem = (size_t)d->hidden * 8u;      // fp32 copy + two f16 slots (the second stays zero)
-    if (!set_smem((const void *)decode_front_kernel, front_smem)) return false;
-    decode_front_kernel<<<std::min<uint32_t>(front_tasks, (uint32_t)sms * 2u - 1u) + 1u, 256, front_smem, stream>>>(a);
-    if (!launch_ok() || !mark(1) || !mark(2)) return false;
+    if (side) {
+        if (!set_smem((const void *)decode_front_kernel<false>, front_smem)) return false;
+        decode_front_kernel<false><<<std::min<uint32_t>(front_tasks, (uint32_t)sms * 4u - 1u) + 1u, 256, front_smem,
+                                     stream>>>(a);
+    } else {
+        if (!set_smem((const void *)decode_front_kernel<true>, front_smem)) return false;
+        decode_front_kernel<true><<<std::min<uint32_t>(front_tasks, (uint32_t)sms * 2u - 1u) + 1u, 256, front_smem,
+                                    stream>>>(a);
+    }
+    if (!launch_ok()) return false;
+    if (side) {
+        // launched after the front kernel so that its blocks are placed first; the side
+        // stream has the lowest priority and fills what the critical path leaves free
+        if (cudaStreamWaitEvent(side->stream, side->fork, 0) != cudaSuccess) {
+            (void)cudaGetLastError();
+            return false;
+        }
+        const size_t gu_smem = (size_t)d->hidden * 4u;
+        const size_t dn_smem = (size_t)d->shared_hidden * 6u;
+        if (!set_smem((const void *)decode_shared_gateup_kernel, gu_smem) ||
+            !set_smem((const void *)decode_shared_down_kernel, dn_smem)) {
+            return false;
+        }
+        decode_shared_gateup_kernel<<<2u * d->shared_hidden / 16u, 256, gu_smem, side->stream>>>(a);
+        decode_shared_down_kernel<<<d->hidden / 16u, 128, dn_smem, side->stream>>>(a);
+        if (!launch_ok() || cudaEventRecord(side->join, side->stream) != cudaSuccess) {
+            (void)cudaGetLastError();
+            return false;
+        }
+    }
+    if (!mark(1) || !mark(2)) return false;
     if (mx) {
         if (!k3_decode_mx_experts(d, ids, act, rows_out, scratch, events ? events[3] : nullptr, stream) ||
             !mark(4)) {
             return false;
         }
-        const size_t tail_smem = (size_t)d->shared_hidden * 4u;   // two f16 slots (the second stays zero)
-        if (!set_smem((const void *)decode_tail_kernel, tail_smem)) return false;
-        decode_tail_kernel<<<std::min<uint32_t>(d->hidden / 16u, (uint32_t)sms * 4u), 128, tail_smem, stream>>>(
-            a, (uint16_t *)out);
-        return launch_ok();
+        if (side && cudaStreamWaitEvent(stream, side->join, 0) != cudaSuccess) {
+            (void)cudaGetLastError();
+            return false;
+        }
+        return k3_moe_combine(out, rows_out, nullptr, weights, d->shared_hidden ? sh_out : nullptr, 1u, d->top_k,
+                              d->hidden, stream);
     }
     size_t smem = (size_t)2 * d->hidden * sizeof(__half) + (2 + 2 * kDecodeWarps) * sizeof(float);
     if (!set_smem((const void *)decode_gateup_kernel, smem)) return false;
