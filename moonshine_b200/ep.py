@@ -9,18 +9,21 @@ exchange step each way:
   1. route + dispatch on the source: rows sorted (expert asc, route asc); the
      rows for destination g are one contiguous slice because experts are
      contiguous per rank;
-  2. all-to-all of the per-destination row counts, of the rows' expert ids, and
-     of the bf16 rows themselves (``all_to_all_single`` with uneven splits);
-  3. on the destination a second dispatch (one "route" per received row) orders
-     the rows (expert asc, source rank asc, route asc) - with the contiguous
-     token partition this is exactly the single-GPU grouping order - and the
-     grouped expert products run on the local shard;
+  2. one all-gather of every rank's per-expert row counts (the only host read of
+     the pass: it gives each rank its send and receive splits and the layout of
+     what it will receive), then the all-to-all of the bf16 rows themselves
+     (``all_to_all_single`` with uneven splits);
+  3. on the destination the received rows (source rank asc, expert asc, route asc)
+     are regrouped (expert asc, source rank asc, route asc) - with the contiguous
+     token partition this is exactly the single-GPU grouping order - through a
+     gather index built from the count matrix, folded into the grouped expert
+     products on the local shard;
   4. rows go back through the inverse permutation and the reverse all-to-all;
   5. combine on the source in rank order (same arithmetic as one GPU).
 
 The arithmetic is delegated to a *backend*: ``NativeBackend`` calls the CUDA
 library; tests pass a CPU backend to exercise this file's exchange logic with
-``gloo`` ranks.  No collective is used beyond the all-to-alls above.
+``gloo`` ranks.  No collective is used beyond the all-gather and the two all-to-alls above.
 """
 from __future__ import annotations
 
@@ -91,18 +94,24 @@ class NativeBackend:
             raise RuntimeError("k3_rocm_gather_rows_bf16 failed")
         return out
 
-    def experts(self, rows, offsets_local):
-        n, d, i = rows.shape[0], self.cfg["hidden"], self.cfg["expert_hidden"]
+    def experts(self, rows, offsets_local, index):
+        """Expert products of rows[index] (grouped by local expert as offsets_local says)."""
+        n, d, i = index.numel(), self.cfg["hidden"], self.cfg["expert_hidden"]
         out = self._buf("eo", (n, d), rows.dtype)
         act = self._buf("ea", (n, i), rows.dtype)
         if not n:
             return out
-        # block-scaled path when the shape allows it (needs scratch), else the bf16 one
-        need = ops.k3_moe_experts_workspace_bytes(self.layer.desc, n, 0)
-        ws = self._buf("ews", (max(need, 1),), torch.uint8)
-        if not ops.k3_moe_experts_grouped_ws(self.layer.desc, out, act, rows, None, 0, offsets_local, n,
-                                             ws if need else None, need):
-            raise RuntimeError("k3_moe_experts_grouped_ws failed")
+        # block-scaled path (gather folded into the row conversion) when the shape allows it
+        need = ops.k3_moe_experts_workspace_bytes(self.layer.desc, n, rows.shape[0])
+        if need:
+            ws = self._buf("ews", (need,), torch.uint8)
+            ok = ops.k3_moe_experts_grouped_ws(self.layer.desc, out, None, rows, index, rows.shape[0],
+                                               offsets_local, n, ws, need)
+        else:
+            ok = ops.k3_moe_experts_grouped(self.layer.desc, out, act, self.gather(rows, index, "rows_in"),
+                                            offsets_local, n)
+        if not ok:
+            raise RuntimeError("grouped expert products failed")
         return out
 
     def shared(self, x):
@@ -130,6 +139,25 @@ class NativeBackend:
         return out
 
 
+def exchange_plan(all_counts: torch.Tensor, rank: int, first: int, per: int):
+    """From the [world, E] matrix of rows each rank routes to each expert (host tensor):
+    the all-to-all splits of this rank and, for the rows it receives (ordered source
+    rank asc, expert asc, route asc), the gather index that regroups them (expert asc,
+    source rank asc, route asc) with the local expert offsets [per + 1]."""
+    world = all_counts.shape[0]
+    own = all_counts[rank].reshape(world, -1).sum(dim=1)
+    send = [int(v) for v in own]
+    mine = all_counts[:, first:first + per]                        # [source, local expert]
+    recv = [int(v) for v in mine.sum(dim=1)]
+    src_base = torch.cumsum(mine.sum(dim=1), 0) - mine.sum(dim=1)  # first received row of each source
+    within = torch.cumsum(mine, 1) - mine                          # offset of an expert inside a source's rows
+    starts = (src_base[:, None] + within).t().reshape(-1)          # [expert, source] blocks of received rows
+    lengths = mine.t().reshape(-1)
+    offsets_local = torch.zeros(per + 1, dtype=torch.int64)
+    offsets_local[1:] = torch.cumsum(mine.sum(dim=0), 0)
+    return send, recv, starts, lengths, offsets_local
+
+
 def ep_forward(backend, x, cfg: dict, group=None, timings: dict | None = None):
     """One expert-parallel layer pass for this rank's rows ``x`` [T_local, d]
     (2-byte elements: bf16, or int16 bit patterns on a CPU backend)."""
@@ -138,31 +166,34 @@ def ep_forward(backend, x, cfg: dict, group=None, timings: dict | None = None):
     e, k = cfg["experts"], cfg["top_k"]
     first, per = shard_range(e, world, rank)
     t_local = x.shape[0]
+    dev = x.device
 
     ids, weights = backend.route(x)
     shared = backend.shared(x)
     offsets, sorted_route, sorted_token, inv_perm = backend.dispatch(ids, t_local, k, e, "src")
-    rows_send = backend.gather(x, sorted_token, "rows_send")
-    ids_sorted = ids.reshape(-1)[sorted_route.long()].contiguous()
+    rows_send = backend.gather(x, sorted_token, "rows_send")     # (expert asc, route asc): contiguous per destination
 
-    send = destination_splits(offsets, e, world)                 # host sync: G+1 integers
-    send_t = torch.tensor(send, dtype=torch.int64, device=x.device)
-    recv_t = torch.empty_like(send_t)
-    dist.all_to_all_single(recv_t, send_t, group=group)
-    recv = [int(v) for v in recv_t.cpu()]
+    # one collective and one host read tell every rank who sends how many rows of which expert
+    counts = (offsets[1:] - offsets[:-1]).to(torch.int64)
+    gathered = [torch.empty_like(counts) for _ in range(world)]
+    dist.all_gather(gathered, counts, group=group)
+    all_counts = torch.stack(gathered).cpu()
+    send, recv, starts, lengths, offsets_local = exchange_plan(all_counts, rank, first, per)
     n_recv = sum(recv)
 
-    ids_recv = torch.empty(n_recv, dtype=ids_sorted.dtype, device=x.device)
-    dist.all_to_all_single(ids_recv, ids_sorted, recv, send, group=group)
-    rows_recv = torch.empty((n_recv, x.shape[1]), dtype=x.dtype, device=x.device)
+    rows_recv = torch.empty((n_recv, x.shape[1]), dtype=x.dtype, device=dev)
     dist.all_to_all_single(rows_recv.view(torch.uint8), rows_send.view(torch.uint8), recv, send, group=group)
 
     if n_recv:
-        local_ids = (ids_recv - first).contiguous()
-        off_l, order, _unused, inv_l = backend.dispatch(local_ids, n_recv, 1, per, "dst")
-        rows_in = backend.gather(rows_recv, order, "rows_in")     # (expert, source rank, route) order
-        rows_out = backend.experts(rows_in, off_l)
-        rows_back = backend.gather(rows_out, inv_l, "rows_back")  # received order again
+        # gather index from the received order to the grouped order, built from the block table
+        starts_d, lengths_d = starts.to(dev), lengths.to(dev)
+        dest_base = torch.cumsum(lengths_d, 0) - lengths_d
+        order = (torch.repeat_interleave(starts_d - dest_base, lengths_d, output_size=n_recv)
+                 + torch.arange(n_recv, device=dev)).to(torch.int32)
+        inverse = torch.empty_like(order)
+        inverse[order.long()] = torch.arange(n_recv, device=dev, dtype=torch.int32)
+        rows_out = backend.experts(rows_recv, offsets_local.to(torch.int32).to(dev), order)
+        rows_back = backend.gather(rows_out, inverse, "rows_back")   # received order again
     else:
         rows_back = rows_recv
     rows_home = torch.empty_like(rows_send)

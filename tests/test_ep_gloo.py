@@ -42,10 +42,10 @@ class OracleBackend:
     def gather(self, rows, index, tag):
         return rows[index.long()].contiguous()
 
-    def experts(self, rows, offsets_local):
+    def experts(self, rows, offsets_local, index):
         o, c, w = self.o, self.cfg, self.w
         off = offsets_local.numpy()
-        x = self._u16(rows)
+        x = self._u16(rows[index.long()].contiguous())
         out = np.zeros_like(x)
         for le in range(self.per):
             lo, hi = int(off[le]), int(off[le + 1])
@@ -114,6 +114,19 @@ def test_two_rank_expert_parallel_equals_single_process(mode, oracle):
         results = manager.dict()
         mp.spawn(_worker, args=(world, port, mode, results), nprocs=world, join=True)
         assert dict(results) == {0: True, 1: True}
+
+
+def test_exchange_plan():
+    from moonshine_b200 import ep
+    # 2 ranks, 4 experts (2 per rank); counts[source, expert]
+    counts = torch.tensor([[3, 0, 2, 1], [1, 2, 0, 4]], dtype=torch.int64)
+    send, recv, starts, lengths, off = ep.exchange_plan(counts, 1, 2, 2)       # rank 1 owns experts 2, 3
+    assert send == [3, 4] and recv == [3, 4]
+    # received rows: source 0 -> [e2, e2, e3], source 1 -> [e3 x 4]; grouped: e2 (s0 x2, s1 x0), e3 (s0 x1, s1 x4)
+    assert starts.tolist() == [0, 3, 2, 3] and lengths.tolist() == [2, 0, 1, 4]
+    assert off.tolist() == [0, 2, 7]
+    send, recv, starts, lengths, off = ep.exchange_plan(counts, 0, 0, 2)
+    assert send == [3, 3] and recv == [3, 3] and off.tolist() == [0, 4, 6]
 
 
 def test_destination_splits():
