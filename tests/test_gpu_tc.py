@@ -109,6 +109,7 @@ def test_grouped_expert_products(oracle, counts):
     ([0, 5, 130, 128, 1, 300, 17, 64], True),
     ([33, 0, 0, 0, 0, 0, 0, 0], True),
     ([0, 0, 0, 700, 0, 0, 0, 1], False),
+    ([144, 145, 143, 0, 16, 129, 272, 273], False),         # around the 128 + 16 row tile limit
 ])
 def test_grouped_expert_products_block_scaled(oracle, counts, gathered):
     """Block-scaled tensor-core path (packed E2M1 weights and E8M0 scales consumed
