@@ -226,10 +226,10 @@ class ExpertParallelLayer:
         orig = self.backend.experts
         spans = []
 
-        def timed(rows, offsets_local):
+        def timed(*args):
             a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             a.record()
-            r = orig(rows, offsets_local)
+            r = orig(*args)
             b.record()
             spans.append((a, b))
             return r
