@@ -382,13 +382,39 @@ def run_native(args):
             dist.destroy_process_group()
         return
 
-    # ---- end to end: pinned host input -> device -> layer -> pinned host output
+    # ---- end to end: pinned host input -> device -> layer -> pinned host output, every
+    # step.  The three legs of consecutive steps overlap as in a serving loop: step i+1's
+    # input is copied while step i computes and step i-1's output goes back; two buffers
+    # per direction, ordering by events, all of it inside the timed region.
+    copy_in, copy_out = torch.cuda.Stream(device), torch.cuda.Stream(device)
+    main = torch.cuda.current_stream(device)
+    x_in = [x_dev, torch.empty_like(x_dev)]
+    out_hosts = [out_host, torch.empty_like(out_host).pin_memory()]
+    in_ready = [torch.cuda.Event() for _ in range(args.steps)]
+    computed = [torch.cuda.Event() for _ in range(args.steps)]
+    returned = [torch.cuda.Event() for _ in range(args.steps)]
     barrier()
     start.record()
-    for _ in range(args.steps):
-        x_dev.copy_(x_host, non_blocking=True)
-        out = layer.forward(x_dev)
-        out_host.copy_(out, non_blocking=True)
+    copy_in.wait_stream(main)
+    copy_out.wait_stream(main)
+    for i in range(args.steps):
+        with torch.cuda.stream(copy_in):
+            if i >= 2:
+                copy_in.wait_event(computed[i - 2])          # the buffer's previous reader is done
+            x_in[i % 2].copy_(x_host, non_blocking=True)
+            in_ready[i].record(copy_in)
+        main.wait_event(in_ready[i])
+        out = layer.forward(x_in[i % 2])
+        computed[i].record(main)
+        with torch.cuda.stream(copy_out):
+            copy_out.wait_event(computed[i])
+            if i >= 2:
+                copy_out.wait_event(returned[i - 2])
+            out.record_stream(copy_out)
+            out_hosts[i % 2].copy_(out, non_blocking=True)
+            returned[i].record(copy_out)
+    main.wait_stream(copy_out)
+    main.wait_stream(copy_in)
     stop.record()
     barrier()
     e2e_ms = start.elapsed_time(stop)
