@@ -219,7 +219,7 @@ def run_reference(args):
 
 
 # DRAM bytes per launch measured with ncu on these workloads (one-pass metrics,
-# profiles/dram_traffic_full_size.md): prefill = gate/up (28.81 GB) + down (11.73 GB)
+# summary kept under profiles/): prefill = gate/up (28.81 GB) + down (11.73 GB)
 # launches of the grouped expert phase; decode = the four kernels of one token.
 PREFILL_TRAFFIC_BYTES = 40.54e9
 DECODE_TRAFFIC_BYTES = 434.8e6
@@ -444,7 +444,7 @@ def run_native(args):
                         "unit": "TFLOP/s", "frac": achieved / peaks["bf16_tflops_sustained"],
                         "traffic": PREFILL_TRAFFIC_BYTES if args.workload == "prefill8k" and world == 1 else None,
                         "traffic_note": "DRAM read+write of the two grouped GEMM launches, ncu one-pass capture "
-                                        "of this workload (profiles/dram_traffic_full_size.md); algorithmic 26.2 GB",
+                                        "of this workload (summary under profiles/); algorithmic 26.2 GB",
                         "peak_source": peaks["source"] + " bf16 sustained",
                         "launch_ms": experts_ms,
                         "hbm_floor_gbs": weight_bytes / (experts_ms * 1e-3) / 1e9}

@@ -43,7 +43,7 @@ def main():
         rel = float(np.sqrt(((g - r) ** 2).sum() / (r ** 2).sum()))
         verdicts.append((bias_mode, same_ids, bool(np.array_equal(got, want)), rel))
     ok = all(v[1] and v[3] <= 1e-3 for v in verdicts)
-    print(f"EP_VERDICT rank={rank} ok={ok} {verdicts}", flush=True)
+    print(f"EP_RESULT rank={rank} ok={ok} {verdicts}", flush=True)
     dist.barrier()
     dist.destroy_process_group()
     sys.exit(0 if ok else 1)

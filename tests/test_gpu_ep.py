@@ -21,6 +21,6 @@ def test_two_gpu_expert_parallel_matches_single_gpu():
            "--master-addr", "127.0.0.1", "--master-port", "29711",
            os.path.join(ROOT, "tests", "ep_gpu_worker.py")]
     res = subprocess.run(cmd, capture_output=True, text=True, timeout=600, cwd=ROOT)
-    lines = [l for l in res.stdout.splitlines() if l.startswith("EP_VERDICT")]
+    lines = [l for l in res.stdout.splitlines() if l.startswith("EP_RESULT")]
     assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-2000:]
     assert len(lines) == 2 and all("ok=True" in l for l in lines), lines
