@@ -168,6 +168,14 @@ bool k3_moe_combine(void *out, const void *rows, const void *index,
                     const void *weights, const void *shared, uint32_t tokens,
                     uint32_t top_k, uint32_t hidden, void *stream);
 
+/* The same with a residual row added last: out = bf16(residual + bf16(routed +
+ * shared)), the two adds of k3_engine.cu:1889-1897 inside the combine kernel.
+ * `residual` bf16 [tokens, d] may be NULL. */
+bool k3_moe_combine_residual(void *out, const void *rows, const void *index,
+                             const void *weights, const void *shared,
+                             const void *residual, uint32_t tokens,
+                             uint32_t top_k, uint32_t hidden, void *stream);
+
 /* Whole layer on one GPU holding every expert (local range == all experts):
  * x bf16 [tokens, d] -> out bf16 [tokens, d].  `workspace` must hold
  * k3_moe_layer_workspace_bytes(desc, tokens).  When ids_out / weights_out are
@@ -188,6 +196,16 @@ bool k3_moe_layer_forward_events(const k3_moe_layer_desc *desc, void *out,
                                  const void *x, uint32_t tokens,
                                  void *workspace, size_t workspace_bytes,
                                  void *const *events, void *stream);
+
+/* The layer with the step either side of it: out = hidden_in + moe(rms_norm(hidden_in)).
+ * The post-attention RMSNorm (k3_engine.cu:1550-1553) runs first and feeds router,
+ * shared expert and experts; the residual add (k3_engine.cu:1889-1897) happens in
+ * the combine kernel.  hidden_in bf16 [tokens, d], norm_weight bf16 [d]. */
+size_t k3_moe_block_workspace_bytes(const k3_moe_layer_desc *desc, uint32_t tokens);
+bool k3_moe_block_forward(const k3_moe_layer_desc *desc, void *out,
+                          const void *hidden_in, const void *norm_weight,
+                          float epsilon, uint32_t tokens, void *workspace,
+                          size_t workspace_bytes, void *stream);
 
 /* The routed layer at the model's real shape, where the experts work on a
  * latent vector narrower than the model width (k3: hidden 7168, latent 3584):

@@ -86,6 +86,9 @@ SIGNATURES = {
     "k3_moe_combine": (C.c_bool, [vp, vp, vp, vp, vp, u32, u32, u32, vp]),
     "k3_moe_latent_workspace_bytes": (sz, [_LP, u32]),
     "k3_moe_latent_layer_forward": (C.c_bool, [_LP, vp, vp, u32, vp, sz, vp, vp, vp]),
+    "k3_moe_combine_residual": (C.c_bool, [vp, vp, vp, vp, vp, vp, u32, u32, u32, vp]),
+    "k3_moe_block_workspace_bytes": (sz, [_DP, u32]),
+    "k3_moe_block_forward": (C.c_bool, [_DP, vp, vp, vp, f32, u32, vp, sz, vp]),
     "k3_moe_layer_forward": (C.c_bool, [_DP, vp, vp, u32, vp, sz, vp, vp, vp]),
     "k3_moe_layer_forward_events": (C.c_bool, [_DP, vp, vp, u32, vp, sz, C.POINTER(vp), vp]),
     "k3_moe_device_status": (u32, []),

@@ -571,8 +571,8 @@ bool k3_decode_supported(const k3_moe_layer_desc *d) {
 // buffers: see DecodeArgs; all caller-owned scratch carved from the layer workspace
 bool k3_decode_layer(const k3_moe_layer_desc *d, const void *x, void *logits, void *ids,
                      void *weights, void *sh_gate, void *sh_up, void *sh_act, void *sh_out,
-                     void *act, void *rows_out, void *out, void *scratch, size_t scratch_bytes,
-                     void *const *events, cudaStream_t stream) {
+                     void *act, void *rows_out, void *out, const void *residual, void *scratch,
+                     size_t scratch_bytes, void *const *events, cudaStream_t stream) {
     // optional phase events: [1], [2] after the front kernel, [3] after gate/up,
     // [4] after down (the caller records [0] before and [5] after the call)
     auto mark = [&](int index) {
@@ -672,8 +672,8 @@ bool k3_decode_layer(const k3_moe_layer_desc *d, const void *x, void *logits, vo
             (void)cudaGetLastError();
             return false;
         }
-        return k3_moe_combine(out, rows_out, nullptr, weights, d->shared_hidden ? sh_out : nullptr, 1u, d->top_k,
-                              d->hidden, stream);
+        return k3_moe_combine_residual(out, rows_out, nullptr, weights, d->shared_hidden ? sh_out : nullptr,
+                                       residual, 1u, d->top_k, d->hidden, stream);
     }
     size_t smem = (size_t)2 * d->hidden * sizeof(__half) + (2 + 2 * kDecodeWarps) * sizeof(float);
     if (!set_smem((const void *)decode_gateup_kernel, smem)) return false;
@@ -683,6 +683,6 @@ bool k3_decode_layer(const k3_moe_layer_desc *d, const void *x, void *logits, vo
     if (!set_smem((const void *)decode_down_kernel, smem)) return false;
     decode_down_kernel<<<sms, kDecodeThreads, smem, stream>>>(a);
     if (!launch_ok() || !mark(4)) return false;
-    return k3_moe_combine(out, rows_out, nullptr, weights, d->shared_hidden ? sh_out : nullptr, 1u,
-                          d->top_k, d->hidden, stream);
+    return k3_moe_combine_residual(out, rows_out, nullptr, weights, d->shared_hidden ? sh_out : nullptr,
+                                   residual, 1u, d->top_k, d->hidden, stream);
 }

@@ -40,13 +40,14 @@ bool k3_grouped_tc_experts(const k3_moe_layer_desc *desc, void *rows_out, void *
                            const void *rows_in, const void *offsets, uint32_t rows, void *stream);
 
 // One-token layer on persistent matrix-vector kernels (router, routing, expert
-// gate/up/down, shared expert and the weighted combine into `out` bf16 [hidden]).
+// gate/up/down, shared expert and the weighted combine into `out` bf16 [hidden],
+// plus `residual` bf16 [hidden] when it is not null).
 // All other buffers are caller-owned scratch.
 bool k3_decode_supported(const k3_moe_layer_desc *desc);
 bool k3_decode_layer(const k3_moe_layer_desc *desc, const void *x, void *logits, void *ids,
                      void *weights, void *sh_gate, void *sh_up, void *sh_act, void *sh_out,
-                     void *act, void *rows_out, void *out, void *scratch, size_t scratch_bytes,
-                     void *const *events, cudaStream_t stream);
+                     void *act, void *rows_out, void *out, const void *residual, void *scratch,
+                     size_t scratch_bytes, void *const *events, cudaStream_t stream);
 
 // Block-scaled tensor-core expert products for one token (k3_decode_mx.cu).
 bool k3_decode_mx_supported(const k3_moe_layer_desc *desc);

@@ -94,12 +94,13 @@ grouped_rows_kernel(uint16_t *__restrict__ out, const uint16_t *__restrict__ in,
     }
 }
 
-// out[t] = bf16( bf16(sum_r w[t,r] * rows[idx[t,r]]) + shared[t] )
+// out[t] = bf16( bf16( bf16(sum_r w[t,r] * rows[idx[t,r]]) + shared[t] ) + residual[t] )
+// (shared and residual optional)
 __global__ void __launch_bounds__(256)
 combine_kernel(uint16_t *__restrict__ out, const uint16_t *__restrict__ rows,
                const uint32_t *__restrict__ index, const float *__restrict__ weights,
-               const uint16_t *__restrict__ shared, uint32_t tokens, uint32_t top_k,
-               uint32_t hidden) {
+               const uint16_t *__restrict__ shared, const uint16_t *__restrict__ residual,
+               uint32_t tokens, uint32_t top_k, uint32_t hidden) {
     __shared__ float w_s[32];
     __shared__ uint32_t idx_s[32];
     for (uint32_t token = blockIdx.x; token < tokens; token += gridDim.x) {
@@ -132,6 +133,11 @@ combine_kernel(uint16_t *__restrict__ out, const uint16_t *__restrict__ rows,
                 sh[0] = bf16_lo(q.x); sh[1] = bf16_hi(q.x); sh[2] = bf16_lo(q.y); sh[3] = bf16_hi(q.y);
                 sh[4] = bf16_lo(q.z); sh[5] = bf16_hi(q.z); sh[6] = bf16_lo(q.w); sh[7] = bf16_hi(q.w);
             }
+            uint32_t res[4] = {0u, 0u, 0u, 0u};
+            if (residual) {
+                const uint4 q = reinterpret_cast<const uint4 *>(residual + (uint64_t)token * hidden)[c];
+                res[0] = q.x; res[1] = q.y; res[2] = q.z; res[3] = q.w;
+            }
             uint32_t r4[4];
 #pragma unroll
             for (int j = 0; j < 4; j++) {
@@ -140,6 +146,10 @@ combine_kernel(uint16_t *__restrict__ out, const uint16_t *__restrict__ rows,
                 if (shared) {
                     lo = float_to_bf16_bits(bf16_bits_to_float(lo) + sh[2 * j]);
                     hi = float_to_bf16_bits(bf16_bits_to_float(hi) + sh[2 * j + 1]);
+                }
+                if (residual) {
+                    lo = float_to_bf16_bits(bf16_lo(res[j]) + bf16_bits_to_float(lo));
+                    hi = float_to_bf16_bits(bf16_hi(res[j]) + bf16_bits_to_float(hi));
                 }
                 r4[j] = lo | (hi << 16);
             }
@@ -388,14 +398,14 @@ extern "C" bool k3_moe_shared_expert_ws(const k3_moe_layer_desc *d, void *out, v
     return k3_grouped_shared_expert(d, out, act, x, tokens, workspace, (cudaStream_t)stream);
 }
 
-extern "C" bool k3_moe_combine(void *out, const void *rows, const void *index,
-                               const void *weights, const void *shared, uint32_t tokens,
-                               uint32_t top_k, uint32_t hidden, void *stream) {
+extern "C" bool k3_moe_combine_residual(void *out, const void *rows, const void *index,
+                                        const void *weights, const void *shared, const void *residual,
+                                        uint32_t tokens, uint32_t top_k, uint32_t hidden, void *stream) {
     if (!out || !rows || !weights || tokens == 0 || top_k == 0 || top_k > 32u || hidden == 0 ||
         hidden % 8u != 0) {
         return false;
     }
-    if ((((uintptr_t)out | (uintptr_t)rows | (uintptr_t)shared) & 15u) != 0) return false;
+    if ((((uintptr_t)out | (uintptr_t)rows | (uintptr_t)shared | (uintptr_t)residual) & 15u) != 0) return false;
     // few tokens: spread the columns of a token over several small CTAs
     const bool few = tokens < 128u;
     const uint32_t threads = few ? 64u : 256u;
@@ -403,8 +413,14 @@ extern "C" bool k3_moe_combine(void *out, const void *rows, const void *index,
                     few ? (hidden / 8u + threads - 1u) / threads : 1u);
     combine_kernel<<<grid, threads, 0, (cudaStream_t)stream>>>(
         (uint16_t *)out, (const uint16_t *)rows, (const uint32_t *)index, (const float *)weights,
-        (const uint16_t *)shared, tokens, top_k, hidden);
+        (const uint16_t *)shared, (const uint16_t *)residual, tokens, top_k, hidden);
     return launch_ok();
+}
+
+extern "C" bool k3_moe_combine(void *out, const void *rows, const void *index, const void *weights,
+                               const void *shared, uint32_t tokens, uint32_t top_k, uint32_t hidden,
+                               void *stream) {
+    return k3_moe_combine_residual(out, rows, index, weights, shared, nullptr, tokens, top_k, hidden, stream);
 }
 
 namespace {
@@ -416,7 +432,8 @@ bool mark(void *const *events, int index, cudaStream_t stream) {
 
 bool layer_forward_impl(const k3_moe_layer_desc *d, void *out, const void *x, uint32_t tokens,
                         void *workspace, size_t workspace_bytes, void *ids_out,
-                        void *weights_out, void *const *events, void *stream_pointer) {
+                        void *weights_out, void *const *events, const void *residual,
+                        void *stream_pointer) {
     if (!desc_ok(d) || !out || !x || tokens == 0 || tokens > 65535u || !workspace ||
         d->local_expert_first != 0 || d->local_expert_count != d->expert_count ||
         !slot_pointers_aligned(d)) {
@@ -435,7 +452,7 @@ bool layer_forward_impl(const k3_moe_layer_desc *d, void *out, const void *x, ui
         // combine is part of the sequence
         // (phase events there: front | gate/up | down | tail)
         if (!k3_decode_layer(d, x, w.logits, w.ids, w.weights, w.sh_gate, w.sh_up, w.sh_act,
-                             w.sh_out, w.act, w.rows_out, out, w.rows_in,
+                             w.sh_out, w.act, w.rows_out, out, residual, w.rows_in,
                              (size_t)routes * d->hidden * 2u, events, stream)) {
             return false;
         }
@@ -481,8 +498,8 @@ bool layer_forward_impl(const k3_moe_layer_desc *d, void *out, const void *x, ui
     }
     if (!one_token && !mark(events, 4, stream)) return false;
     if (!one_token &&
-        !k3_moe_combine(out, w.rows_out, index, w.weights, d->shared_hidden ? w.sh_out : nullptr,
-                        tokens, d->top_k, d->hidden, stream)) {
+        !k3_moe_combine_residual(out, w.rows_out, index, w.weights, d->shared_hidden ? w.sh_out : nullptr,
+                                 residual, tokens, d->top_k, d->hidden, stream)) {
         return false;
     }
     if (!mark(events, 5, stream)) return false;
@@ -503,7 +520,7 @@ extern "C" bool k3_moe_layer_forward(const k3_moe_layer_desc *d, void *out, cons
                                      uint32_t tokens, void *workspace, size_t workspace_bytes,
                                      void *ids_out, void *weights_out, void *stream) {
     return layer_forward_impl(d, out, x, tokens, workspace, workspace_bytes, ids_out, weights_out,
-                              nullptr, stream);
+                              nullptr, nullptr, stream);
 }
 
 extern "C" bool k3_moe_layer_forward_events(const k3_moe_layer_desc *d, void *out, const void *x,
@@ -511,7 +528,32 @@ extern "C" bool k3_moe_layer_forward_events(const k3_moe_layer_desc *d, void *ou
                                             size_t workspace_bytes, void *const *events,
                                             void *stream) {
     return layer_forward_impl(d, out, x, tokens, workspace, workspace_bytes, nullptr, nullptr,
-                              events, stream);
+                              events, nullptr, stream);
+}
+
+// The layer with the step either side of it: post-attention RMSNorm in front (its
+// output feeds router, shared expert and experts) and the residual add behind, the
+// latter inside the combine kernel.  (k3_engine.cu:1550-1553 norm, :1889-1897 adds.)
+extern "C" size_t k3_moe_block_workspace_bytes(const k3_moe_layer_desc *d, uint32_t tokens) {
+    const size_t inner = k3_moe_layer_workspace_bytes(d, tokens);
+    return inner ? inner + align_up((size_t)tokens * d->hidden * 2u, 256) + 256u : 0;
+}
+
+extern "C" bool k3_moe_block_forward(const k3_moe_layer_desc *d, void *out, const void *hidden_in,
+                                     const void *norm_weight, float epsilon, uint32_t tokens,
+                                     void *workspace, size_t workspace_bytes, void *stream) {
+    if (!desc_ok(d) || !out || !hidden_in || !norm_weight || !workspace || tokens == 0 || !(epsilon > 0.0f)) {
+        return false;
+    }
+    const size_t need = k3_moe_block_workspace_bytes(d, tokens);
+    if (need == 0 || workspace_bytes < need) return false;
+    char *base = (char *)(((uintptr_t)workspace + 255u) & ~(uintptr_t)255u);
+    void *normed = base;
+    char *inner = base + align_up((size_t)tokens * d->hidden * 2u, 256);
+    const size_t inner_bytes = workspace_bytes - (size_t)(inner - (char *)workspace);
+    return k3_rocm_rms_norm_bf16(normed, hidden_in, norm_weight, tokens, d->hidden, epsilon, stream) &&
+           layer_forward_impl(d, out, normed, tokens, inner, inner_bytes, nullptr, nullptr, nullptr, hidden_in,
+                              stream);
 }
 
 // Thin wrappers so a host language without CUDA runtime bindings can own the

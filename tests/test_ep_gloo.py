@@ -106,10 +106,9 @@ def _worker(rank, world, port, mode, results):
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("mode", ["balanced", "rank1_idle"])
-def test_two_rank_expert_parallel_equals_single_process(mode, oracle):
-    world = 2
-    port = 29600 + (os.getpid() % 200) + (0 if mode == "balanced" else 1)
+@pytest.mark.parametrize("mode,world", [("balanced", 2), ("rank1_idle", 2), ("balanced", 4)])
+def test_expert_parallel_ranks_equal_single_process(mode, world, oracle):
+    port = 29600 + (os.getpid() % 200) + (0 if mode == "balanced" else 1) + 2 * world
     with mp.Manager() as manager:
         results = manager.dict()
         mp.spawn(_worker, args=(world, port, mode, results), nprocs=world, join=True)
