@@ -66,6 +66,16 @@ class NativeBackend:
             self._bufs[name] = t
         return t[:n].view(*shape)
 
+    def exchange_resources(self, world, experts):
+        """Side stream, pinned host buffer and event for the count exchange (made once)."""
+        r = getattr(self, "_exchange", None)
+        if r is None:
+            r = (torch.cuda.Stream(self.device),
+                 torch.empty((world, experts), dtype=torch.int64).pin_memory(),
+                 torch.cuda.Event())
+            self._exchange = r
+        return r
+
     def route(self, x):
         t, k, e = x.shape[0], self.cfg["top_k"], self.cfg["experts"]
         ids = self._buf("ids", (t, k), torch.int32)
@@ -169,15 +179,33 @@ def ep_forward(backend, x, cfg: dict, group=None, timings: dict | None = None):
     dev = x.device
 
     ids, weights = backend.route(x)
-    shared = backend.shared(x)
     offsets, sorted_route, sorted_token, inv_perm = backend.dispatch(ids, t_local, k, e, "src")
-    rows_send = backend.gather(x, sorted_token, "rows_send")     # (expert asc, route asc): contiguous per destination
 
-    # one collective and one host read tell every rank who sends how many rows of which expert
+    # One collective and one host read tell every rank who sends how many rows of which
+    # expert.  On a GPU the exchange runs on a side stream and the host reads it only after
+    # the shared expert and the row gather have been queued, so the device stays busy
+    # while the host waits and plans.
     counts = (offsets[1:] - offsets[:-1]).to(torch.int64)
-    gathered = [torch.empty_like(counts) for _ in range(world)]
-    dist.all_gather(gathered, counts, group=group)
-    all_counts = torch.stack(gathered).cpu()
+    if x.is_cuda:
+        main = torch.cuda.current_stream(dev)
+        side, pinned, done = backend.exchange_resources(world, e)
+        side.wait_stream(main)
+        with torch.cuda.stream(side):
+            counts.record_stream(side)
+            gathered = [torch.empty_like(counts) for _ in range(world)]
+            dist.all_gather(gathered, counts, group=group)
+            pinned.copy_(torch.stack(gathered), non_blocking=True)
+            done.record(side)
+        shared = backend.shared(x)
+        rows_send = backend.gather(x, sorted_token, "rows_send")
+        done.synchronize()
+        all_counts = pinned.clone()
+    else:
+        gathered = [torch.empty_like(counts) for _ in range(world)]
+        dist.all_gather(gathered, counts, group=group)
+        all_counts = torch.stack(gathered).cpu()
+        shared = backend.shared(x)
+        rows_send = backend.gather(x, sorted_token, "rows_send")  # (expert asc, route asc): contiguous per destination
     send, recv, starts, lengths, offsets_local = exchange_plan(all_counts, rank, first, per)
     n_recv = sum(recv)
 

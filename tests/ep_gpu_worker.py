@@ -43,10 +43,16 @@ def main():
         rel = float(np.sqrt(((g - r) ** 2).sum() / (r ** 2).sum()))
         verdicts.append((bias_mode, same_ids, bool(np.array_equal(got, want)), rel))
     ok = all(v[1] and v[3] <= 1e-3 for v in verdicts)
-    print(f"EP_RESULT rank={rank} ok={ok} {verdicts}", flush=True)
+    sys.stderr.write(f"rank {rank}: {verdicts}\n")
+    # one verdict line for the whole job (lines of several ranks could interleave)
+    flag = torch.tensor([1 if ok else 0], device=device)
+    dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+    all_ok = bool(flag.item())
+    if rank == 0:
+        print(f"EP_RESULT ranks={world} ok={all_ok}", flush=True)
     dist.barrier()
     dist.destroy_process_group()
-    sys.exit(0 if ok else 1)
+    sys.exit(0 if all_ok else 1)
 
 
 if __name__ == "__main__":

@@ -23,4 +23,4 @@ def test_two_gpu_expert_parallel_matches_single_gpu():
     res = subprocess.run(cmd, capture_output=True, text=True, timeout=600, cwd=ROOT)
     lines = [l for l in res.stdout.splitlines() if l.startswith("EP_RESULT")]
     assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-2000:]
-    assert len(lines) == 2 and all("ok=True" in l for l in lines), lines
+    assert len(lines) == 1 and "ok=True" in lines[0], (lines, res.stderr[-2000:])
