@@ -39,8 +39,37 @@ class LatentDesc(C.Structure):
 
 _LP = C.POINTER(LatentDesc)
 
+
+
+class SlotAccess(C.Structure):
+    """Mirror of ``k3_moe_slot_access`` (include/k3_moe_store.h)."""
+    _fields_ = [("hit", C.c_bool), ("admit", C.c_bool), ("source_slot", u32), ("destination_slot", u32)]
+
+
+class SlotStats(C.Structure):
+    """Mirror of ``k3_moe_slot_stats`` (include/k3_moe_store.h)."""
+    _fields_ = [("batches", u64), ("accesses", u64), ("hits", u64), ("misses", u64),
+                ("admissions", u64), ("evictions", u64)]
+
+
+u16 = C.c_uint16
+_U16P, _U32P = C.POINTER(u16), C.POINTER(u32)
+
 # name -> (restype, argtypes)
 SIGNATURES = {
+    # slot policy of the partially resident expert store (host code)
+    "k3_moe_slot_cache_create": (C.c_bool, [C.POINTER(vp), u16, u16, C.c_char_p, sz]),
+    "k3_moe_slot_cache_plan": (C.c_bool, [vp, u16, _U16P, u16, C.POINTER(SlotAccess), C.c_char_p, sz]),
+    "k3_moe_slot_cache_commit": (C.c_bool, [vp, u16, C.c_char_p, sz]),
+    "k3_moe_slot_cache_abort": (None, [vp, u16]),
+    "k3_moe_slot_cache_slot_count": (u32, [vp]),
+    "k3_moe_slot_cache_storage_bytes": (u64, [vp, u64]),
+    "k3_moe_slot_cache_get_stats": (None, [vp, C.POINTER(SlotStats)]),
+    "k3_moe_slot_cache_snapshot_layer": (C.c_bool, [vp, u16, _U16P, u16, _U16P, C.c_char_p, sz]),
+    "k3_moe_slot_cache_reset": (C.c_bool, [vp, C.c_char_p, sz]),
+    "k3_moe_slot_cache_invalidate_slots": (C.c_bool, [vp, u32, u32, C.c_char_p, sz]),
+    "k3_moe_slot_cache_destroy": (None, [vp]),
+    "k3_moe_slot_cache_replay_line": (C.c_bool, [vp, u16, _U16P, u16, _U32P, _U32P, C.c_char_p, sz]),
     # legacy operator interface
     "k3_rocm_situ_bf16": (C.c_bool, [vp, vp, vp, u64, f32, f32, vp]),
     "k3_rocm_mxfp4_gemv_bf16": (C.c_bool, [vp, vp, vp, vp, u32, u32, vp]),

@@ -109,7 +109,19 @@ decode_front_kernel(DecodeArgs a) {
     const uint32_t warp = threadIdx.x / kWarp, lane = threadIdx.x % kWarp;
     const uint32_t E = a.d.expert_count, S = a.d.shared_hidden, H = a.d.hidden, k = a.d.top_k;
     const uint32_t split_tasks = a.x_hl ? (H / 32u + 7u) / 8u : 0u;        // 8 blocks (one per warp) each
-    for (uint32_t i = threadIdx.x; i < H; i += blockDim.x) xf[i] = bf16_bits_to_float(a.x[i]);
+    if ((reinterpret_cast<uintptr_t>(a.x) & 15u) == 0u && H % 8u == 0u) {
+        // 16 bytes per load: the whole token is in flight after at most four loads per thread
+        for (uint32_t i = threadIdx.x; i < H / 8u; i += blockDim.x) {
+            const uint4 v = __ldg(reinterpret_cast<const uint4 *>(a.x) + i);
+            float4 *dst = reinterpret_cast<float4 *>(xf + 8u * i);
+            dst[0] = make_float4(__uint_as_float(v.x << 16), __uint_as_float(v.x & 0xffff0000u),
+                                 __uint_as_float(v.y << 16), __uint_as_float(v.y & 0xffff0000u));
+            dst[1] = make_float4(__uint_as_float(v.z << 16), __uint_as_float(v.z & 0xffff0000u),
+                                 __uint_as_float(v.w << 16), __uint_as_float(v.w & 0xffff0000u));
+        }
+    } else {
+        for (uint32_t i = threadIdx.x; i < H; i += blockDim.x) xf[i] = bf16_bits_to_float(a.x[i]);
+    }
     if (kWithShared) {
         stage_vectors_f16(xh, inv_scale, a.x, nullptr, H, H, stage_scratch);     // ends with a block barrier
     } else {
