@@ -229,7 +229,7 @@ DECODE_TRAFFIC_BYTES = 434.8e6
 def launches_per_step(tokens: int, shared: bool) -> int:
     """Kernels of this library one layer pass launches (baseline shapes)."""
     if tokens == 1:
-        return 6                                   # front, gate/up, down, combine + shared gate/up, shared down
+        return 5                                   # front, gate/up, down (+ combine) + shared gate/up, shared down
     route, shared_k, dispatch, combine = 2, (5 if shared else 0), 3, 1
     experts = 1 + 3 + 2                            # row split, 3 gathers, gate/up and down GEMMs
     return route + shared_k + dispatch + experts + combine

@@ -1,4 +1,4 @@
-// One-token (decode) routed-MoE layer: four launches on the caller's stream and two
+// One-token (decode) routed-MoE layer: three launches on the caller's stream and two
 // on a side stream, no host round trip.
 //
 //   front    router logits (one 256-thread block per BF16 row, the reference's
@@ -8,9 +8,12 @@
 //            expert's gate/up rows and activation.
 //   gate/up  the top_k selected experts' gate and up rows + activation
 //   down     the selected experts' down rows
-//   combine  weighted sum in rank order + shared output
 // and, on a low-priority side stream next to them (it depends only on the token):
 //   shared gate/up, shared activation + down (Q8 rows on mma.sync)
+// The weighted sum in rank order + shared output + residual has no launch of its
+// own: the producers of its inputs (down epilogue warps, shared-down blocks) count
+// arrivals per 32 output columns and the last one forms them (k3_decode_tail.cuh).
+// With an expert-parallel shard (not every expert local) a combine launch follows.
 //
 // It replaces the per-token sequence of the reference's decode_routed_layer
 // (k3_engine.cu:1554-1563 router, :1668-1689 static projections, :1032-1066
@@ -24,6 +27,7 @@
 // MXFP4 weights over the full K extent with a three-deep register prefetch,
 // converts nibbles to f16 with byte-permute lookups and accumulates per 32-column
 // scale group on mma.sync (see k3_gemv.cuh for the fragment layout).
+#include "k3_decode_tail.cuh"
 #include "k3_gemv.cuh"
 #include "k3_grouped.h"
 #include "k3_rowdot.cuh"
@@ -58,6 +62,7 @@ struct DecodeArgs {
     uint8_t *x_hl, *x_sf;     // front: two-term E4M3 form of x ([2, hidden], [hidden/32]) or null
     unsigned int *ticket;     // front: completion counter of this call
     uint32_t shared_elsewhere;  // front: the shared expert runs in its own kernels (side stream)
+    DecodeTail tail;            // shared down: its share of the layer's tail (tail.out null: none)
 };
 
 // ------------------------------------------------------------------- front
@@ -67,6 +72,7 @@ struct DecodeArgs {
 // kTicketSlots of them are in flight.
 constexpr uint32_t kTicketSlots = 64;
 __device__ unsigned int g_front_tickets[kTicketSlots];
+__device__ uint32_t g_decode_status = 0;     // set when an arrival count of the tail did not go through
 
 // float -> unsigned key with the same order (-0 is folded into +0 first)
 K3_DEVINL uint32_t order_key(float f) {
@@ -516,9 +522,21 @@ decode_shared_down_kernel(DecodeArgs a) {
             for (int w = 0; w < 4; w++) v += part[w][threadIdx.x];
             a.sh_out[c0 + threadIdx.x] = float_to_bf16_bits(v * inv_scale[0]);
         }
+        // these 16 columns are one of the inputs of their 32-column group of the layer output
+        if (warp == 0 && a.tail.out != nullptr && !tail_arrive(a.tail, c0 / 32u, lane)) g_decode_status = 1u;
         __syncthreads();
     }
 }
+
+}  // namespace
+
+uint32_t k3_decode_status() {
+    uint32_t v = 0xffffffffu;
+    if (cudaMemcpyFromSymbol(&v, g_decode_status, sizeof(v)) != cudaSuccess) (void)cudaGetLastError();
+    return v;
+}
+
+namespace {
 
 // (attribute changes are remembered per kernel: the call costs microseconds of host time)
 bool set_smem(const void *kernel, size_t smem) {
@@ -629,7 +647,24 @@ bool k3_decode_layer(const k3_moe_layer_desc *d, const void *x, void *logits, vo
     }
     a.ticket = tickets + next_ticket.fetch_add(1u) % kTicketSlots;
     // Block-scaled path: the shared expert runs on a side stream next to everything
-    // that depends on the routing, and joins before the combine.
+    // that depends on the routing.  With every expert in this table there is no
+    // combine launch either: the down kernel's epilogue warps and the shared-down
+    // blocks count arrivals per 32 output columns and the last one adds them up.
+    const bool fused_tail = mx && d->local_expert_first == 0u && d->local_expert_count == d->expert_count &&
+                            d->hidden % 32u == 0u;
+    static std::atomic<uint32_t> tail_epoch{1};
+    if (fused_tail) {
+        a.tail.out = (uint16_t *)out;
+        a.tail.rows = (const uint16_t *)rows_out;
+        a.tail.weights = (const float *)weights;
+        a.tail.shared = d->shared_hidden ? (const uint16_t *)sh_out : nullptr;
+        a.tail.residual = (const uint16_t *)residual;
+        a.tail.count = (uint32_t *)k3_decode_mx_tail_words(d, scratch);
+        a.tail.epoch = tail_epoch.fetch_add(1u) & 0xffffffu;
+        a.tail.expected = d->top_k + (d->shared_hidden ? 2u : 0u);     // + two 16-column shared blocks
+        a.tail.ranks = d->top_k;
+        a.tail.hidden = d->hidden;
+    }
     SideStream *side = nullptr;
     if (mx && d->shared_hidden != 0) {
         side = side_stream();
@@ -676,14 +711,18 @@ bool k3_decode_layer(const k3_moe_layer_desc *d, const void *x, void *logits, vo
     }
     if (!mark(1) || !mark(2)) return false;
     if (mx) {
-        if (!k3_decode_mx_experts(d, ids, act, rows_out, scratch, events ? events[3] : nullptr, stream) ||
+        k3_decode_tail tail{out, weights, a.tail.shared, residual, a.tail.epoch, a.tail.expected};
+        if (!k3_decode_mx_experts(d, ids, act, rows_out, scratch, events ? events[3] : nullptr,
+                                  fused_tail ? &tail : nullptr, stream) ||
             !mark(4)) {
             return false;
         }
+        // what follows on the caller's stream also follows the shared expert
         if (side && cudaStreamWaitEvent(stream, side->join, 0) != cudaSuccess) {
             (void)cudaGetLastError();
             return false;
         }
+        if (fused_tail) return true;
         return k3_moe_combine_residual(out, rows_out, nullptr, weights, d->shared_hidden ? sh_out : nullptr,
                                        residual, 1u, d->top_k, d->hidden, stream);
     }

@@ -24,6 +24,7 @@
 //               down next to the routed down), exact reference order, overlapping
 //               the HBM-bound tensor pipeline
 // Every barrier wait is bounded (see k3_tc_ptx.cuh).
+#include "k3_decode_tail.cuh"
 #include "k3_grouped.h"
 #include "k3_rowdot.cuh"
 #include "k3_tc_ptx.cuh"
@@ -33,6 +34,7 @@
 #include <cuda_fp8.h>
 
 #include <algorithm>
+#include <atomic>
 #include <cstring>
 #include <mutex>
 
@@ -108,6 +110,7 @@ struct MxArgs {
     float beta, linear_beta;
     uint8_t *act_hl;            // gate/up: E4M3 split of the produced activation [2*ranks, w_rows]
     uint8_t *act_sf;            //          and its block scales [ranks, w_rows/32]
+    DecodeTail tail;            // down: the layer's tail (tail.out null: none)
     // shared-expert side work (Q8 rows, one warp per row)
     const int8_t *q8_q;
     const void *q8_s;
@@ -392,6 +395,7 @@ decode_mx_kernel(const __grid_constant__ MxMaps maps, MxArgs a) {
                 }
             } else {
                 *dst = float_to_bf16_bits(v0);
+                if (a.tail.out != nullptr && !tail_arrive(a.tail, tile * 4u + quad, lane)) *abort_flag = 1u;
             }
         }
     }
@@ -467,8 +471,9 @@ uint32_t k3_decode_mx_status() {
 }
 
 size_t k3_decode_mx_scratch_bytes(const k3_moe_layer_desc *d) {
+    // token terms and scales, activation terms and scales, arrival words of the tail
     return (size_t)2 * d->hidden + d->hidden / 32u + (size_t)2 * d->top_k * d->expert_hidden +
-           (size_t)d->top_k * d->expert_hidden / 32u + 4u * 256u;
+           (size_t)d->top_k * d->expert_hidden / 32u + (size_t)d->hidden / 32u * 4u + 5u * 256u;
 }
 
 bool k3_decode_mx_supported(const k3_moe_layer_desc *d) {
@@ -485,10 +490,19 @@ void k3_decode_mx_vector_scratch(const k3_moe_layer_desc *d, void *scratch, void
     *x_sf = align(hl + (size_t)2 * d->hidden);
 }
 
+void *k3_decode_mx_tail_words(const k3_moe_layer_desc *d, void *scratch) {
+    auto align = [](uint8_t *p) { return (uint8_t *)(((uintptr_t)p + 255u) & ~(uintptr_t)255u); };
+    uint8_t *x_hl = nullptr, *x_sf = nullptr;
+    k3_decode_mx_vector_scratch(d, scratch, (void **)&x_hl, (void **)&x_sf);
+    uint8_t *a_hl = align(x_sf + d->hidden / 32u);
+    uint8_t *a_sf = align(a_hl + (size_t)2 * d->top_k * d->expert_hidden);
+    return align(a_sf + (size_t)d->top_k * d->expert_hidden / 32u);
+}
+
 // Routed experts of one token: act [top_k, I] and rows_out [top_k, hidden] in rank
 // order (ids on the device) from the token's E4M3 form in `scratch`.
 bool k3_decode_mx_experts(const k3_moe_layer_desc *d, const void *ids, void *act, void *rows_out,
-                          void *scratch, void *between, cudaStream_t stream) {
+                          void *scratch, void *between, const k3_decode_tail *tail, cudaStream_t stream) {
     const uint32_t H = d->hidden, I = d->expert_hidden, k = d->top_k;
     auto align = [](uint8_t *p) { return (uint8_t *)(((uintptr_t)p + 255u) & ~(uintptr_t)255u); };
     uint8_t *x_hl = nullptr, *x_sf = nullptr;
@@ -564,7 +578,20 @@ bool k3_decode_mx_experts(const k3_moe_layer_desc *d, const void *ids, void *act
     decode_mx_kernel<true><<<sms, kThreads, smem, stream>>>(gu, a);
     if (!launch_ok()) return false;
     if (between && cudaEventRecord((cudaEvent_t)between, stream) != cudaSuccess) return false;
-    // down
+    // down (+ its share of the layer's tail)
+    if (tail != nullptr) {
+        if (d->local_expert_first != 0u || d->local_expert_count != d->expert_count) return false;
+        a.tail.out = (uint16_t *)tail->out;
+        a.tail.rows = (const uint16_t *)rows_out;
+        a.tail.weights = (const float *)tail->weights;
+        a.tail.shared = (const uint16_t *)tail->shared;
+        a.tail.residual = (const uint16_t *)tail->residual;
+        a.tail.count = (uint32_t *)k3_decode_mx_tail_words(d, scratch);
+        a.tail.epoch = tail->epoch & 0xffffffu;
+        a.tail.expected = tail->expected;
+        a.tail.ranks = k;
+        a.tail.hidden = H;
+    }
     a.out = (uint16_t *)rows_out;
     a.act_hl = nullptr;
     a.act_sf = nullptr;

@@ -57,9 +57,23 @@ size_t k3_decode_mx_scratch_bytes(const k3_moe_layer_desc *desc);
 void k3_decode_mx_vector_scratch(const k3_moe_layer_desc *desc, void *scratch, void **x_hl, void **x_sf);
 // Expert products of one token from its E4M3 form already in `scratch`;
 // `between` (a CUDA event or null) is recorded between gate/up and down.
+// With `tail` the down kernel's epilogue takes part in the layer's tail
+// (k3_decode_tail.cuh): it counts an arrival per finished row and 32-column group in
+// the words k3_decode_mx_tail_words() returns, and the arrival that completes
+// `expected` forms the output columns.  Requires every selected expert in this table.
+struct k3_decode_tail {
+    void *out;                 // bf16 [hidden]
+    const void *weights;       // f32 [top_k] on the device
+    const void *shared;        // bf16 [hidden] or null
+    const void *residual;      // bf16 [hidden] or null
+    uint32_t epoch;            // unique per layer call (24 bits used)
+    uint32_t expected;         // arrivals per 32-column group
+};
+void *k3_decode_mx_tail_words(const k3_moe_layer_desc *desc, void *scratch);
 bool k3_decode_mx_experts(const k3_moe_layer_desc *desc, const void *ids, void *act, void *rows_out,
-                          void *scratch, void *between, cudaStream_t stream);
+                          void *scratch, void *between, const k3_decode_tail *tail, cudaStream_t stream);
 uint32_t k3_decode_mx_status();
+uint32_t k3_decode_status();
 
 // Block-scaled tensor-core grouped expert products for many rows
 // (k3_grouped_mx.cu).  `index` (u32 per row, or null) gathers rows_in, which then

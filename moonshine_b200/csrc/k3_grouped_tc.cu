@@ -607,7 +607,7 @@ bool tc_shape_ok(uint32_t k, uint32_t rows) {
 extern "C" uint32_t k3_moe_device_status(void) {
     uint32_t v = 0xffffffffu;
     if (cudaMemcpyFromSymbol(&v, g_tc_status, sizeof(v)) != cudaSuccess) (void)cudaGetLastError();
-    return v | k3_decode_mx_status() | k3_grouped_mx_status();
+    return v | k3_decode_mx_status() | k3_decode_status() | k3_grouped_mx_status();
 }
 
 bool k3_grouped_dense_bf16_f32(void *out, const void *weights, const void *x, uint32_t tokens,
