@@ -500,9 +500,21 @@ decode_shared_down_kernel(DecodeArgs a) {
     __shared__ float inv_scale[2], stage_scratch[2 * 4];
     const uint32_t H = a.d.hidden, S = a.d.shared_hidden;
     const uint32_t warp = threadIdx.x / kWarp, lane = threadIdx.x % kWarp;
-    for (uint32_t i = threadIdx.x; i < S; i += blockDim.x) {
-        act_b[i] = float_to_bf16_bits(activation(bf16_bits_to_float(a.sh_gate[i]), bf16_bits_to_float(a.sh_up[i]),
-                                                 a.d.activation, a.d.beta, a.d.linear_beta));
+    // eight elements per 16-byte load (S % 128 == 0), all loads of a thread in flight together
+    for (uint32_t c = threadIdx.x; c < S / 8u; c += blockDim.x) {
+        const uint4 g = reinterpret_cast<const uint4 *>(a.sh_gate)[c], u = reinterpret_cast<const uint4 *>(a.sh_up)[c];
+        const uint32_t gw[4] = {g.x, g.y, g.z, g.w}, uw[4] = {u.x, u.y, u.z, u.w};
+        uint32_t o[4];
+#pragma unroll
+        for (int q = 0; q < 4; q++) {
+            const uint32_t lo = float_to_bf16_bits(activation(__uint_as_float(gw[q] << 16), __uint_as_float(uw[q] << 16),
+                                                              a.d.activation, a.d.beta, a.d.linear_beta));
+            const uint32_t hi = float_to_bf16_bits(activation(__uint_as_float(gw[q] & 0xffff0000u),
+                                                              __uint_as_float(uw[q] & 0xffff0000u), a.d.activation,
+                                                              a.d.beta, a.d.linear_beta));
+            o[q] = lo | (hi << 16);
+        }
+        reinterpret_cast<uint4 *>(act_b)[c] = make_uint4(o[0], o[1], o[2], o[3]);
     }
     __syncthreads();
     stage_vectors_f16(act_h, inv_scale, act_b, nullptr, S, S, stage_scratch);
@@ -678,7 +690,9 @@ bool k3_decode_layer(const k3_moe_layer_desc *d, const void *x, void *logits, vo
     }
     const uint32_t front_tasks = d->expert_count + (side ? 0u : 2u * d->shared_hidden / 16u) +
                                  (mx ? (d->hidden / 32u + 7u) / 8u : 0u);
-    const size_t front_smem = (size_t)d->hidden * 8u;      // fp32 copy + two f16 slots (the second stays zero)
+    // fp32 copy of the token; with the shared rows in the kernel also two f16 slots (the
+    // second stays zero).  Without them four blocks fit on an SM and the grid is one wave.
+    const size_t front_smem = (size_t)d->hidden * (side ? 4u : 8u);
     if (side) {
         if (!set_smem((const void *)decode_front_kernel<false>, front_smem)) return false;
         decode_front_kernel<false><<<std::min<uint32_t>(front_tasks, (uint32_t)sms * 4u - 1u) + 1u, 256, front_smem,

@@ -71,6 +71,68 @@ K3_DEVINL void stage_vectors_f16(__half *xs, float *inv_scale, const uint16_t *x
     const uint32_t nthreads = blockDim.x;
     const uint16_t *src[2] = {x0, x1};
     float mx[2] = {0.f, 0.f};
+    // Fast path, same arithmetic: every thread fetches its share with 16-byte loads
+    // that are all in flight at once and converts from registers, instead of two
+    // passes of 2-byte loads that each wait a memory round trip per few elements.
+    const uint32_t chunks = k / 8u;
+    if (k == k_pad && k % 8u == 0u && chunks <= 4u * nthreads &&
+        ((reinterpret_cast<uintptr_t>(x0) | reinterpret_cast<uintptr_t>(x1)) & 15u) == 0u) {
+        uint4 held[2][4];
+#pragma unroll
+        for (int v = 0; v < 2; v++) {
+            if (src[v] == nullptr) continue;
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                const uint32_t c = tid + (uint32_t)j * nthreads;
+                held[v][j] = c < chunks ? reinterpret_cast<const uint4 *>(src[v])[c] : make_uint4(0u, 0u, 0u, 0u);
+            }
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                const uint32_t w[4] = {held[v][j].x, held[v][j].y, held[v][j].z, held[v][j].w};
+#pragma unroll
+                for (int q = 0; q < 4; q++) {
+                    mx[v] = fmaxf(mx[v], fabsf(__uint_as_float(w[q] << 16)));
+                    mx[v] = fmaxf(mx[v], fabsf(__uint_as_float(w[q] & 0xffff0000u)));
+                }
+            }
+            mx[v] = warp_max(mx[v]);
+            if ((tid % kWarp) == 0) scratch[v * (nthreads / kWarp) + tid / kWarp] = mx[v];
+        }
+        __syncthreads();
+#pragma unroll
+        for (int v = 0; v < 2; v++) {
+            float m = 0.f;
+            for (uint32_t w = 0; w < nthreads / kWarp; w++) m = fmaxf(m, scratch[v * (nthreads / kWarp) + w]);
+            int e = 0;
+            if (m > 0.f && m <= 3.0e38f) {
+                e = (int)((__float_as_uint(m) >> 23) & 0xffu) - 127 - 14;
+                e = max(-100, min(100, e));
+            }
+            const float mul = __uint_as_float((uint32_t)(127 - e) << 23);   // 2^-e
+            if (tid == 0) inv_scale[v] = __uint_as_float((uint32_t)(127 + e) << 23);  // 2^e
+            uint4 *dst = reinterpret_cast<uint4 *>(xs + (size_t)v * k_pad);
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                const uint32_t c = tid + (uint32_t)j * nthreads;
+                if (c >= chunks) continue;
+                uint4 o = make_uint4(0u, 0u, 0u, 0u);
+                if (src[v] != nullptr) {
+                    const uint32_t w[4] = {held[v][j].x, held[v][j].y, held[v][j].z, held[v][j].w};
+                    uint32_t h[4];
+#pragma unroll
+                    for (int q = 0; q < 4; q++) {
+                        const __half2 p = __floats2half2_rn(__uint_as_float(w[q] << 16) * mul,
+                                                            __uint_as_float(w[q] & 0xffff0000u) * mul);
+                        h[q] = *reinterpret_cast<const uint32_t *>(&p);
+                    }
+                    o = make_uint4(h[0], h[1], h[2], h[3]);
+                }
+                dst[c] = o;
+            }
+        }
+        __syncthreads();
+        return;
+    }
 #pragma unroll
     for (int v = 0; v < 2; v++) {
         if (src[v] == nullptr) continue;
