@@ -60,6 +60,7 @@ struct DecodeArgs {
     uint16_t *rows_out;       // [top_k, hidden]
     uint32_t skip_shared;     // down kernel: the shared expert's rows are computed elsewhere
     uint8_t *x_hl, *x_sf;     // front: two-term E4M3 form of x ([2, hidden], [hidden/32]) or null
+    float *route_words;       // front: [2][1024] scores and choices written by the row tasks, or null
     unsigned int *ticket;     // front: completion counter of this call
     uint32_t shared_elsewhere;  // front: the shared expert runs in its own kernels (side stream)
     DecodeTail tail;            // shared down: its share of the layer's tail (tail.out null: none)
@@ -144,10 +145,21 @@ decode_front_kernel(DecodeArgs a) {
     const uint32_t workers = gridDim.x - 1u;
     for (uint32_t task = blockIdx.x; !warmer && task < tasks_total; task += workers) {
         if (task < E) {
+            // the row's bias is fetched with the row, so the routing step finds score and
+            // choice ready instead of starting from the logits
+            float bias = 0.f;
+            if (threadIdx.x == 0 && a.route_words != nullptr) bias = __ldg((const float *)a.d.router_bias + task);
             Bf16RowLoad p;
             bf16_block_load(p, (const uint16_t *)a.d.router_weight + (uint64_t)task * H, H);
             const float v = block_tree_256(bf16_block_lane_sum(p, xf, H), red);
-            if (threadIdx.x == 0) a.logits[task] = v;
+            if (threadIdx.x == 0) {
+                a.logits[task] = v;
+                if (a.route_words != nullptr) {
+                    const float sc = sigmoid_exact(v);
+                    a.route_words[task] = sc;
+                    a.route_words[1024u + task] = sc + bias;
+                }
+            }
         } else if (kWithShared && task < E + groups) {
             // 16 gate or up rows on the tensor-core Q8 scheme, the K extent split over the 8 warps
             const uint32_t r0 = (task - E) * 16u;                     // S % 16 == 0
@@ -195,14 +207,29 @@ decode_front_kernel(DecodeArgs a) {
     }
     const bool commit = !warmer;
     // ---- routing and shared activation: results of the other blocks come from L2
-    for (uint32_t e = threadIdx.x; e < 1024u; e += blockDim.x) {
-        float sc = 0.f, ch = 0.f;
-        if (e < E) {
-            sc = sigmoid_exact(__ldcg(a.logits + e));
-            ch = sc + ((const float *)a.d.router_bias)[e];
+    if (a.route_words != nullptr) {
+        float sc[4], ch[4];
+#pragma unroll
+        for (uint32_t j = 0; j < 4u; j++) {                 // all eight loads in flight
+            const uint32_t e = threadIdx.x + j * 256u;
+            sc[j] = e < E ? __ldcg(a.route_words + e) : 0.f;
+            ch[j] = e < E ? __ldcg(a.route_words + 1024u + e) : 0.f;
         }
-        score_s[e] = sc;
-        choice_s[e] = ch;
+#pragma unroll
+        for (uint32_t j = 0; j < 4u; j++) {
+            score_s[threadIdx.x + j * 256u] = sc[j];
+            choice_s[threadIdx.x + j * 256u] = ch[j];
+        }
+    } else {
+        for (uint32_t e = threadIdx.x; e < 1024u; e += blockDim.x) {
+            float sc = 0.f, ch = 0.f;
+            if (e < E) {
+                sc = sigmoid_exact(__ldcg(a.logits + e));
+                ch = sc + ((const float *)a.d.router_bias)[e];
+            }
+            score_s[e] = sc;
+            choice_s[e] = ch;
+        }
     }
     __syncthreads();
     // Two levels of arg-max rounds on order keys (0 = none).  Level 1: warp w owns
@@ -636,7 +663,10 @@ bool k3_decode_layer(const k3_moe_layer_desc *d, const void *x, void *logits, vo
     const int sms = sm_count();
     const bool mx = scratch != nullptr && k3_decode_mx_supported(d) && d->top_k < 32u &&
                     scratch_bytes >= k3_decode_mx_scratch_bytes(d);
-    if (mx) k3_decode_mx_vector_scratch(d, scratch, (void **)&a.x_hl, (void **)&a.x_sf);
+    if (mx) {
+        k3_decode_mx_vector_scratch(d, scratch, (void **)&a.x_hl, (void **)&a.x_sf);
+        a.route_words = (float *)k3_decode_mx_route_words(d, scratch);
+    }
     static std::atomic<uint32_t> next_ticket{0};
     // address of the ticket array on the current device (looked up once per device)
     static std::mutex ticket_lock;
@@ -693,19 +723,7 @@ bool k3_decode_layer(const k3_moe_layer_desc *d, const void *x, void *logits, vo
     // fp32 copy of the token; with the shared rows in the kernel also two f16 slots (the
     // second stays zero).  Without them four blocks fit on an SM and the grid is one wave.
     const size_t front_smem = (size_t)d->hidden * (side ? 4u : 8u);
-    if (side) {
-        if (!set_smem((const void *)decode_front_kernel<false>, front_smem)) return false;
-        decode_front_kernel<false><<<std::min<uint32_t>(front_tasks, (uint32_t)sms * 4u - 1u) + 1u, 256, front_smem,
-                                     stream>>>(a);
-    } else {
-        if (!set_smem((const void *)decode_front_kernel<true>, front_smem)) return false;
-        decode_front_kernel<true><<<std::min<uint32_t>(front_tasks, (uint32_t)sms * 2u - 1u) + 1u, 256, front_smem,
-                                    stream>>>(a);
-    }
-    if (!launch_ok()) return false;
-    if (side) {
-        // launched after the front kernel so that its blocks are placed first; the side
-        // stream has the lowest priority and fills what the critical path leaves free
+    auto launch_side = [&]() -> bool {
         if (cudaStreamWaitEvent(side->stream, side->fork, 0) != cudaSuccess) {
             (void)cudaGetLastError();
             return false;
@@ -722,7 +740,21 @@ bool k3_decode_layer(const k3_moe_layer_desc *d, const void *x, void *logits, vo
             (void)cudaGetLastError();
             return false;
         }
+        return true;
+    };
+    if (side) {
+        if (!set_smem((const void *)decode_front_kernel<false>, front_smem)) return false;
+        decode_front_kernel<false><<<std::min<uint32_t>(front_tasks, (uint32_t)sms * 4u - 1u) + 1u, 256, front_smem,
+                                     stream>>>(a);
+    } else {
+        if (!set_smem((const void *)decode_front_kernel<true>, front_smem)) return false;
+        decode_front_kernel<true><<<std::min<uint32_t>(front_tasks, (uint32_t)sms * 2u - 1u) + 1u, 256, front_smem,
+                                    stream>>>(a);
     }
+    if (!launch_ok()) return false;
+    // after the front kernel in launch order (measured: the order makes no difference);
+    // the side stream has the lowest priority and fills what the critical path leaves free
+    if (side && !launch_side()) return false;
     if (!mark(1) || !mark(2)) return false;
     if (mx) {
         k3_decode_tail tail{out, weights, a.tail.shared, residual, a.tail.epoch, a.tail.expected};

@@ -471,9 +471,10 @@ uint32_t k3_decode_mx_status() {
 }
 
 size_t k3_decode_mx_scratch_bytes(const k3_moe_layer_desc *d) {
-    // token terms and scales, activation terms and scales, arrival words of the tail
+    // token terms and scales, activation terms and scales, arrival words of the tail,
+    // scores and choices of the routing step
     return (size_t)2 * d->hidden + d->hidden / 32u + (size_t)2 * d->top_k * d->expert_hidden +
-           (size_t)d->top_k * d->expert_hidden / 32u + (size_t)d->hidden / 32u * 4u + 5u * 256u;
+           (size_t)d->top_k * d->expert_hidden / 32u + (size_t)d->hidden / 32u * 4u + 2u * 1024u * 4u + 6u * 256u;
 }
 
 bool k3_decode_mx_supported(const k3_moe_layer_desc *d) {
@@ -497,6 +498,11 @@ void *k3_decode_mx_tail_words(const k3_moe_layer_desc *d, void *scratch) {
     uint8_t *a_hl = align(x_sf + d->hidden / 32u);
     uint8_t *a_sf = align(a_hl + (size_t)2 * d->top_k * d->expert_hidden);
     return align(a_sf + (size_t)d->top_k * d->expert_hidden / 32u);
+}
+
+void *k3_decode_mx_route_words(const k3_moe_layer_desc *d, void *scratch) {
+    uint8_t *tail = (uint8_t *)k3_decode_mx_tail_words(d, scratch);
+    return (void *)(((uintptr_t)(tail + (size_t)d->hidden / 32u * 4u) + 255u) & ~(uintptr_t)255u);
 }
 
 // Routed experts of one token: act [top_k, I] and rows_out [top_k, hidden] in rank

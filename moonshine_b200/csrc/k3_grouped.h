@@ -70,6 +70,8 @@ struct k3_decode_tail {
     uint32_t expected;         // arrivals per 32-column group
 };
 void *k3_decode_mx_tail_words(const k3_moe_layer_desc *desc, void *scratch);
+// f32 [2][1024] inside `scratch`: sigmoid scores and score + bias per expert (front kernel)
+void *k3_decode_mx_route_words(const k3_moe_layer_desc *desc, void *scratch);
 bool k3_decode_mx_experts(const k3_moe_layer_desc *desc, const void *ids, void *act, void *rows_out,
                           void *scratch, void *between, const k3_decode_tail *tail, cudaStream_t stream);
 uint32_t k3_decode_mx_status();

@@ -178,8 +178,8 @@ struct Workspace {
     uint32_t *offsets, *sorted_route, *sorted_token, *inv_perm;
     void *dispatch_ws;
     size_t dispatch_bytes;
-    void *mx_ws, *sh_ws;
-    size_t mx_bytes, sh_bytes;
+    void *mx_ws, *sh_ws, *decode_ws;
+    size_t mx_bytes, sh_bytes, decode_bytes;
     uint16_t *rows_in, *act, *rows_out, *sh_gate, *sh_up, *sh_act, *sh_out;
     size_t total;
 };
@@ -211,6 +211,8 @@ Workspace carve(const k3_moe_layer_desc *d, uint32_t tokens, void *base) {
     w.mx_ws = take(w.mx_bytes);
     w.sh_bytes = k3_grouped_shared_workspace_bytes(d, tokens);
     w.sh_ws = take(w.sh_bytes);
+    w.decode_bytes = tokens == 1u ? k3_decode_mx_scratch_bytes(d) : 0;
+    w.decode_ws = take(w.decode_bytes);
     if (d->shared_hidden) {
         w.sh_gate = (uint16_t *)take((size_t)tokens * d->shared_hidden * 2u);
         w.sh_up = (uint16_t *)take((size_t)tokens * d->shared_hidden * 2u);
@@ -313,7 +315,9 @@ extern "C" bool k3_moe_store_admit(const k3_moe_layer_desc *d, uint32_t slot, co
 
 extern "C" size_t k3_moe_layer_workspace_bytes(const k3_moe_layer_desc *d, uint32_t tokens) {
     if (!desc_ok(d) || tokens == 0) return 0;
-    return carve(d, tokens, nullptr).total;
+    // a workspace sized for `tokens` also serves any smaller call, the one-token
+    // sequence (which has scratch of its own) included
+    return std::max(carve(d, tokens, nullptr).total, carve(d, 1u, nullptr).total);
 }
 
 extern "C" bool k3_moe_route(const k3_moe_layer_desc *d, void *expert_ids, void *expert_weights,
@@ -452,8 +456,8 @@ bool layer_forward_impl(const k3_moe_layer_desc *d, void *out, const void *x, ui
         // combine is part of the sequence
         // (phase events there: front | gate/up | down | tail)
         if (!k3_decode_layer(d, x, w.logits, w.ids, w.weights, w.sh_gate, w.sh_up, w.sh_act,
-                             w.sh_out, w.act, w.rows_out, out, residual, w.rows_in,
-                             (size_t)routes * d->hidden * 2u, events, stream)) {
+                             w.sh_out, w.act, w.rows_out, out, residual, w.decode_ws, w.decode_bytes,
+                             events, stream)) {
             return false;
         }
     } else {
