@@ -334,7 +334,7 @@ def run_native(args):
         return run_latent(args, cfg, tokens, device, peaks, torch)
     if world > 1:
         from moonshine_b200.ep import ExpertParallelLayer
-        layer = ExpertParallelLayer(cfg, seed=0, device=device, tokens=tokens)
+        layer = ExpertParallelLayer(cfg, seed=0, device=device, tokens=tokens, pieces=args.ep_pieces)
         local_tokens = layer.local_tokens
     else:
         layer = MoELayer(cfg, None, seed=0, device=device, max_tokens=tokens)
@@ -480,7 +480,8 @@ def run_native(args):
             "config": {"workload": args.workload, "tokens": tokens, "experts": cfg["experts"],
                        "top_k": k, "hidden": d, "expert_hidden": cfg["expert_hidden"],
                        "shared_hidden": cfg["shared_hidden"], "router_bias": cfg["bias_mode"],
-                       "parallelism": f"ep{world}" if world > 1 else "single",
+                       "parallelism": (f"ep{world}" + (f" x {args.ep_pieces} pipelined row ranges" if args.ep_pieces > 1 else ""))
+                       if world > 1 else "single",
                        "l2": "inputs larger than L2 (expert weights 20.96 GB per pass)"},
             "e2e": {"value": e2e_value, "unit": UNIT,
                     "h2d_bytes_per_step": local_tokens * d * 2 * world,
@@ -503,6 +504,8 @@ def main():
     ap.add_argument("--impl", default="native", choices=["native", "reference"])
     ap.add_argument("--workload", default="prefill8k", choices=["prefill8k", "prefill512", "decode", "latent8k"])
     ap.add_argument("--lean", action="store_true", help="timed region only (for profiler captures)")
+    ap.add_argument("--ep-pieces", type=int, default=1,
+                    help="expert-parallel runs: row ranges per pass pipelined against each other")
     ap.add_argument("--experts", type=int, default=0, help="override the expert count (profiler captures)")
     ap.add_argument("--tokens", type=int, default=0, help="override the token count (profiler captures)")
     args = ap.parse_args()

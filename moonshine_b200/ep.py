@@ -168,9 +168,11 @@ def exchange_plan(all_counts: torch.Tensor, rank: int, first: int, per: int):
     return send, recv, starts, lengths, offsets_local
 
 
-def ep_forward(backend, x, cfg: dict, group=None, timings: dict | None = None):
-    """One expert-parallel layer pass for this rank's rows ``x`` [T_local, d]
-    (2-byte elements: bf16, or int16 bit patterns on a CPU backend)."""
+def _ep_steps(backend, x, cfg: dict, group):
+    """One expert-parallel pass for the rows ``x`` as a generator: it yields after
+    every point where the host has queued all it can without waiting, so that a
+    driver can advance another pass (on another stream) in the meantime.  The
+    value of the generator (StopIteration.value) is (out, ids, weights)."""
     world = dist.get_world_size(group)
     rank = dist.get_rank(group)
     e, k = cfg["experts"], cfg["top_k"]
@@ -198,6 +200,7 @@ def ep_forward(backend, x, cfg: dict, group=None, timings: dict | None = None):
             done.record(side)
         shared = backend.shared(x)
         rows_send = backend.gather(x, sorted_token, "rows_send")
+        yield
         done.synchronize()
         all_counts = pinned.clone()
     else:
@@ -206,33 +209,106 @@ def ep_forward(backend, x, cfg: dict, group=None, timings: dict | None = None):
         all_counts = torch.stack(gathered).cpu()
         shared = backend.shared(x)
         rows_send = backend.gather(x, sorted_token, "rows_send")  # (expert asc, route asc): contiguous per destination
+        yield
     send, recv, starts, lengths, offsets_local = exchange_plan(all_counts, rank, first, per)
     n_recv = sum(recv)
 
     rows_recv = torch.empty((n_recv, x.shape[1]), dtype=x.dtype, device=dev)
-    dist.all_to_all_single(rows_recv.view(torch.uint8), rows_send.view(torch.uint8), recv, send, group=group)
-
+    arriving = dist.all_to_all_single(rows_recv.view(torch.uint8), rows_send.view(torch.uint8), recv, send,
+                                      group=group, async_op=True)
     if n_recv:
-        # gather index from the received order to the grouped order, built from the block table
+        # gather index from the received order to the grouped order, built from the block
+        # table while the rows are in flight
         starts_d, lengths_d = starts.to(dev), lengths.to(dev)
         dest_base = torch.cumsum(lengths_d, 0) - lengths_d
         order = (torch.repeat_interleave(starts_d - dest_base, lengths_d, output_size=n_recv)
                  + torch.arange(n_recv, device=dev)).to(torch.int32)
         inverse = torch.empty_like(order)
         inverse[order.long()] = torch.arange(n_recv, device=dev, dtype=torch.int32)
-        rows_out = backend.experts(rows_recv, offsets_local.to(torch.int32).to(dev), order)
+        offsets_d = offsets_local.to(torch.int32).to(dev)
+    yield
+    arriving.wait()
+    if n_recv:
+        rows_out = backend.experts(rows_recv, offsets_d, order)
         rows_back = backend.gather(rows_out, inverse, "rows_back")   # received order again
     else:
         rows_back = rows_recv
     rows_home = torch.empty_like(rows_send)
-    dist.all_to_all_single(rows_home.view(torch.uint8), rows_back.view(torch.uint8), send, recv, group=group)
+    returning = dist.all_to_all_single(rows_home.view(torch.uint8), rows_back.view(torch.uint8), send, recv,
+                                       group=group, async_op=True)
+    yield
+    returning.wait()
     return backend.combine(rows_home, inv_perm, weights, shared, t_local), ids, weights
+
+
+def _drive(generators):
+    """Advance the generators round-robin until all have returned; -> their values."""
+    results = [None] * len(generators)
+    live = list(range(len(generators)))
+    while live:
+        for i in list(live):
+            try:
+                next(generators[i])
+            except StopIteration as stop:
+                results[i] = stop.value
+                live.remove(i)
+    return results
+
+
+def ep_forward(backend, x, cfg: dict, group=None, timings: dict | None = None):
+    """One expert-parallel layer pass for this rank's rows ``x`` [T_local, d]
+    (2-byte elements: bf16, or int16 bit patterns on a CPU backend)."""
+    return _drive([_ep_steps(backend, x, cfg, group)])[0]
+
+
+def ep_forward_pipelined(backends, x, cfg: dict, group=None, streams=None):
+    """The same pass with the rows cut into ``len(backends)`` consecutive pieces that
+    advance in lock step, each with a backend (scratch buffers) of its own and, on
+    a GPU, a stream of its own: while one piece's rows cross the links, another
+    piece's kernels run.  Every rank must use the same number of pieces (the
+    collectives pair up in issue order).  Rows are independent in every kernel of
+    the pass, so the result equals ``ep_forward`` bit for bit."""
+    pieces = len(backends)
+    t = x.shape[0]
+    bounds = [t * p // pieces for p in range(pieces + 1)]
+    parts = [x[bounds[p]:bounds[p + 1]] for p in range(pieces)]
+    if not x.is_cuda:
+        results = _drive([_ep_steps(b, part, cfg, group) for b, part in zip(backends, parts)])
+    else:
+        main = torch.cuda.current_stream(x.device)
+
+        def on_stream(gen, stream):
+            # every step of a piece is issued with the piece's stream current
+            while True:
+                with torch.cuda.stream(stream):
+                    try:
+                        next(gen)
+                    except StopIteration as stop:
+                        return stop.value
+                yield
+
+        for s in streams:
+            s.wait_stream(main)
+        results = _drive([on_stream(_ep_steps(b, part, cfg, group), s)
+                          for b, part, s in zip(backends, parts, streams)])
+        for s, r in zip(streams, results):
+            main.wait_stream(s)
+            for tensor in r:
+                tensor.record_stream(main)
+        for s in streams:
+            x.record_stream(s)
+    out = torch.cat([r[0] for r in results])
+    ids = torch.cat([r[1] for r in results])
+    weights = torch.cat([r[2] for r in results])
+    return out, ids, weights
 
 
 class ExpertParallelLayer:
     """The benchmark's layer sharded over the default process group (one rank per GPU)."""
 
-    def __init__(self, cfg: dict, seed: int, device, tokens: int, weights: dict | None = None):
+    def __init__(self, cfg: dict, seed: int, device, tokens: int, weights: dict | None = None, pieces: int = 1):
+        """``pieces`` > 1 cuts every pass into that many consecutive row ranges that are
+        pipelined against each other (``ep_forward_pipelined``); same results."""
         self.world, self.rank = dist.get_world_size(), dist.get_rank()
         if tokens % self.world != 0:
             raise ValueError("token count must divide evenly over the ranks")
@@ -240,29 +316,37 @@ class ExpertParallelLayer:
         self.local_tokens = tokens // self.world
         first, per = shard_range(cfg["experts"], self.world, self.rank)
         self.layer = MoELayer(cfg, weights, seed=seed, device=device, local=(first, per), max_tokens=1)
-        self.backend = NativeBackend(self.layer)
+        self.backends = [NativeBackend(self.layer) for _ in range(max(1, pieces))]
+        self.backend = self.backends[0]
         self.device = self.layer.device
+        self.streams = [torch.cuda.Stream(self.device) for _ in self.backends] if len(self.backends) > 1 else None
 
     def forward(self, x: torch.Tensor, want_routes: bool = False):
-        out, ids, w = ep_forward(self.backend, x, self.cfg)
+        if len(self.backends) > 1:
+            out, ids, w = ep_forward_pipelined(self.backends, x, self.cfg, streams=self.streams)
+        else:
+            out, ids, w = ep_forward(self.backend, x, self.cfg)
         return (out, ids, w) if want_routes else out
 
     def phase_times(self, x: torch.Tensor, steps: int = 5) -> dict:
         """Device time of the grouped expert products on this rank's received rows,
         plus the whole-pass time, averaged over ``steps`` passes."""
         start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        orig = self.backend.experts
+        originals = [b.experts for b in self.backends]
         spans = []
 
-        def timed(*args):
-            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            a.record()
-            r = orig(*args)
-            b.record()
-            spans.append((a, b))
-            return r
+        def timed_call(orig):
+            def timed(*args):
+                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a.record()
+                r = orig(*args)
+                b.record()
+                spans.append((a, b))
+                return r
+            return timed
 
-        self.backend.experts = timed
+        for backend, orig in zip(self.backends, originals):
+            backend.experts = timed_call(orig)
         try:
             start.record()
             for _ in range(steps):
@@ -270,6 +354,7 @@ class ExpertParallelLayer:
             stop.record()
             torch.cuda.synchronize()
         finally:
-            self.backend.experts = orig
+            for backend, orig in zip(self.backends, originals):
+                backend.experts = orig
         experts_ms = sum(a.elapsed_time(b) for a, b in spans) / steps
         return {"experts_ms": experts_ms, "pass_ms": start.elapsed_time(stop) / steps}

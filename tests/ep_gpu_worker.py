@@ -42,6 +42,13 @@ def main():
         r = (want.astype(np.uint32) << 16).view(np.float32).astype(np.float64)
         rel = float(np.sqrt(((g - r) ** 2).sum() / (r ** 2).sum()))
         verdicts.append((bias_mode, same_ids, bool(np.array_equal(got, want)), rel))
+        # the same pass cut into two row ranges pipelined against each other: same bits
+        piped = ExpertParallelLayer(cfg, seed=5, device=device, tokens=tokens, weights=weights, pieces=2)
+        for _ in range(3):
+            out2, ids2, _ = piped.forward(xl, want_routes=True)
+        torch.cuda.synchronize()
+        same = bool(np.array_equal(bf16_tensor_to_bits(out2), got)) and bool(torch.equal(ids2, ids))
+        verdicts.append((bias_mode + "/pipelined", same, same, 0.0 if same else 1.0))
     ok = all(v[1] and v[3] <= 1e-3 for v in verdicts)
     sys.stderr.write(f"rank {rank}: {verdicts}\n")
     # one verdict line for the whole job (lines of several ranks could interleave)

@@ -98,7 +98,12 @@ def _worker(rank, world, port, mode, results):
         backend = OracleBackend(cfg, weights, first, per)
         lo, hi = rank * tokens // world, (rank + 1) * tokens // world
         xl = torch.from_numpy(x[lo:hi].view(np.int16).copy())
-        out, ids, _ = ep.ep_forward(backend, xl, cfg)
+        if mode == "pipelined":
+            # three row ranges advancing in lock step, each with its own backend
+            backends = [OracleBackend(cfg, weights, first, per) for _ in range(3)]
+            out, ids, _ = ep.ep_forward_pipelined(backends, xl, cfg)
+        else:
+            out, ids, _ = ep.ep_forward(backend, xl, cfg)
         got = out.numpy().view(np.uint16)
         ok = np.array_equal(got, want[lo:hi]) and np.array_equal(ids.numpy().view(np.uint32), want_ids[lo:hi])
         results[rank] = bool(ok)
@@ -106,9 +111,9 @@ def _worker(rank, world, port, mode, results):
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("mode,world", [("balanced", 2), ("rank1_idle", 2), ("balanced", 4)])
+@pytest.mark.parametrize("mode,world", [("balanced", 2), ("rank1_idle", 2), ("balanced", 4), ("pipelined", 2)])
 def test_expert_parallel_ranks_equal_single_process(mode, world, oracle):
-    port = 29600 + (os.getpid() % 200) + (0 if mode == "balanced" else 1) + 2 * world
+    port = 29600 + (os.getpid() % 200) + {"balanced": 0, "rank1_idle": 1, "pipelined": 5}[mode] + 2 * world
     with mp.Manager() as manager:
         results = manager.dict()
         mp.spawn(_worker, args=(world, port, mode, results), nprocs=world, join=True)
