@@ -488,11 +488,11 @@ decode_down_kernel(DecodeArgs a) {
 __global__ void __launch_bounds__(256, 2)
 decode_shared_gateup_kernel(DecodeArgs a) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
-    __half *xh = reinterpret_cast<__half *>(smem_raw);                       // [2][hidden] f16, rescaled
+    __half *xh = reinterpret_cast<__half *>(smem_raw);                       // [hidden] f16, rescaled
     __shared__ float inv_scale[2], stage_scratch[2 * 8], part[8][16];
     const uint32_t warp = threadIdx.x / kWarp, lane = threadIdx.x % kWarp;
     const uint32_t S = a.d.shared_hidden, H = a.d.hidden;
-    stage_vectors_f16(xh, inv_scale, a.x, nullptr, H, H, stage_scratch);
+    stage_vectors_f16_n<1>(xh, inv_scale, a.x, nullptr, H, H, stage_scratch);
     const uint32_t steps = H / 128u, per = (steps + 7u) / 8u;
     for (uint32_t task = blockIdx.x; task < 2u * S / 16u; task += gridDim.x) {
         const uint32_t r0 = task * 16u;
@@ -728,7 +728,7 @@ bool k3_decode_layer(const k3_moe_layer_desc *d, const void *x, void *logits, vo
             (void)cudaGetLastError();
             return false;
         }
-        const size_t gu_smem = (size_t)d->hidden * 4u;
+        const size_t gu_smem = (size_t)d->hidden * 2u;
         const size_t dn_smem = (size_t)d->shared_hidden * 6u;
         if (!set_smem((const void *)decode_shared_gateup_kernel, gu_smem) ||
             !set_smem((const void *)decode_shared_down_kernel, dn_smem)) {

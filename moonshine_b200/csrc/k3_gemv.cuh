@@ -64,9 +64,10 @@ K3_DEVINL void mma_f16_m16n8k16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_
 // Stage `nvec` (1 or 2) bf16 vectors of K columns into shared memory as f16,
 // zero padded to k_pad (multiple of 128).  Returns through inv_scale[v] the
 // power of two to multiply final sums with.  All threads of the CTA call it.
-K3_DEVINL void stage_vectors_f16(__half *xs, float *inv_scale, const uint16_t *x0,
-                                 const uint16_t *x1, uint32_t k, uint32_t k_pad,
-                                 float *scratch /* >= 2*warps floats */) {
+template <int kSlots>
+K3_DEVINL void stage_vectors_f16_n(__half *xs, float *inv_scale, const uint16_t *x0,
+                                   const uint16_t *x1, uint32_t k, uint32_t k_pad,
+                                   float *scratch /* >= 2*warps floats */) {
     const uint32_t tid = threadIdx.x;
     const uint32_t nthreads = blockDim.x;
     const uint16_t *src[2] = {x0, x1};
@@ -79,7 +80,7 @@ K3_DEVINL void stage_vectors_f16(__half *xs, float *inv_scale, const uint16_t *x
         ((reinterpret_cast<uintptr_t>(x0) | reinterpret_cast<uintptr_t>(x1)) & 15u) == 0u) {
         uint4 held[2][4];
 #pragma unroll
-        for (int v = 0; v < 2; v++) {
+        for (int v = 0; v < kSlots; v++) {
             if (src[v] == nullptr) continue;
 #pragma unroll
             for (int j = 0; j < 4; j++) {
@@ -100,7 +101,7 @@ K3_DEVINL void stage_vectors_f16(__half *xs, float *inv_scale, const uint16_t *x
         }
         __syncthreads();
 #pragma unroll
-        for (int v = 0; v < 2; v++) {
+        for (int v = 0; v < kSlots; v++) {
             float m = 0.f;
             for (uint32_t w = 0; w < nthreads / kWarp; w++) m = fmaxf(m, scratch[v * (nthreads / kWarp) + w]);
             int e = 0;
@@ -134,7 +135,7 @@ K3_DEVINL void stage_vectors_f16(__half *xs, float *inv_scale, const uint16_t *x
         return;
     }
 #pragma unroll
-    for (int v = 0; v < 2; v++) {
+    for (int v = 0; v < kSlots; v++) {
         if (src[v] == nullptr) continue;
         for (uint32_t i = tid; i < k; i += nthreads) {
             mx[v] = fmaxf(mx[v], fabsf(bf16_bits_to_float(src[v][i])));
@@ -145,7 +146,7 @@ K3_DEVINL void stage_vectors_f16(__half *xs, float *inv_scale, const uint16_t *x
     __syncthreads();
     float mul[2];
 #pragma unroll
-    for (int v = 0; v < 2; v++) {
+    for (int v = 0; v < kSlots; v++) {
         float m = 0.f;
         for (uint32_t w = 0; w < nthreads / kWarp; w++) m = fmaxf(m, scratch[v * (nthreads / kWarp) + w]);
         int e = 0;
@@ -157,7 +158,7 @@ K3_DEVINL void stage_vectors_f16(__half *xs, float *inv_scale, const uint16_t *x
         if (tid == 0) inv_scale[v] = __uint_as_float((uint32_t)(127 + e) << 23);  // 2^e
     }
 #pragma unroll
-    for (int v = 0; v < 2; v++) {
+    for (int v = 0; v < kSlots; v++) {
         __half *dst = xs + (size_t)v * k_pad;
         for (uint32_t i = tid; i < k_pad; i += nthreads) {
             float val = 0.f;
@@ -166,6 +167,13 @@ K3_DEVINL void stage_vectors_f16(__half *xs, float *inv_scale, const uint16_t *x
         }
     }
     __syncthreads();
+}
+
+// two slots (the second zero-filled when x1 is null)
+K3_DEVINL void stage_vectors_f16(__half *xs, float *inv_scale, const uint16_t *x0,
+                                 const uint16_t *x1, uint32_t k, uint32_t k_pad,
+                                 float *scratch /* >= 2*warps floats */) {
+    stage_vectors_f16_n<2>(xs, inv_scale, x0, x1, k, k_pad, scratch);
 }
 
 // ---------------------------------------------------------------------------
