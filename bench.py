@@ -220,9 +220,9 @@ def run_reference(args):
 
 # DRAM bytes per launch measured with ncu on these workloads (one-pass metrics,
 # summary kept under profiles/): prefill = gate/up (28.81 GB) + down (11.73 GB)
-# launches of the grouped expert phase; decode = the four kernels of one token.
+# launches of the grouped expert phase; decode = the five kernels of one token.
 PREFILL_TRAFFIC_BYTES = 40.54e9
-DECODE_TRAFFIC_BYTES = 434.8e6
+DECODE_TRAFFIC_BYTES = 435.6e6
 
 
 # --------------------------------------------------------------- native arm
