@@ -12,7 +12,9 @@ exchange step each way:
   2. one all-gather of every rank's per-expert row counts (the only host read of
      the pass: it gives each rank its send and receive splits and the layout of
      what it will receive), then the all-to-all of the bf16 rows themselves
-     (``all_to_all_single`` with uneven splits);
+     (``all_to_all_single`` with uneven splits) - each token row once per
+     destination, however many of its routes go there, with a 4-byte slot per
+     route telling the destination which received row the route reads;
   3. on the destination the received rows (source rank asc, expert asc, route asc)
      are regrouped (expert asc, source rank asc, route asc) - with the contiguous
      token partition this is exactly the single-GPU grouping order - through a
@@ -183,14 +185,24 @@ def _ep_steps(backend, x, cfg: dict, group):
     ids, weights = backend.route(x)
     offsets, sorted_route, sorted_token, inv_perm = backend.dispatch(ids, t_local, k, e, "src")
 
+    # A token with several routes to one destination crosses the link once: per
+    # destination g the source sends the rows of the tokens that have a route there
+    # (token asc) and, per route, the slot of its token among them.
+    dest = torch.div(ids.long(), per, rounding_mode="floor")                 # [T, k]
+    member = torch.zeros((t_local, world), dtype=torch.int64, device=dev).scatter_(1, dest, 1)
+    slots = torch.cumsum(member, 0) - 1                                       # [T, world]
+    route_slot = slots[sorted_token.long(), dest.reshape(-1)[sorted_route.long()]].to(torch.int32)
+    members_first = torch.argsort(member.t().reshape(-1), descending=True, stable=True)
+    token_of_unique = (members_first % t_local).to(torch.int32)               # (destination asc, token asc)
+
     # One collective and one host read tell every rank who sends how many rows of which
-    # expert.  On a GPU the exchange runs on a side stream and the host reads it only after
-    # the shared expert and the row gather have been queued, so the device stays busy
-    # while the host waits and plans.
-    counts = (offsets[1:] - offsets[:-1]).to(torch.int64)
+    # expert (and how many distinct token rows to whom).  On a GPU the exchange runs on
+    # a side stream and the host reads it only after the shared expert has been queued,
+    # so the device stays busy while the host waits and plans.
+    counts = torch.cat([(offsets[1:] - offsets[:-1]).to(torch.int64), member.sum(0)])
     if x.is_cuda:
         main = torch.cuda.current_stream(dev)
-        side, pinned, done = backend.exchange_resources(world, e)
+        side, pinned, done = backend.exchange_resources(world, e + world)
         side.wait_stream(main)
         with torch.cuda.stream(side):
             counts.record_stream(side)
@@ -199,7 +211,6 @@ def _ep_steps(backend, x, cfg: dict, group):
             pinned.copy_(torch.stack(gathered), non_blocking=True)
             done.record(side)
         shared = backend.shared(x)
-        rows_send = backend.gather(x, sorted_token, "rows_send")
         yield
         done.synchronize()
         all_counts = pinned.clone()
@@ -208,14 +219,18 @@ def _ep_steps(backend, x, cfg: dict, group):
         dist.all_gather(gathered, counts, group=group)
         all_counts = torch.stack(gathered).cpu()
         shared = backend.shared(x)
-        rows_send = backend.gather(x, sorted_token, "rows_send")  # (expert asc, route asc): contiguous per destination
         yield
-    send, recv, starts, lengths, offsets_local = exchange_plan(all_counts, rank, first, per)
-    n_recv = sum(recv)
+    send, recv, starts, lengths, offsets_local = exchange_plan(all_counts[:, :e], rank, first, per)
+    send_unique = [int(v) for v in all_counts[rank, e:]]
+    recv_unique = [int(v) for v in all_counts[:, e + rank]]
+    n_recv, n_unique = sum(recv), sum(recv_unique)
 
-    rows_recv = torch.empty((n_recv, x.shape[1]), dtype=x.dtype, device=dev)
-    arriving = dist.all_to_all_single(rows_recv.view(torch.uint8), rows_send.view(torch.uint8), recv, send,
-                                      group=group, async_op=True)
+    rows_send = backend.gather(x, token_of_unique[:sum(send_unique)], "rows_send")
+    rows_recv = torch.empty((n_unique, x.shape[1]), dtype=x.dtype, device=dev)
+    slots_recv = torch.empty(n_recv, dtype=torch.int32, device=dev)
+    slots_arriving = dist.all_to_all_single(slots_recv, route_slot, recv, send, group=group, async_op=True)
+    arriving = dist.all_to_all_single(rows_recv.view(torch.uint8), rows_send.view(torch.uint8), recv_unique,
+                                      send_unique, group=group, async_op=True)
     if n_recv:
         # gather index from the received order to the grouped order, built from the block
         # table while the rows are in flight
@@ -226,14 +241,22 @@ def _ep_steps(backend, x, cfg: dict, group):
         inverse = torch.empty_like(order)
         inverse[order.long()] = torch.arange(n_recv, device=dev, dtype=torch.int32)
         offsets_d = offsets_local.to(torch.int32).to(dev)
+        # first received row of each source, repeated for each of its routes
+        recv_unique_t = torch.tensor(recv_unique, dtype=torch.int64)
+        base_of_source = (torch.cumsum(recv_unique_t, 0) - recv_unique_t).to(dev)
+        base_of_route = torch.repeat_interleave(base_of_source, torch.tensor(recv, dtype=torch.int64).to(dev),
+                                                output_size=n_recv)
     yield
+    slots_arriving.wait()
     arriving.wait()
     if n_recv:
-        rows_out = backend.experts(rows_recv, offsets_d, order)
+        # grouped position -> received route -> row of its token among the received rows
+        row_of_route = (base_of_route + slots_recv.long())[order.long()].to(torch.int32)
+        rows_out = backend.experts(rows_recv, offsets_d, row_of_route)
         rows_back = backend.gather(rows_out, inverse, "rows_back")   # received order again
     else:
-        rows_back = rows_recv
-    rows_home = torch.empty_like(rows_send)
+        rows_back = torch.empty((0, x.shape[1]), dtype=x.dtype, device=dev)
+    rows_home = torch.empty((t_local * k, x.shape[1]), dtype=x.dtype, device=dev)
     returning = dist.all_to_all_single(rows_home.view(torch.uint8), rows_back.view(torch.uint8), send, recv,
                                        group=group, async_op=True)
     yield
