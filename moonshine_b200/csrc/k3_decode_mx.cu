@@ -20,9 +20,8 @@
 //   warps 6-9   epilogue: tcgen05.ld columns 0/1 (+16/17), sum, bf16, activation;
 //               the gate/up epilogue also splits the activation it produces into
 //               the two E4M3 terms the down projection reads
-//   warps 10-15 shared-expert Q8 rows (gate and up next to the routed gate/up,
-//               down next to the routed down), exact reference order, overlapping
-//               the HBM-bound tensor pipeline
+//   warp 10     scale producer: block scales of four K steps into a shared-memory ring
+//   warp 11     second MMA issuer (odd K steps, its own accumulator columns)
 // Every barrier wait is bounded (see k3_tc_ptx.cuh).
 #include "k3_decode_tail.cuh"
 #include "k3_grouped.h"
@@ -53,15 +52,14 @@ constexpr uint32_t kATile = 128 * 128;     // bytes in shared memory (8-bit cont
 constexpr uint32_t kATx = 128 * 64;        // bytes the TMA transaction counts (packed)
 constexpr uint32_t kBTile = 16 * 128;
 constexpr uint32_t kStageBytes = kATile + kBTile;
-constexpr uint32_t kThreads = 512;
-constexpr uint32_t kSideWarps = 4;          // warps 12..15 (10: scale producer, 11: second MMA issuer)
+constexpr uint32_t kThreads = 384;          // 12 warps, see the role list above
 constexpr uint32_t kTmemCols = 512;
 constexpr uint32_t kAccCol = 0;            // 2 buffers x 2 issuers x 2 phases x 16 columns
 constexpr uint32_t kSfaCol = 128;          // kSfStages x 4 columns
 constexpr uint32_t kSfbCol = 128 + 4 * kSfStages;  // kSfStages x 4 columns
 constexpr uint32_t kBarrierBytes = 512;
 constexpr uint32_t kSmemBytes =
-    kStages * kStageBytes + kSfSlots * kSfSlotBytes + 1024 + kBarrierBytes;   // + shared activation vector
+    kStages * kStageBytes + kSfSlots * kSfSlotBytes + 1024 + kBarrierBytes;   // 1024: alignment slack
 
 __device__ uint32_t g_mx_status = 0;
 
@@ -111,13 +109,6 @@ struct MxArgs {
     uint8_t *act_hl;            // gate/up: E4M3 split of the produced activation [2*ranks, w_rows]
     uint8_t *act_sf;            //          and its block scales [ranks, w_rows/32]
     DecodeTail tail;            // down: the layer's tail (tail.out null: none)
-    // shared-expert side work (Q8 rows, one warp per row)
-    const int8_t *q8_q;
-    const void *q8_s;
-    uint16_t *q8_out;
-    const uint16_t *q8_x;       // input vector [q8_cols] bf16
-    uint32_t q8_rows, q8_cols, q8_block;
-    int q8_scale_f16;
 };
 
 // value -> (hi, lo) E4M3 pair and block scale of a 32-element block held one
@@ -158,7 +149,6 @@ decode_mx_kernel(const __grid_constant__ MxMaps maps, MxArgs a) {
     uint64_t *acc_full = sfs_empty + kSfSlots, *acc_empty = acc_full + 2;
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(acc_empty + 2);
     volatile uint32_t *abort_flag = tmem_slot + 1;
-    uint16_t *side_x = reinterpret_cast<uint16_t *>(reinterpret_cast<unsigned char *>(bars) + kBarrierBytes);
     const uint32_t warp = threadIdx.x / kWarp, lane = threadIdx.x % kWarp;
     const uint32_t steps = a.k / 128u;
     const uint32_t phases = kGateUp ? 2u : 1u;
@@ -189,30 +179,12 @@ decode_mx_kernel(const __grid_constant__ MxMaps maps, MxArgs a) {
         tmem_alloc(tmem_slot, kTmemCols);
         tmem_relinquish();
     }
-    for (uint32_t i = threadIdx.x; i < (a.q8_rows != 0u ? a.q8_cols : 0u); i += blockDim.x) side_x[i] = a.q8_x[i];
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = *tmem_slot;
 
-    if (warp >= 12) {
-        // ---- shared-expert rows (SIMT), independent of the tensor pipeline
-        // two rows per pass so that twice the loads are in flight
-        const uint32_t side = blockIdx.x * kSideWarps + (warp - 12u);
-        const uint32_t side_total = gridDim.x * kSideWarps;
-        const uint32_t bpr = a.q8_cols / (a.q8_block ? a.q8_block : 1u);
-        for (uint32_t row = 2u * side; row < a.q8_rows; row += 2u * side_total) {
-            const uint32_t row1 = min(row + 1u, a.q8_rows - 1u);
-            const float v0 = q8_row_dot_exact(a.q8_q + (uint64_t)row * a.q8_cols, a.q8_s, (uint64_t)row * bpr,
-                                              side_x, a.q8_cols, a.q8_block, a.q8_scale_f16, lane);
-            const float v1 = q8_row_dot_exact(a.q8_q + (uint64_t)row1 * a.q8_cols, a.q8_s, (uint64_t)row1 * bpr,
-                                              side_x, a.q8_cols, a.q8_block, a.q8_scale_f16, lane);
-            if (lane == 0) {
-                a.q8_out[row] = float_to_bf16_bits(v0);
-                a.q8_out[row1] = float_to_bf16_bits(v1);
-            }
-        }
-    } else if (warp == 0) {
+    if (warp == 0) {
         // weight tile + vector tile of every K step
         if (lane == 0) {
             prefetch_tensormap(&maps.a0);
