@@ -211,6 +211,10 @@ def _ep_steps(backend, x, cfg: dict, group):
             pinned.copy_(torch.stack(gathered), non_blocking=True)
             done.record(side)
         shared = backend.shared(x)
+        # every (destination, token) candidate row is gathered before the host knows how
+        # many are members (members come first): the copy of the few surplus rows costs
+        # less than leaving the device idle while the host plans
+        rows_send = backend.gather(x, token_of_unique, "rows_send")
         yield
         done.synchronize()
         all_counts = pinned.clone()
@@ -219,13 +223,14 @@ def _ep_steps(backend, x, cfg: dict, group):
         dist.all_gather(gathered, counts, group=group)
         all_counts = torch.stack(gathered).cpu()
         shared = backend.shared(x)
+        rows_send = backend.gather(x, token_of_unique, "rows_send")
         yield
     send, recv, starts, lengths, offsets_local = exchange_plan(all_counts[:, :e], rank, first, per)
     send_unique = [int(v) for v in all_counts[rank, e:]]
     recv_unique = [int(v) for v in all_counts[:, e + rank]]
     n_recv, n_unique = sum(recv), sum(recv_unique)
 
-    rows_send = backend.gather(x, token_of_unique[:sum(send_unique)], "rows_send")
+    rows_send = rows_send[:sum(send_unique)]
     rows_recv = torch.empty((n_unique, x.shape[1]), dtype=x.dtype, device=dev)
     slots_recv = torch.empty(n_recv, dtype=torch.int32, device=dev)
     slots_arriving = dist.all_to_all_single(slots_recv, route_slot, recv, send, group=group, async_op=True)
@@ -234,18 +239,21 @@ def _ep_steps(backend, x, cfg: dict, group):
     if n_recv:
         # gather index from the received order to the grouped order, built from the block
         # table while the rows are in flight
-        starts_d, lengths_d = starts.to(dev), lengths.to(dev)
+        # (one host-to-device copy for all the small tables)
+        recv_unique_t = torch.tensor(recv_unique, dtype=torch.int64)
+        tables = torch.cat([starts, lengths, offsets_local, torch.cumsum(recv_unique_t, 0) - recv_unique_t,
+                            torch.tensor(recv, dtype=torch.int64)]).to(dev)
+        n_blocks = starts.numel()
+        starts_d, lengths_d = tables[:n_blocks], tables[n_blocks:2 * n_blocks]
+        offsets_d = tables[2 * n_blocks:2 * n_blocks + per + 1].to(torch.int32)
+        base_of_source, recv_d = tables[-2 * world:-world], tables[-world:]
         dest_base = torch.cumsum(lengths_d, 0) - lengths_d
         order = (torch.repeat_interleave(starts_d - dest_base, lengths_d, output_size=n_recv)
                  + torch.arange(n_recv, device=dev)).to(torch.int32)
         inverse = torch.empty_like(order)
         inverse[order.long()] = torch.arange(n_recv, device=dev, dtype=torch.int32)
-        offsets_d = offsets_local.to(torch.int32).to(dev)
         # first received row of each source, repeated for each of its routes
-        recv_unique_t = torch.tensor(recv_unique, dtype=torch.int64)
-        base_of_source = (torch.cumsum(recv_unique_t, 0) - recv_unique_t).to(dev)
-        base_of_route = torch.repeat_interleave(base_of_source, torch.tensor(recv, dtype=torch.int64).to(dev),
-                                                output_size=n_recv)
+        base_of_route = torch.repeat_interleave(base_of_source, recv_d, output_size=n_recv)
     yield
     slots_arriving.wait()
     arriving.wait()
