@@ -42,6 +42,14 @@ def main():
         r = (want.astype(np.uint32) << 16).view(np.float32).astype(np.float64)
         rel = float(np.sqrt(((g - r) ** 2).sum() / (r ** 2).sum()))
         verdicts.append((bias_mode, same_ids, bool(np.array_equal(got, want)), rel))
+        # both forms of the exchange (a row per route / a row per destination): same bits
+        from moonshine_b200.ep import ep_forward
+        for form in (False, True):
+            out1, ids1, _ = ep_forward(ep_layer.backend, xl, cfg, once_per_destination=form)
+            torch.cuda.synchronize()
+            same = bool(np.array_equal(bf16_tensor_to_bits(out1), got)) and bool(torch.equal(ids1, ids))
+            verdicts.append((bias_mode + ("/row per destination" if form else "/row per route"), same, same,
+                             0.0 if same else 1.0))
         # the same pass cut into two row ranges pipelined against each other: same bits
         piped = ExpertParallelLayer(cfg, seed=5, device=device, tokens=tokens, weights=weights, pieces=2)
         for _ in range(3):

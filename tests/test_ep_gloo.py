@@ -102,8 +102,10 @@ def _worker(rank, world, port, mode, results):
             # three row ranges advancing in lock step, each with its own backend
             backends = [OracleBackend(cfg, weights, first, per) for _ in range(3)]
             out, ids, _ = ep.ep_forward_pipelined(backends, xl, cfg)
+        elif mode == "row_per_route":
+            out, ids, _ = ep.ep_forward(backend, xl, cfg, once_per_destination=False)
         else:
-            out, ids, _ = ep.ep_forward(backend, xl, cfg)
+            out, ids, _ = ep.ep_forward(backend, xl, cfg, once_per_destination=True)
         got = out.numpy().view(np.uint16)
         ok = np.array_equal(got, want[lo:hi]) and np.array_equal(ids.numpy().view(np.uint32), want_ids[lo:hi])
         results[rank] = bool(ok)
@@ -111,9 +113,10 @@ def _worker(rank, world, port, mode, results):
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("mode,world", [("balanced", 2), ("rank1_idle", 2), ("balanced", 4), ("pipelined", 2)])
+@pytest.mark.parametrize("mode,world", [("balanced", 2), ("rank1_idle", 2), ("balanced", 4), ("pipelined", 2),
+                                        ("row_per_route", 2)])
 def test_expert_parallel_ranks_equal_single_process(mode, world, oracle):
-    port = 29600 + (os.getpid() % 200) + {"balanced": 0, "rank1_idle": 1, "pipelined": 5}[mode] + 2 * world
+    port = 29600 + (os.getpid() % 200) + {"balanced": 0, "rank1_idle": 1, "pipelined": 5, "row_per_route": 7}[mode] + 2 * world
     with mp.Manager() as manager:
         results = manager.dict()
         mp.spawn(_worker, args=(world, port, mode, results), nprocs=world, join=True)
@@ -131,6 +134,13 @@ def test_exchange_plan():
     assert off.tolist() == [0, 2, 7]
     send, recv, starts, lengths, off = ep.exchange_plan(counts, 0, 0, 2)
     assert send == [3, 3] and recv == [3, 3] and off.tolist() == [0, 4, 6]
+
+
+def test_exchange_form_by_world_size():
+    from moonshine_b200 import ep
+    assert ep.rows_once_per_destination(2, 16) and ep.rows_once_per_destination(4, 16)
+    assert not ep.rows_once_per_destination(8, 16)
+    assert not ep.rows_once_per_destination(2, 2)
 
 
 def test_destination_splits():
