@@ -42,9 +42,9 @@ using namespace k3::tc;
 
 namespace {
 
-constexpr uint32_t kStages = 10;            // TMA ring of weight / vector tiles
+constexpr uint32_t kStages = 12;            // TMA ring of weight / vector tiles
 constexpr uint32_t kSfBatches = 6;          // scale ring in tensor memory: batches of 4 steps
-constexpr uint32_t kSfSlots = 8;            // scale ring in shared memory (one batch per slot)
+constexpr uint32_t kSfSlots = 4;            // scale ring in shared memory (one batch per slot)
 constexpr uint32_t kSfaBytes = 128 * 16;    // 128 rows x 16 scale bytes (4 steps)
 constexpr uint32_t kSfSlotBytes = kSfaBytes + 128;   // + the vector's 16 scale bytes
 constexpr uint32_t kSfStages = 4 * kSfBatches;
