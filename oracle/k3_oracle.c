@@ -243,6 +243,9 @@ void k3o_activation(uint16_t *output, const uint16_t *gate,
             float sigmoid_gate = 1.0f / (1.0f + expf(-g));
             float bounded_up = linear_beta * tanhf(u / linear_beta);
             value = bounded_gate * sigmoid_gate * bounded_up;
+        } else if (activation == K3O_ACT_SITU_HOST) {
+            value = (beta * tanhf(g / beta) / (1.0f + expf(-g))) *
+                    (linear_beta * tanhf(u / linear_beta));
         } else {
             float sigmoid_gate = 1.0f / (1.0f + expf(-g));
             value = g * sigmoid_gate * u;

@@ -16,7 +16,7 @@ import numpy as np
 _HERE = os.path.dirname(os.path.abspath(__file__))
 _LIB_PATH = os.path.join(_HERE, "_build", "libk3oracle.so")
 
-ACT_SITU, ACT_SWIGLU = 0, 1
+ACT_SITU, ACT_SWIGLU, ACT_SITU_HOST = 0, 1, 2
 Q8_F32, Q8_F16 = 0, 1
 
 
