@@ -77,7 +77,8 @@ size_t k3_moe_layer_workspace_bytes(const k3_moe_layer_desc *desc,
  * k3_engine_prefill.inc:1175-1194): from expert_ids u32 [tokens, top_k] build
  * offsets u32 [experts+1], and for every sorted position p: sorted_route[p] =
  * token*top_k+rank, sorted_token[p] = token; inv_perm[route] = p.  Order:
- * expert ascending, route ascending inside an expert. */
+ * expert ascending, route ascending inside an expert.  Every id must be
+ * < experts; an id that is not raises bit 1 of k3_moe_device_status(). */
 size_t k3_moe_dispatch_workspace_bytes(uint32_t tokens, uint32_t top_k,
                                        uint32_t experts);
 bool k3_moe_dispatch_build(void *offsets, void *sorted_route,
@@ -197,6 +198,27 @@ bool k3_moe_layer_forward_events(const k3_moe_layer_desc *desc, void *out,
                                  void *workspace, size_t workspace_bytes,
                                  void *const *events, void *stream);
 
+/* Phase ledger under the reference's field names (k3_engine_prefill_stats,
+ * k3_engine.h:90-96), filled from the six events of one
+ * k3_moe_layer_forward_events call; every call ADDS to the fields, as the
+ * reference's host ledger does per layer (k3_engine_prefill.inc:1521, 1196,
+ * 1224, 1624), so an engine can copy the sums into its own statistics.
+ * Mapping: router_seconds = events 0->1; routed_index_seconds = 2->3 (dispatch
+ * and row gather); routed_expert_pipeline_seconds = 3->4 (grouped expert
+ * products); moe_tail_seconds = 1->2 + 4->5 (shared expert and combine, the
+ * work the reference's tail interval spans); shared_expert_seconds = 1->2 on
+ * its own.  Waits for events[5]; false if an event is missing or unrecorded. */
+typedef struct k3_moe_phase_stats {
+    double   router_seconds;
+    double   routed_index_seconds;
+    double   routed_expert_pipeline_seconds;
+    double   moe_tail_seconds;
+    double   shared_expert_seconds;
+    uint64_t layer_passes;
+} k3_moe_phase_stats;
+
+bool k3_moe_phase_stats_add(k3_moe_phase_stats *stats, void *const *events);
+
 /* The layer with the step either side of it: out = hidden_in + moe(rms_norm(hidden_in)).
  * The post-attention RMSNorm (k3_engine.cu:1550-1553) runs first and feeds router,
  * shared expert and experts; the residual add (k3_engine.cu:1889-1897) happens in
@@ -241,10 +263,24 @@ bool k3_moe_latent_layer_forward(const k3_moe_latent_desc *desc, void *out,
                                  size_t workspace_bytes, void *ids_out,
                                  void *weights_out, void *stream);
 
-/* Device-side status of the tensor-core kernels since the library was loaded:
- * 0 = ok, 1 = a bounded barrier wait gave up (the launch's output is then
- * undefined).  Synchronises with the device. */
+/* Device-side status since the library was loaded, a bit mask: 0 = ok;
+ * bit 0 (1) = a bounded barrier wait of a tensor-core kernel gave up (that
+ * launch's output is undefined); bit 1 (2) = a dispatch (either entry point)
+ * met an expert id >= experts: such routes are skipped, so the offsets
+ * undercount and the sorted arrays keep stale entries for them.
+ * Synchronises with the device. */
 uint32_t k3_moe_device_status(void);
+
+/* Reset the status to 0 (after the host has dealt with what it reported). */
+bool k3_moe_device_status_clear(void);
+
+/* Self test of the bounded waits: one warp waits on a barrier that nothing
+ * arrives on, gives up after `limit_us` microseconds (1 .. 1000000), and leaves
+ * by the same path as the product kernels: bit 0 of k3_moe_device_status() is
+ * raised and, if `gave_up` (a device u32) is given, 1 is stored there.  The
+ * kernel touches no tensor memory and the context stays usable.  No
+ * counterpart in the reference. */
+bool k3_moe_selftest_bounded_wait(uint32_t limit_us, void *gave_up, void *stream);
 
 /* Event helpers for hosts without CUDA runtime bindings: create / destroy a
  * timing event and read the milliseconds between two recorded events (waits

@@ -40,6 +40,25 @@ class LatentDesc(C.Structure):
 _LP = C.POINTER(LatentDesc)
 
 
+class PhaseStats(C.Structure):
+    """Mirror of ``k3_moe_phase_stats`` (include/k3_moe_layer.h)."""
+    _fields_ = [("router_seconds", C.c_double), ("routed_index_seconds", C.c_double),
+                ("routed_expert_pipeline_seconds", C.c_double), ("moe_tail_seconds", C.c_double),
+                ("shared_expert_seconds", C.c_double), ("layer_passes", C.c_uint64)]
+
+
+class StTensor(C.Structure):
+    """Mirror of ``k3_st_tensor`` (include/k3_static_weight.h)."""
+    _fields_ = [("name", C.c_char_p), ("physical_offset", C.c_uint64), ("byte_length", C.c_uint64),
+                ("shape", C.c_uint64 * 8), ("shard", C.c_uint16), ("ndim", C.c_uint8), ("dtype", C.c_int)]
+
+
+class StaticWeight(C.Structure):
+    """Mirror of ``k3_static_weight`` (include/k3_static_weight.h)."""
+    _fields_ = [("tensor", C.POINTER(StTensor)), ("data", C.c_void_p), ("scales", C.c_void_p),
+                ("resident_bytes", C.c_uint64), ("kind", C.c_int)]
+
+
 
 class SlotAccess(C.Structure):
     """Mirror of ``k3_moe_slot_access`` (include/k3_moe_store.h)."""
@@ -121,6 +140,11 @@ SIGNATURES = {
     "k3_moe_layer_forward": (C.c_bool, [_DP, vp, vp, u32, vp, sz, vp, vp, vp]),
     "k3_moe_layer_forward_events": (C.c_bool, [_DP, vp, vp, u32, vp, sz, C.POINTER(vp), vp]),
     "k3_moe_device_status": (u32, []),
+    "k3_moe_device_status_clear": (C.c_bool, []),
+    "k3_moe_selftest_bounded_wait": (C.c_bool, [u32, vp, vp]),
+    "k3_moe_phase_stats_add": (C.c_bool, [C.POINTER(PhaseStats), C.POINTER(vp)]),
+    "k3_static_weight_gemv_bf16": (C.c_bool, [C.POINTER(StaticWeight), vp, vp, vp]),
+    "k3_static_weight_gemm_bf16": (C.c_bool, [C.POINTER(StaticWeight), vp, vp, u32, vp]),
     "k3_moe_event_create": (vp, []),
     "k3_moe_event_destroy": (None, [vp]),
     "k3_moe_event_elapsed_ms": (f32, [vp, vp]),

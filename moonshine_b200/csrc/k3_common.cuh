@@ -6,6 +6,11 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <atomic>
+#include <map>
+#include <mutex>
+#include <utility>
+
 #define K3_DEVINL __device__ __forceinline__
 
 namespace k3 {
@@ -83,17 +88,53 @@ K3_DEVINL uint2 ld_stream_8(const void *p) {
 
 inline bool launch_ok() { return cudaGetLastError() == cudaSuccess; }
 
-inline int sm_count() {
-    static int cached = 0;
-    if (cached == 0) {
-        int dev = 0;
-        if (cudaGetDevice(&dev) != cudaSuccess) return 148;
-        int n = 0;
-        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0)
-            return 148;
-        cached = n;
+// Host-side per-device state.  One process may drive several GPUs, and both the SM
+// count and a kernel's dynamic shared-memory limit belong to the device that is
+// current when the call is made.
+constexpr int kMaxDevices = 64;
+
+inline int current_device() {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) {
+        (void)cudaGetLastError();
+        return 0;
     }
-    return cached;
+    return dev;
+}
+
+inline int sm_count() {
+    static std::atomic<int> cached[kMaxDevices];
+    const int dev = current_device();
+    if (dev < 0 || dev >= kMaxDevices) return 148;
+    int n = cached[dev].load(std::memory_order_relaxed);
+    if (n == 0) {
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) {
+            (void)cudaGetLastError();
+            return 148;
+        }
+        cached[dev].store(n, std::memory_order_relaxed);
+    }
+    return n;
+}
+
+// cudaFuncAttributeMaxDynamicSharedMemorySize for `kernel` on the current device,
+// remembered per (device, kernel) so that the call is made once each (it costs
+// microseconds of host time).  Requests of 48 KB or less need no attribute.
+inline bool set_max_dynamic_smem(const void *kernel, size_t bytes) {
+    if (bytes <= 48u * 1024u) return true;
+    static std::mutex lock;
+    static std::map<std::pair<int, const void *>, size_t> done;
+    const int dev = current_device();
+    std::lock_guard<std::mutex> guard(lock);
+    const auto key = std::make_pair(dev, kernel);
+    auto it = done.find(key);
+    if (it != done.end() && it->second >= bytes) return true;
+    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes) != cudaSuccess) {
+        (void)cudaGetLastError();
+        return false;
+    }
+    done[key] = bytes;
+    return true;
 }
 
 }  // namespace k3

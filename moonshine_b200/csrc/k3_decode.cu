@@ -575,26 +575,16 @@ uint32_t k3_decode_status() {
     return v;
 }
 
-namespace {
-
-// (attribute changes are remembered per kernel: the call costs microseconds of host time)
-bool set_smem(const void *kernel, size_t smem) {
-    if (smem <= 48 * 1024) return true;
-    static std::mutex lock;
-    static std::map<std::pair<int, const void *>, size_t> done;      // (device, kernel) -> bytes set
-    int device = 0;
-    (void)cudaGetDevice(&device);
-    std::lock_guard<std::mutex> guard(lock);
-    const auto key = std::make_pair(device, kernel);
-    auto it = done.find(key);
-    if (it != done.end() && it->second >= smem) return true;
-    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
+bool k3_decode_status_clear() {
+    const uint32_t zero = 0u;
+    if (cudaMemcpyToSymbol(g_decode_status, &zero, sizeof(zero)) != cudaSuccess) {
         (void)cudaGetLastError();
         return false;
     }
-    done[key] = smem;
     return true;
 }
+
+namespace {
 
 // One side stream and a fork / join event pair per device, created on first use
 // (the one allocation-like step of the one-token path; never destroyed).
@@ -730,8 +720,8 @@ bool k3_decode_layer(const k3_moe_layer_desc *d, const void *x, void *logits, vo
         }
         const size_t gu_smem = (size_t)d->hidden * 2u;
         const size_t dn_smem = (size_t)d->shared_hidden * 6u;
-        if (!set_smem((const void *)decode_shared_gateup_kernel, gu_smem) ||
-            !set_smem((const void *)decode_shared_down_kernel, dn_smem)) {
+        if (!set_max_dynamic_smem((const void *)decode_shared_gateup_kernel, gu_smem) ||
+            !set_max_dynamic_smem((const void *)decode_shared_down_kernel, dn_smem)) {
             return false;
         }
         decode_shared_gateup_kernel<<<2u * d->shared_hidden / 16u, 256, gu_smem, side->stream>>>(a);
@@ -743,11 +733,11 @@ bool k3_decode_layer(const k3_moe_layer_desc *d, const void *x, void *logits, vo
         return true;
     };
     if (side) {
-        if (!set_smem((const void *)decode_front_kernel<false>, front_smem)) return false;
+        if (!set_max_dynamic_smem((const void *)decode_front_kernel<false>, front_smem)) return false;
         decode_front_kernel<false><<<std::min<uint32_t>(front_tasks, (uint32_t)sms * 4u - 1u) + 1u, 256, front_smem,
                                      stream>>>(a);
     } else {
-        if (!set_smem((const void *)decode_front_kernel<true>, front_smem)) return false;
+        if (!set_max_dynamic_smem((const void *)decode_front_kernel<true>, front_smem)) return false;
         decode_front_kernel<true><<<std::min<uint32_t>(front_tasks, (uint32_t)sms * 2u - 1u) + 1u, 256, front_smem,
                                     stream>>>(a);
     }
@@ -773,11 +763,11 @@ bool k3_decode_layer(const k3_moe_layer_desc *d, const void *x, void *logits, vo
                                        residual, 1u, d->top_k, d->hidden, stream);
     }
     size_t smem = (size_t)2 * d->hidden * sizeof(__half) + (2 + 2 * kDecodeWarps) * sizeof(float);
-    if (!set_smem((const void *)decode_gateup_kernel, smem)) return false;
+    if (!set_max_dynamic_smem((const void *)decode_gateup_kernel, smem)) return false;
     decode_gateup_kernel<<<sms, kDecodeThreads, smem, stream>>>(a);
     if (!launch_ok() || !mark(3)) return false;
     smem = (size_t)(d->top_k + 1u) * d->expert_hidden * sizeof(__half) + (34 + 2 * kDecodeWarps) * sizeof(float);
-    if (!set_smem((const void *)decode_down_kernel, smem)) return false;
+    if (!set_max_dynamic_smem((const void *)decode_down_kernel, smem)) return false;
     decode_down_kernel<<<sms, kDecodeThreads, smem, stream>>>(a);
     if (!launch_ok() || !mark(4)) return false;
     return k3_moe_combine_residual(out, rows_out, nullptr, weights, d->shared_hidden ? sh_out : nullptr,

@@ -35,6 +35,7 @@
 #include <algorithm>
 #include <atomic>
 #include <cstring>
+#include <map>
 #include <mutex>
 
 using namespace k3;
@@ -442,6 +443,15 @@ uint32_t k3_decode_mx_status() {
     return v;
 }
 
+bool k3_decode_mx_status_clear() {
+    const uint32_t zero = 0u;
+    if (cudaMemcpyToSymbol(g_mx_status, &zero, sizeof(zero)) != cudaSuccess) {
+        (void)cudaGetLastError();
+        return false;
+    }
+    return true;
+}
+
 size_t k3_decode_mx_scratch_bytes(const k3_moe_layer_desc *d) {
     // token terms and scales, activation terms and scales, arrival words of the tail,
     // scores and choices of the routing step
@@ -488,37 +498,40 @@ bool k3_decode_mx_experts(const k3_moe_layer_desc *d, const void *ids, void *act
     uint8_t *a_hl = align(x_sf + H / 32u);
     uint8_t *a_sf = align(a_hl + (size_t)2 * k * I);
     const size_t smem = kSmemBytes;
-    static size_t configured = 0;
-    if (configured < smem) {
-        if (cudaFuncSetAttribute(decode_mx_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess ||
-            cudaFuncSetAttribute(decode_mx_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
-            (void)cudaGetLastError();
-            return false;
-        }
-        configured = smem;
+    if (!set_max_dynamic_smem((const void *)decode_mx_kernel<true>, smem) ||
+        !set_max_dynamic_smem((const void *)decode_mx_kernel<false>, smem)) {
+        return false;
     }
-    // Tensor maps depend only on the tables, the scratch block and the shape: the
-    // last set is kept (encoding ten maps costs more host time than the launches).
+    // Tensor maps depend only on the tables, the scratch block and the shape.  Encoding
+    // ten maps costs more host time than the launches, so the sets of the most recent
+    // layers are kept (a model alternates between its layers' descriptors token by
+    // token); when the table is full it starts over.
     struct MapKey {
         int device;
         const void *p[7];
         uint32_t dims[4];
-        bool operator==(const MapKey &o) const {
-            return device == o.device && memcmp(p, o.p, sizeof(p)) == 0 && memcmp(dims, o.dims, sizeof(dims)) == 0;
+        bool operator<(const MapKey &o) const {
+            if (device != o.device) return device < o.device;
+            const int c = memcmp(p, o.p, sizeof(p));
+            return c != 0 ? c < 0 : memcmp(dims, o.dims, sizeof(dims)) < 0;
         }
     };
+    struct MapSet {
+        MxMaps gu, dn;
+    };
+    constexpr size_t kCachedLayers = 256;
     static std::mutex map_lock;
-    static MapKey cached_key{-1, {}, {}};
-    static MxMaps cached_gu, cached_dn;
+    static std::map<MapKey, MapSet> cached;
     MapKey key{};
-    (void)cudaGetDevice(&key.device);
+    key.device = current_device();
     const void *ptrs[7] = {d->w1_packed, d->w3_packed, d->w2_packed, d->w1_scales, d->w3_scales, d->w2_scales, scratch};
     memcpy(key.p, ptrs, sizeof(ptrs));
     key.dims[0] = H; key.dims[1] = I; key.dims[2] = k; key.dims[3] = d->local_expert_count;
     MxMaps gu, dn;
     {
         std::lock_guard<std::mutex> guard(map_lock);
-        if (!(cached_key == key)) {
+        auto it = cached.find(key);
+        if (it == cached.end()) {
             const uint64_t total = (uint64_t)d->local_expert_count;
             if (!map_fp4(&gu.a0, d->w1_packed, total * I, H) || !map_fp4(&gu.a1, d->w3_packed, total * I, H) ||
                 !map_u8(&gu.b, x_hl, 2, H) || !map_sf(&gu.sfa0, d->w1_scales, total * I, H, 128) ||
@@ -529,12 +542,11 @@ bool k3_decode_mx_experts(const k3_moe_layer_desc *d, const void *ids, void *act
             }
             dn.a1 = dn.a0;
             dn.sfa1 = dn.sfa0;
-            cached_gu = gu;
-            cached_dn = dn;
-            cached_key = key;
+            if (cached.size() >= kCachedLayers) cached.clear();
+            cached.emplace(key, MapSet{gu, dn});
         } else {
-            gu = cached_gu;
-            dn = cached_dn;
+            gu = it->second.gu;
+            dn = it->second.dn;
         }
     }
     MxArgs a{};

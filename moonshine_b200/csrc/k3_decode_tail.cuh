@@ -26,7 +26,8 @@ struct DecodeTail {
 
 // Counts an arrival in a word that carries the call's epoch in its upper 24 bits:
 // a word left by an earlier call (or by whatever used the memory before) reads as
-// zero arrivals, so the words need no clearing.  Returns the arrivals including this
+// zero arrivals, so the words need no clearing before first use (the arrival that
+// completes a group clears the word again).  Returns the arrivals including this
 // one, or 0 if the update did not go through in 1024 attempts (a few dozen warps
 // at most contend for a word).
 K3_DEVINL uint32_t count_arrival(uint32_t *word, uint32_t epoch24) {
@@ -73,6 +74,11 @@ K3_DEVINL bool tail_arrive(const DecodeTail &t, uint32_t group, uint32_t lane) {
     if (t.residual != nullptr)
         bits = float_to_bf16_bits(bf16_bits_to_float(__ldcg(t.residual + col)) + bf16_bits_to_float(bits));
     t.out[col] = bits;
+    // Last toucher of the group's word: leave it at zero, so that the same call
+    // replayed with the same epoch (a captured graph launched again) counts from
+    // zero like a fresh one instead of finding the full count of its last run.
+    __syncwarp();
+    if (lane == 0) atomicExch(t.count + group, 0u);
     return true;
 }
 

@@ -20,6 +20,11 @@ constexpr uint32_t kChunk = 512;        // routes per warp
 constexpr uint32_t kWarpsPerBlock = 4;
 constexpr uint32_t kMaxExperts = 1024;
 
+// Set (to 2) when a dispatch saw an expert id >= experts; read by k3_moe_device_status().
+// Such routes are counted nowhere and placed nowhere, so the outputs of that call
+// are incomplete.  Shared by both dispatch entry points.
+__device__ uint32_t g_dispatch_status = 0;
+
 __global__ void __launch_bounds__(kWarpsPerBlock * 32)
 route_hist_kernel(uint32_t *__restrict__ hist, const uint32_t *__restrict__ ids,
                   uint32_t routes, uint32_t experts, uint32_t chunks,
@@ -36,7 +41,10 @@ route_hist_kernel(uint32_t *__restrict__ hist, const uint32_t *__restrict__ ids,
         for (uint32_t r = begin + lane; r < end; r += kWarp) {
             const uint32_t e = ids[r];
             if (e < experts) atomicAdd(&h[e], 1u);
-            else atomicExch(error_flag, 1u);          // invalid route id
+            else {                                     // invalid route id
+                atomicExch(error_flag, 1u);
+                g_dispatch_status = 2u;
+            }
         }
         __syncwarp();
         for (uint32_t e = lane; e < experts; e += kWarp) {
@@ -125,6 +133,21 @@ route_place_kernel(uint32_t *__restrict__ sorted_route, uint32_t *__restrict__ s
 
 }  // namespace
 
+uint32_t k3_dispatch_status() {
+    uint32_t v = 0xffffffffu;
+    if (cudaMemcpyFromSymbol(&v, g_dispatch_status, sizeof(v)) != cudaSuccess) (void)cudaGetLastError();
+    return v;
+}
+
+bool k3_dispatch_status_clear() {
+    const uint32_t zero = 0u;
+    if (cudaMemcpyToSymbol(g_dispatch_status, &zero, sizeof(zero)) != cudaSuccess) {
+        (void)cudaGetLastError();
+        return false;
+    }
+    return true;
+}
+
 extern "C" size_t k3_moe_dispatch_workspace_bytes(uint32_t tokens, uint32_t top_k,
                                                   uint32_t experts) {
     const uint64_t routes = (uint64_t)tokens * top_k;
@@ -195,8 +218,8 @@ static __device__ __align__(256) unsigned char g_dispatch_scratch[kNoAllocScratc
 
 namespace {
 
-constexpr int kMaxDevices = 64;
-void *g_scratch_address[kMaxDevices] = {};   // device address of g_dispatch_scratch, per GPU
+// device address of g_dispatch_scratch per GPU; several host threads may make the first call
+std::atomic<void *> g_scratch_address[kMaxDevices];
 
 void set_error(char *error, size_t error_size, const char *message) {
     if (!error || error_size == 0) return;
@@ -214,16 +237,16 @@ void *scratch_for_current_device(char *error, size_t error_size) {
         set_error(error, error_size, "no current CUDA device (or ordinal >= 64)");
         return nullptr;
     }
-    if (g_scratch_address[device] == nullptr) {
-        void *address = nullptr;
+    void *address = g_scratch_address[device].load(std::memory_order_acquire);
+    if (address == nullptr) {
         if (cudaGetSymbolAddress(&address, g_dispatch_scratch) != cudaSuccess || !address) {
             (void)cudaGetLastError();
             set_error(error, error_size, "cudaGetSymbolAddress failed for the dispatch scratch");
             return nullptr;
         }
-        g_scratch_address[device] = address;
+        g_scratch_address[device].store(address, std::memory_order_release);   // same value from every thread
     }
-    return g_scratch_address[device];
+    return address;
 }
 
 }  // namespace
@@ -264,12 +287,20 @@ extern "C" bool k3_moe_dispatch_build_noalloc(void *offsets, void *sorted_route,
     const size_t smem = (size_t)kWarpsPerBlock * experts * sizeof(uint32_t);
     route_hist_kernel<<<blocks, kWarpsPerBlock * 32, smem, stream>>>(
         hist, (const uint32_t *)expert_ids, routes, experts, chunks, error_flag);
+    if (!launch_ok()) {
+        set_error(error, error_size, "histogram kernel launch failed");
+        return false;
+    }
     route_scan_kernel<<<1, kMaxExperts, 0, stream>>>(hist, (uint32_t *)offsets, experts, chunks);
+    if (!launch_ok()) {
+        set_error(error, error_size, "scan kernel launch failed");
+        return false;
+    }
     route_place_kernel<<<blocks, kWarpsPerBlock * 32, smem, stream>>>(
         (uint32_t *)sorted_route, (uint32_t *)sorted_token, (uint32_t *)inv_perm, hist,
         (const uint32_t *)offsets, (const uint32_t *)expert_ids, routes, experts, chunks, top_k);
     if (!launch_ok()) {
-        set_error(error, error_size, "kernel launch failed");
+        set_error(error, error_size, "placement kernel launch failed");
         return false;
     }
     return true;

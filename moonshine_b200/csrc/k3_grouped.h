@@ -76,6 +76,12 @@ bool k3_decode_mx_experts(const k3_moe_layer_desc *desc, const void *ids, void *
                           void *scratch, void *between, const k3_decode_tail *tail, cudaStream_t stream);
 uint32_t k3_decode_mx_status();
 uint32_t k3_decode_status();
+uint32_t k3_dispatch_status();
+bool k3_decode_status_clear();
+bool k3_decode_mx_status_clear();
+bool k3_dispatch_status_clear();
+bool k3_grouped_mx_status_clear();
+bool k3_status_words_clear();   // all of the above and the dense kernels' word   // 2: a dispatch saw an expert id >= experts
 
 // Block-scaled tensor-core grouped expert products for many rows
 // (k3_grouped_mx.cu).  `index` (u32 per row, or null) gathers rows_in, which then

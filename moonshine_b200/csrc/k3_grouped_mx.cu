@@ -575,15 +575,7 @@ bool launch(const Operands &op, const GmxArgs &args, cudaStream_t stream) {
         !map_2d(&maps.sfb, op.sfb, u8, args.rows, kb, kb, 16, BN, none, 16u)) {
         return false;
     }
-    static bool configured = false;
-    if (!configured) {
-        if (cudaFuncSetAttribute(grouped_mx_kernel<kE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 (int)kSmemBytes) != cudaSuccess) {
-            (void)cudaGetLastError();
-            return false;
-        }
-        configured = true;
-    }
+    if (!set_max_dynamic_smem((const void *)grouped_mx_kernel<kE>, kSmemBytes)) return false;
     grouped_mx_kernel<kE><<<sm_count(), kThreads, kSmemBytes, stream>>>(maps, args);
     return launch_ok();
 }
@@ -626,6 +618,15 @@ uint32_t k3_grouped_mx_status() {
     uint32_t v = 0xffffffffu;
     if (cudaMemcpyFromSymbol(&v, g_gmx_status, sizeof(v)) != cudaSuccess) (void)cudaGetLastError();
     return v;
+}
+
+bool k3_grouped_mx_status_clear() {
+    const uint32_t zero = 0u;
+    if (cudaMemcpyToSymbol(g_gmx_status, &zero, sizeof(zero)) != cudaSuccess) {
+        (void)cudaGetLastError();
+        return false;
+    }
+    return true;
 }
 
 size_t k3_grouped_mx_workspace_bytes(const k3_moe_layer_desc *d, uint32_t rows, uint32_t source_rows) {

@@ -558,15 +558,7 @@ bool launch_tc(const void *a0, const void *a1, const TcArgs &args, const void *b
                         CU_TENSOR_MAP_SWIZZLE_128B);
     if (!ok) return false;
     auto kernel = grouped_tc_kernel<kA, kE>;
-    static bool configured = false;
-    if (!configured) {
-        if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 (int)C::kSmemBytes) != cudaSuccess) {
-            (void)cudaGetLastError();
-            return false;
-        }
-        configured = true;
-    }
+    if (!set_max_dynamic_smem((const void *)kernel, C::kSmemBytes)) return false;
     kernel<<<sm_count(), kThreads, C::kSmemBytes, stream>>>(ma0, ma1, mb, args);
     return launch_ok();
 }
@@ -607,7 +599,54 @@ bool tc_shape_ok(uint32_t k, uint32_t rows) {
 extern "C" uint32_t k3_moe_device_status(void) {
     uint32_t v = 0xffffffffu;
     if (cudaMemcpyFromSymbol(&v, g_tc_status, sizeof(v)) != cudaSuccess) (void)cudaGetLastError();
-    return v | k3_decode_mx_status() | k3_decode_status() | k3_grouped_mx_status();
+    return v | k3_decode_mx_status() | k3_decode_status() | k3_grouped_mx_status() | k3_dispatch_status();
+}
+
+bool k3_status_words_clear() {
+    const uint32_t zero = 0u;
+    bool ok = cudaMemcpyToSymbol(g_tc_status, &zero, sizeof(zero)) == cudaSuccess;
+    if (!ok) (void)cudaGetLastError();
+    ok = k3_decode_status_clear() && ok;
+    ok = k3_decode_mx_status_clear() && ok;
+    ok = k3_dispatch_status_clear() && ok;
+    ok = k3_grouped_mx_status_clear() && ok;
+    return ok;
+}
+
+extern "C" bool k3_moe_device_status_clear(void) {
+    return k3_status_words_clear();
+}
+
+namespace {
+
+// One warp waits on an mbarrier that nobody arrives on, with a limit given by the
+// caller; when the wait gives up it takes the same way out as the product kernels
+// (abort flag in shared memory -> status word), touches no tensor memory and returns.
+__global__ void bounded_wait_selftest_kernel(unsigned long long limit_ns, uint32_t *gave_up) {
+    __shared__ uint64_t bar;
+    __shared__ uint32_t abort_word;
+    volatile uint32_t *abort_flag = &abort_word;
+    if (threadIdx.x == 0) {
+        *abort_flag = 0u;
+        mbar_init(&bar, 1);
+        fence_barrier_init();
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const bool ok = mbar_wait(&bar, 0u, abort_flag, limit_ns);
+        if (gave_up) *gave_up = ok ? 0u : 1u;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0 && *abort_flag != 0u) atomicExch(&g_tc_status, 1u);
+}
+
+}  // namespace
+
+extern "C" bool k3_moe_selftest_bounded_wait(uint32_t limit_us, void *gave_up, void *stream) {
+    if (limit_us == 0u || limit_us > 1000000u) return false;          // at most one second
+    bounded_wait_selftest_kernel<<<1, 32, 0, (cudaStream_t)stream>>>((unsigned long long)limit_us * 1000ull,
+                                                                     (uint32_t *)gave_up);
+    return launch_ok();
 }
 
 bool k3_grouped_dense_bf16_f32(void *out, const void *weights, const void *x, uint32_t tokens,

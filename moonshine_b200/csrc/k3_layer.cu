@@ -223,16 +223,6 @@ Workspace carve(const k3_moe_layer_desc *d, uint32_t tokens, void *base) {
     return w;
 }
 
-bool set_smem(const void *kernel, size_t smem) {
-    if (smem <= 48 * 1024) return true;
-    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) !=
-        cudaSuccess) {
-        (void)cudaGetLastError();
-        return false;
-    }
-    return true;
-}
-
 // SIMT/mma.sync grouped path: any row count, weights re-streamed per row pair.
 bool launch_grouped_rows(const k3_moe_layer_desc *d, void *rows_out, void *act,
                          const void *rows_in, const uint32_t *offsets, const uint32_t *rank_ids,
@@ -255,7 +245,7 @@ bool launch_grouped_rows(const k3_moe_layer_desc *d, void *rows_out, void *act,
     a.k_pad = (a.k + 127u) / 128u * 128u;
     a.in_shared_row = shared_row ? 1u : 0u;
     size_t smem = gemv_smem_bytes(a.k_pad);
-    if (!set_smem((const void *)grouped_rows_kernel<true>, smem)) return false;
+    if (!set_max_dynamic_smem((const void *)grouped_rows_kernel<true>, smem)) return false;
     dim3 grid((d->expert_hidden + 15u) / 16u, groups_y);
     grouped_rows_kernel<true><<<grid, kGemvThreads, smem, stream>>>(
         (uint16_t *)act, (const uint16_t *)rows_in, a);
@@ -268,7 +258,7 @@ bool launch_grouped_rows(const k3_moe_layer_desc *d, void *rows_out, void *act,
     a.k_pad = (a.k + 127u) / 128u * 128u;
     a.in_shared_row = 0u;
     smem = gemv_smem_bytes(a.k_pad);
-    if (!set_smem((const void *)grouped_rows_kernel<false>, smem)) return false;
+    if (!set_max_dynamic_smem((const void *)grouped_rows_kernel<false>, smem)) return false;
     grid = dim3((d->hidden + 31u) / 32u, groups_y);
     grouped_rows_kernel<false><<<grid, kGemvThreads, smem, stream>>>(
         (uint16_t *)rows_out, (const uint16_t *)act, a);
@@ -558,6 +548,32 @@ extern "C" bool k3_moe_block_forward(const k3_moe_layer_desc *d, void *out, cons
     return k3_rocm_rms_norm_bf16(normed, hidden_in, norm_weight, tokens, d->hidden, epsilon, stream) &&
            layer_forward_impl(d, out, normed, tokens, inner, inner_bytes, nullptr, nullptr, nullptr, hidden_in,
                               stream);
+}
+
+// Device-timed phase ledger under the reference's field names.
+extern "C" bool k3_moe_phase_stats_add(k3_moe_phase_stats *stats, void *const *events) {
+    if (!stats || !events) return false;
+    for (int i = 0; i < 6; i++) {
+        if (!events[i]) return false;
+    }
+    if (cudaEventSynchronize((cudaEvent_t)events[5]) != cudaSuccess) {
+        (void)cudaGetLastError();
+        return false;
+    }
+    float ms[5];
+    for (int i = 0; i < 5; i++) {
+        if (cudaEventElapsedTime(&ms[i], (cudaEvent_t)events[i], (cudaEvent_t)events[i + 1]) != cudaSuccess) {
+            (void)cudaGetLastError();
+            return false;
+        }
+    }
+    stats->router_seconds += 1e-3 * ms[0];
+    stats->shared_expert_seconds += 1e-3 * ms[1];
+    stats->routed_index_seconds += 1e-3 * ms[2];
+    stats->routed_expert_pipeline_seconds += 1e-3 * ms[3];
+    stats->moe_tail_seconds += 1e-3 * (ms[1] + ms[4]);
+    stats->layer_passes += 1u;
+    return true;
 }
 
 // Thin wrappers so a host language without CUDA runtime bindings can own the

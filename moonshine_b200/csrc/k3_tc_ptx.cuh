@@ -49,14 +49,15 @@ K3_DEVINL unsigned long long global_timer_ns() {
     return t;
 }
 
-K3_DEVINL bool mbar_wait(uint64_t *bar, uint32_t parity, volatile uint32_t *abort_flag) {
+K3_DEVINL bool mbar_wait(uint64_t *bar, uint32_t parity, volatile uint32_t *abort_flag,
+                         unsigned long long limit_ns = kWaitLimitNs) {
     if (mbar_try_wait(bar, parity)) return true;
     const unsigned long long t0 = global_timer_ns();
     for (uint32_t spin = 1;; spin++) {
         if (mbar_try_wait(bar, parity)) return true;
         if ((spin & 63u) == 0u) {
             if (*abort_flag != 0u) return false;
-            if (global_timer_ns() - t0 > kWaitLimitNs) break;
+            if (global_timer_ns() - t0 > limit_ns) break;
         }
     }
     *abort_flag = 1u;

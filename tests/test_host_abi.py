@@ -78,4 +78,10 @@ def test_invalid_arguments_return_false_without_a_device(native):
     assert lib.k3_rocm_add_bf16(p, p, None, 8, None) is False
     assert lib.k3_rocm_gather_rows_bf16(p, p, p, 0, 64, None) is False
     assert lib.k3_moe_layer_workspace_bytes(None, 4) == 0
+    # k3_static_store.cu:315-369: null weight, null tensor, raw kind
+    assert lib.k3_static_weight_gemv_bf16(None, p, p, None) is False
+    empty = native.StaticWeight()
+    assert lib.k3_static_weight_gemm_bf16(empty, p, p, 4, None) is False
+    assert lib.k3_moe_selftest_bounded_wait(0, None, None) is False
+    assert lib.k3_moe_phase_stats_add(None, None) is False
     assert lib.k3_moe_version().startswith(b"k3moe")
