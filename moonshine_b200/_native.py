@@ -148,6 +148,19 @@ SIGNATURES = {
     "k3_moe_event_create": (vp, []),
     "k3_moe_event_destroy": (None, [vp]),
     "k3_moe_event_elapsed_ms": (f32, [vp, vp]),
+    # expert parallel over NCCL
+    "k3_moe_ep_unique_id": (C.c_bool, [vp, C.c_char_p, sz]),
+    "k3_moe_ep_create": (C.c_bool, [C.POINTER(vp), vp, C.c_int, C.c_int, C.c_char_p, sz]),
+    "k3_moe_ep_destroy": (None, [vp]),
+    "k3_moe_ep_rank": (C.c_int, [vp]),
+    "k3_moe_ep_world": (C.c_int, [vp]),
+    "k3_moe_ep_plan": (C.c_bool, [_U32P, u32, u32, u32, _U32P, _U32P, _U32P, _U32P, _U32P, _U32P]),
+    "k3_moe_ep_workspace_bytes": (sz, [vp, _DP, u32, u32]),
+    "k3_moe_ep_layer_forward": (C.c_bool, [vp, _DP, vp, vp, u32, u32, vp, sz, vp, vp, C.c_char_p, sz, vp]),
+    "k3_moe_ep_last_pass": (C.c_bool, [vp, C.POINTER(f32), C.POINTER(f32), _U32P]),
+    "k3_moe_ep_decode_workspace_bytes": (sz, [vp, _DP]),
+    "k3_moe_ep_decode": (C.c_bool, [vp, _DP, vp, vp, vp, vp, sz, vp]),
+    "k3_moe_ep_decode_stack": (C.c_bool, [vp, C.POINTER(_DP), u32, vp, vp, vp, f32, vp, sz, vp]),
     "k3_synth_fill_bytes": (C.c_bool, [vp, u64, u64, u64, u32, u32, vp]),
     "k3_synth_fill_int8": (C.c_bool, [vp, u64, u64, u64, vp]),
     "k3_synth_fill_uniform": (C.c_bool, [vp, u64, u64, u64, f32, f32, i32, vp]),

@@ -631,7 +631,7 @@ bool k3_decode_supported(const k3_moe_layer_desc *d) {
 bool k3_decode_layer(const k3_moe_layer_desc *d, const void *x, void *logits, void *ids,
                      void *weights, void *sh_gate, void *sh_up, void *sh_act, void *sh_out,
                      void *act, void *rows_out, void *out, const void *residual, void *scratch,
-                     size_t scratch_bytes, void *const *events, cudaStream_t stream) {
+                     size_t scratch_bytes, void *const *events, cudaStream_t stream, bool combine) {
     // optional phase events: [1], [2] after the front kernel, [3] after gate/up,
     // [4] after down (the caller records [0] before and [5] after the call)
     auto mark = [&](int index) {
@@ -682,8 +682,8 @@ bool k3_decode_layer(const k3_moe_layer_desc *d, const void *x, void *logits, vo
     // that depends on the routing.  With every expert in this table there is no
     // combine launch either: the down kernel's epilogue warps and the shared-down
     // blocks count arrivals per 32 output columns and the last one adds them up.
-    const bool fused_tail = mx && d->local_expert_first == 0u && d->local_expert_count == d->expert_count &&
-                            d->hidden % 32u == 0u;
+    const bool fused_tail = combine && mx && d->local_expert_first == 0u &&
+                            d->local_expert_count == d->expert_count && d->hidden % 32u == 0u;
     static std::atomic<uint32_t> tail_epoch{1};
     if (fused_tail) {
         a.tail.out = (uint16_t *)out;
@@ -758,7 +758,7 @@ bool k3_decode_layer(const k3_moe_layer_desc *d, const void *x, void *logits, vo
             (void)cudaGetLastError();
             return false;
         }
-        if (fused_tail) return true;
+        if (fused_tail || !combine) return true;
         return k3_moe_combine_residual(out, rows_out, nullptr, weights, d->shared_hidden ? sh_out : nullptr,
                                        residual, 1u, d->top_k, d->hidden, stream);
     }
@@ -770,6 +770,7 @@ bool k3_decode_layer(const k3_moe_layer_desc *d, const void *x, void *logits, vo
     if (!set_max_dynamic_smem((const void *)decode_down_kernel, smem)) return false;
     decode_down_kernel<<<sms, kDecodeThreads, smem, stream>>>(a);
     if (!launch_ok() || !mark(4)) return false;
+    if (!combine) return true;
     return k3_moe_combine_residual(out, rows_out, nullptr, weights, d->shared_hidden ? sh_out : nullptr,
                                    residual, 1u, d->top_k, d->hidden, stream);
 }

@@ -44,10 +44,14 @@ bool k3_grouped_tc_experts(const k3_moe_layer_desc *desc, void *rows_out, void *
 // plus `residual` bf16 [hidden] when it is not null).
 // All other buffers are caller-owned scratch.
 bool k3_decode_supported(const k3_moe_layer_desc *desc);
+// With combine == false the call ends after the expert rows (rows_out [top_k, hidden] in
+// rank order, rows of experts outside this table untouched), ids, weights and the shared
+// expert's output are complete on `stream`; `out` and `residual` are then unused.
 bool k3_decode_layer(const k3_moe_layer_desc *desc, const void *x, void *logits, void *ids,
                      void *weights, void *sh_gate, void *sh_up, void *sh_act, void *sh_out,
                      void *act, void *rows_out, void *out, const void *residual, void *scratch,
-                     size_t scratch_bytes, void *const *events, cudaStream_t stream);
+                     size_t scratch_bytes, void *const *events, cudaStream_t stream,
+                     bool combine = true);
 
 // Block-scaled tensor-core expert products for one token (k3_decode_mx.cu).
 bool k3_decode_mx_supported(const k3_moe_layer_desc *desc);

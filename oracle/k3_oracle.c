@@ -21,6 +21,14 @@
 
 enum { K3O_LANES = 256, K3O_MXFP4_KERNEL_LANES = 128 };
 
+void k3o_set_threads(int threads) {
+#ifdef _OPENMP
+    if (threads > 0) omp_set_num_threads(threads);
+#else
+    (void)threads;
+#endif
+}
+
 int k3o_thread_count(void) {
 #ifdef _OPENMP
     return omp_get_max_threads();
@@ -105,12 +113,20 @@ void k3o_bf16_gemm(float *output_f32, uint16_t *output_bf16,
             const float *xv = x + (uint64_t)v * columns;
             float partial[K3O_LANES];
             memset(partial, 0, sizeof(partial));
-            /* lane t owns columns t, t+256, ... in ascending order */
-            for (uint32_t column = 0; column < columns; column++) {
-                uint32_t lane = column % K3O_LANES;
-                partial[lane] =
-                    fmaf(k3o_bf16_to_float(w[column]), xv[column],
-                         partial[lane]);
+            /* lane t owns columns t, t+256, ... in ascending order (written as
+             * blocks of 256 columns so that the compiler can use vector FMAs
+             * across lanes; each lane's own order is unchanged) */
+            uint32_t column = 0;
+            for (; column + K3O_LANES <= columns; column += K3O_LANES) {
+                for (uint32_t lane = 0; lane < K3O_LANES; lane++) {
+                    partial[lane] =
+                        fmaf(k3o_bf16_to_float(w[column + lane]),
+                             xv[column + lane], partial[lane]);
+                }
+            }
+            for (uint32_t lane = 0; column < columns; column++, lane++) {
+                partial[lane] = fmaf(k3o_bf16_to_float(w[column]), xv[column],
+                                     partial[lane]);
             }
             float sum = tree_reduce(partial, K3O_LANES);
             if (output_f32) output_f32[(uint64_t)v * rows + row] = sum;
@@ -154,8 +170,14 @@ void k3o_mxfp4_gemm(uint16_t *output, const uint8_t *packed,
                 const float *xv = x + (uint64_t)v * columns;
                 float partial[K3O_LANES];
                 memset(partial, 0, sizeof(partial));
-                for (uint32_t column = 0; column < columns; column++) {
-                    uint32_t lane = column % K3O_LANES;
+                uint32_t column = 0;
+                for (; column + K3O_LANES <= columns; column += K3O_LANES) {
+                    for (uint32_t lane = 0; lane < K3O_LANES; lane++) {
+                        partial[lane] = fmaf(decoded[column + lane],
+                                             xv[column + lane], partial[lane]);
+                    }
+                }
+                for (uint32_t lane = 0; column < columns; column++, lane++) {
                     partial[lane] =
                         fmaf(decoded[column], xv[column], partial[lane]);
                 }
@@ -643,4 +665,28 @@ void k3o_xorshift_unit(uint32_t *state, float *out, uint64_t count) {
         out[i] = (float)(s & 0x00ffffffu) / (float)0x01000000u;
     }
     *state = s;
+}
+
+/* The seeded byte streams of the synthetic layers (moonshine_b200/synth.py,
+ * raw_bytes / bytes_uniform): byte j of 8-byte chunk c is bits [8j, 8j+8) of the
+ * splitmix64 finaliser of (key * golden + golden + c); low + floor(b*span/256). */
+void k3o_synth_bytes(uint8_t *out, uint64_t count, uint64_t key,
+                     uint64_t first, uint32_t low, uint32_t span) {
+    const uint64_t golden = 0x9E3779B97F4A7C15ull;
+    const uint64_t base = key * golden + golden;
+    const uint64_t first_chunk = first / 8u;
+    const uint64_t chunks = (count + 7u) / 8u;
+#pragma omp parallel for schedule(static)
+    for (int64_t c = 0; c < (int64_t)chunks; c++) {
+        uint64_t z = (first_chunk + (uint64_t)c) + base;
+        z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+        z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+        z = z ^ (z >> 31);
+        for (uint32_t j = 0; j < 8u; j++) {
+            const uint64_t i = (uint64_t)c * 8u + j;
+            if (i >= count) break;
+            const uint32_t b = (uint32_t)((z >> (8u * j)) & 0xffu);
+            out[i] = (uint8_t)(low + ((b * span) >> 8));
+        }
+    }
 }

@@ -181,6 +181,15 @@ int k3o_thread_count(void);
  * (state & 0x00ffffff) / 2^24 after each update; *state carries on. */
 void k3o_xorshift_unit(uint32_t *state, float *out, uint64_t count);
 
+/* Seeded byte stream of the synthetic layers (mirror of synth.bytes_uniform);
+ * `first` is a multiple of 8. */
+void k3o_synth_bytes(uint8_t *out, uint64_t count, uint64_t key,
+                     uint64_t first, uint32_t low, uint32_t span);
+
+/* Number of OpenMP threads the parallel loops use from now on (the timed CPU
+ * baseline sets it itself instead of inheriting OMP_NUM_THREADS). */
+void k3o_set_threads(int threads);
+
 #ifdef __cplusplus
 }
 #endif

@@ -62,6 +62,10 @@ def _u16(a):
     return a
 
 
+def set_threads(threads: int) -> None:
+    lib().k3o_set_threads(C.c_int(threads))
+
+
 def thread_count() -> int:
     return int(lib().k3o_thread_count())
 
@@ -259,6 +263,65 @@ def moe_layer(weights: dict, x: np.ndarray, expert_subset: int = 0):
     products = lib().k3o_moe_layer(_p(out), _p(ids), _p(w), _p(logits), C.byref(layer), _p(x),
                                    C.c_uint32(t), C.c_uint32(expert_subset))
     return out, ids, w, logits, int(products)
+
+
+def synth_bytes(key: int, count: int, low: int = 0, span: int = 256, first: int = 0) -> np.ndarray:
+    """The seeded byte stream ``synth.bytes_uniform(key, count, low, span, first)``,
+    generated in C (whole experts of the full-size layers in milliseconds)."""
+    assert first % 8 == 0
+    out = np.empty(count, np.uint8)
+    lib().k3o_synth_bytes(_p(out), C.c_uint64(count), C.c_uint64(key), C.c_uint64(first),
+                          C.c_uint32(low), C.c_uint32(span))
+    return out
+
+
+def expert_tensors(cfg: dict, seed: int, expert: int) -> dict:
+    """The six tensors of one expert of a synthetic layer, generated on the host from
+    the layer's seeded streams (equal to the slices of ``synth.make_layer``)."""
+    from moonshine_b200 import synth
+    out = {}
+    for name, (tp, ts, rows, cols) in synth.expert_tensor_specs(cfg).items():
+        per_p, per_s = rows * cols // 2, rows * cols // 32
+        out[name + "_packed"] = synth_bytes(synth.stream_key(seed, tp), per_p, first=expert * per_p
+                                            ).reshape(rows, cols // 2)
+        out[name + "_scales"] = synth_bytes(synth.stream_key(seed, ts), per_s, cfg["scale_low"],
+                                            cfg["scale_span"], first=expert * per_s).reshape(rows, cols // 32)
+    return out
+
+
+def moe_layer_tokens(cfg: dict, seed: int, x: np.ndarray, weights: dict | None = None):
+    """The layer's answer for a few token rows ``x`` [n, d] of a synthetic layer too large
+    to hold on the host: only the experts those tokens select are generated.  Every
+    operator is the one ``moe_layer`` uses, in the same order, so the result equals the
+    rows ``moe_layer`` would give.  ``weights`` = ``synth.make_layer(cfg, seed, experts=False)``.
+    Returns (out bf16 [n, d], ids, route weights, logits)."""
+    from moonshine_b200 import synth
+    if weights is None:
+        weights = synth.make_layer(cfg, seed, experts=False)
+    d, i, e, k, s = cfg["hidden"], cfg["expert_hidden"], cfg["experts"], cfg["top_k"], cfg["shared_hidden"]
+    x = _u16(x).reshape(-1, d)
+    n = x.shape[0]
+    logits = bf16_gemm(weights["router_weight"], x, e, d)
+    ids, wts = router_topk(logits, weights["router_bias"], k, cfg["route_scale"])
+    offsets, toks, slots = group_routes(ids, e)
+    outputs = np.zeros((n * k, d), np.uint16)
+    for ex in np.unique(ids):
+        lo, hi = int(offsets[ex]), int(offsets[ex + 1])
+        t = expert_tensors(cfg, seed, int(ex))
+        rows = x[toks[lo:hi]]
+        gate = mxfp4_gemm(t["w1_packed"], t["w1_scales"], rows, i, d)
+        up = mxfp4_gemm(t["w3_packed"], t["w3_scales"], rows, i, d)
+        act = activation(gate, up, cfg["activation"], cfg["beta"], cfg["linear_beta"])
+        outputs[slots[lo:hi]] = mxfp4_gemm(t["w2_packed"], t["w2_scales"], act, d, i)
+    out = weighted_sum(outputs, wts, n, k, d)
+    if s:
+        q, st = cfg["q8_block"], cfg["q8_scale_type"]
+        sg = q8_gemm(weights["shared_gate_q"], weights["shared_gate_s"], x, s, d, q, st)
+        su = q8_gemm(weights["shared_up_q"], weights["shared_up_s"], x, s, d, q, st)
+        sa = activation(sg, su, cfg["activation"], cfg["beta"], cfg["linear_beta"])
+        so = q8_gemm(weights["shared_down_q"], weights["shared_down_s"], sa, d, s, q, st)
+        out = add(out, so)
+    return out, ids, wts, logits
 
 
 class XorShift:

@@ -8,7 +8,7 @@ import re
 import pytest
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
-DECL = re.compile(r"^(?:bool|size_t|float|void|uint32_t|uint64_t|void \*|const char \*)\s*(k3_[a-z0-9_]+)\s*\(", re.M)
+DECL = re.compile(r"^(?:bool|size_t|float|void|int|uint32_t|uint64_t|void \*|const char \*)\s*(k3_[a-z0-9_]+)\s*\(", re.M)
 
 
 @pytest.fixture(scope="module")
