@@ -2,14 +2,21 @@
 """Benchmark of the routed-MoE layer (synthetic data, seeded).
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl native|reference]
-                    [--workload prefill8k|prefill512|decode|latent8k]
+                    [--workload prefill8k|prefill512|decode|latent8k|stress|decode_stack]
 
 One step = one pass of the layer over one batch.  Default workload: layer-major
 prefill of 8192 tokens with a Zipf-skewed router bias (the configuration the
 headline metric is quoted on); at N > 1 the same 8192 tokens are split over the
 ranks and the 896 experts are sharded expert-parallel (strong scaling).  The
 one-token decode figure and its HBM roofline are reported in the same line
-under "decode".  Rank 0 prints one JSON line.
+under "decode" (at N > 1: the token replicated, experts sharded, one all-reduce of
+the expert rows), the 512-token prefill under "prefill512" (N = 1), and a parity
+check against the CPU oracle on a small layer under "parity" (every N).  Rank 0
+prints one JSON line.
+
+Other workloads: ``stress`` sweeps token counts 1..16384 with four always-selected
+experts, duplicated router rows (exact ties) and E8M0 scale bytes 0..127;
+``decode_stack`` decodes tokens one at a time through 92 layer positions.
 
 --impl reference times the CPU restatement of the reference's host path
 (oracle/) on the host cores, on a bounded sample of the same workload.
@@ -127,65 +134,103 @@ class ClockSampler:
 
 
 # ------------------------------------------------------------- CPU baseline
-def cpu_baseline(cfg: dict, tokens: int, seed: int = 0, budget_s: float = 12.0) -> dict:
-    """Times the CPU oracle on a bounded sample of the workload and extrapolates
-    to tokens/s.  Prefill: `sample_experts` whole experts with the number of rows
-    an average expert receives, plus router / shared expert / combine on
-    `sample_tokens` tokens.  Decode: one token's 16 experts in full."""
+def host_threads() -> int:
+    """Hardware threads this process may run on (the CPU arm uses all of them)."""
+    try:
+        return len(os.sched_getaffinity(0))
+    except AttributeError:
+        return os.cpu_count() or 1
+
+
+def _expert_seconds(o, cfg, seed, expert, rows, x_rows):
+    """Seconds of gate, up, activation and down for `rows` rows on one expert."""
+    d, i = cfg["hidden"], cfg["expert_hidden"]
+    t = o.expert_tensors(cfg, seed, expert)
+    xr = x_rows[:rows]
+    begin = time.perf_counter()
+    g = o.mxfp4_gemm(t["w1_packed"], t["w1_scales"], xr, i, d)
+    u = o.mxfp4_gemm(t["w3_packed"], t["w3_scales"], xr, i, d)
+    a = o.activation(g, u, cfg["activation"], cfg["beta"], cfg["linear_beta"])
+    o.mxfp4_gemm(t["w2_packed"], t["w2_scales"], a, d, i)
+    return time.perf_counter() - begin
+
+
+def cpu_baseline(cfg: dict, tokens: int, seed: int = 0, strata: int = 8, full: bool = False) -> dict:
+    """Times the CPU oracle (the restatement of the reference's host path) on all host
+    threads, which it sets itself.
+
+    One token, or ``full``: the whole workload, nothing extrapolated.
+    Otherwise a bounded sample: router, top-k, dispatch, shared expert and combine on up to
+    256 tokens; the routing of those tokens also gives each expert's share of the routes.
+    The experts are cut into ``strata`` groups of equal route count (sorted by load) and the
+    median expert of each group is timed with the number of rows it would receive in the
+    full batch; expert time of the batch = routes x mean over groups of (seconds / rows).
+    The expert part is measured twice and both figures are reported."""
     from oracle import k3_oracle as o
-    d, i, e, k, s = cfg["hidden"], cfg["expert_hidden"], cfg["experts"], cfg["top_k"], cfg["shared_hidden"]
+    o.set_threads(host_threads())
+    d, e, k, s = cfg["hidden"], cfg["experts"], cfg["top_k"], cfg["shared_hidden"]
     cores = o.thread_count()
-    rows_per_expert = max(1, round(tokens * k / e)) if tokens > 1 else 1
-    sample_experts = 2 if tokens > 1 else k
-    key = lambda tag: synth.stream_key(seed, tag)
-    per13, per13s = i * d // 2, i * d // 32
-    per2, per2s = d * i // 2, d * i // 32
-    xs = synth.activations(seed, max(rows_per_expert, 8), d)
-    t_expert = 0.0
-    done_routes = 0
-    t0 = time.perf_counter()
-    for ex in range(sample_experts):
-        w1p = synth.bytes_uniform(key(synth.TAG_W1P), per13, first=ex * per13)
-        w1s = synth.bytes_uniform(key(synth.TAG_W1S), per13s, cfg["scale_low"], cfg["scale_span"], first=ex * per13s)
-        w3p = synth.bytes_uniform(key(synth.TAG_W3P), per13, first=ex * per13)
-        w3s = synth.bytes_uniform(key(synth.TAG_W3S), per13s, cfg["scale_low"], cfg["scale_span"], first=ex * per13s)
-        w2p = synth.bytes_uniform(key(synth.TAG_W2P), per2, first=ex * per2)
-        w2s = synth.bytes_uniform(key(synth.TAG_W2S), per2s, cfg["scale_low"], cfg["scale_span"], first=ex * per2s)
-        xr = xs[:rows_per_expert]
-        t = time.perf_counter()
-        g = o.mxfp4_gemm(w1p, w1s, xr, i, d)
-        u = o.mxfp4_gemm(w3p, w3s, xr, i, d)
-        a = o.activation(g, u, cfg["activation"], cfg["beta"], cfg["linear_beta"])
-        o.mxfp4_gemm(w2p, w2s, a, d, i)
-        t_expert += time.perf_counter() - t
-        done_routes += rows_per_expert
-        if time.perf_counter() - t0 > budget_s and ex >= 1:
-            break
-    per_route = t_expert / done_routes
-    # router + top-k + shared expert + combine on a token sample
-    sample_tokens = 1 if tokens == 1 else 32
     w = synth.make_layer(cfg, seed, experts=False)
-    xt = synth.activations(seed, sample_tokens, d)
-    t = time.perf_counter()
+    t_all = time.perf_counter()
+    if tokens == 1 or full:
+        x = synth.activations(seed, tokens, d)
+        begin = time.perf_counter()
+        o.moe_layer_tokens(cfg, seed, x, w)
+        seconds = time.perf_counter() - begin
+        generate = time.perf_counter()
+        for ex in range(2):                           # generating an expert's tensors is not the workload
+            o.expert_tensors(cfg, seed, ex)
+        per_expert_gen = (time.perf_counter() - generate) / 2
+        logits = o.bf16_gemm(w["router_weight"], x, e, d)
+        ids, _ = o.router_topk(logits, w["router_bias"], k, cfg["route_scale"])
+        seconds -= per_expert_gen * len(np.unique(ids))
+        return {"value": tokens / seconds, "unit": UNIT, "cores": cores, "kind": "port",
+                "sample": f"the whole workload ({tokens} token(s), every selected expert), not extrapolated",
+                "seconds": round(time.perf_counter() - t_all, 2)}
+    sample_tokens = min(tokens, 256)
+    xt = synth.activations(seed, tokens, d)[:: max(1, tokens // sample_tokens)][:sample_tokens]
+    begin = time.perf_counter()
     logits = o.bf16_gemm(w["router_weight"], xt, e, d)
     ids, wts = o.router_topk(logits, w["router_bias"], k, cfg["route_scale"])
     o.group_routes(ids, e)
+    shared_tokens = min(sample_tokens, 32)
+    rest_router = (time.perf_counter() - begin) / sample_tokens
+    begin = time.perf_counter()
+    xs = np.ascontiguousarray(xt[:shared_tokens])
     if s:
-        sg = o.q8_gemm(w["shared_gate_q"], w["shared_gate_s"], xt, s, d, cfg["q8_block"], cfg["q8_scale_type"])
-        su = o.q8_gemm(w["shared_up_q"], w["shared_up_s"], xt, s, d, cfg["q8_block"], cfg["q8_scale_type"])
+        sg = o.q8_gemm(w["shared_gate_q"], w["shared_gate_s"], xs, s, d, cfg["q8_block"], cfg["q8_scale_type"])
+        su = o.q8_gemm(w["shared_up_q"], w["shared_up_s"], xs, s, d, cfg["q8_block"], cfg["q8_scale_type"])
         sa = o.activation(sg, su, cfg["activation"], cfg["beta"], cfg["linear_beta"])
         so = o.q8_gemm(w["shared_down_q"], w["shared_down_s"], sa, d, s, cfg["q8_block"], cfg["q8_scale_type"])
-    fake = np.zeros((sample_tokens * k, d), np.uint16)
-    routed = o.weighted_sum(fake, wts, sample_tokens, k, d)
+    routed = o.weighted_sum(np.zeros((shared_tokens * k, d), np.uint16), wts[:shared_tokens], shared_tokens, k, d)
     if s:
         o.add(routed, so)
-    per_token_rest = (time.perf_counter() - t) / sample_tokens
-    per_token = per_route * k + per_token_rest
+    rest_tail = (time.perf_counter() - begin) / shared_tokens
+    # expected rows per expert in the full batch, strata of equal route count
+    share = np.bincount(ids.ravel(), minlength=e).astype(np.float64) / ids.size
+    rows_full = share * tokens * k
+    order = np.argsort(rows_full, kind="stable")
+    cum = np.cumsum(rows_full[order]) / max(rows_full.sum(), 1.0)
+    picks = []
+    for j in range(strata):
+        pos = int(np.searchsorted(cum, (j + 0.5) / strata))
+        ex = int(order[min(pos, e - 1)])
+        picks.append((ex, max(1, int(round(rows_full[ex])))))
+    x_rows = synth.activations(seed + 1, max(r for _, r in picks), d)
+    runs = []
+    for _ in range(2):
+        per_row = [(_expert_seconds(o, cfg, seed, ex, rows, x_rows) / rows) for ex, rows in picks]
+        runs.append(float(np.mean(per_row)))
+    per_route = float(np.mean(runs))
+    per_token = per_route * k + rest_router + rest_tail
+    values = [1.0 / (r * k + rest_router + rest_tail) for r in runs]
     return {"value": 1.0 / per_token, "unit": UNIT, "cores": cores, "kind": "port",
-            "sample": (f"{done_routes // rows_per_expert} experts x {rows_per_expert} rows "
-                       f"(gate, up, activation, down) + router/top-k/dispatch/shared/combine on "
-                       f"{sample_tokens} tokens; per-token time = 16 x per-route + rest; extrapolated"),
-            "seconds": round(time.perf_counter() - t0, 2)}
+            "sample": (f"{strata} experts at the medians of {strata} equal-route strata of the batch's own load "
+                       f"(rows {[r for _, r in picks]}), gate/up/activation/down; router, top-k, dispatch on "
+                       f"{sample_tokens} tokens, shared expert and combine on {shared_tokens}; tokens/s = 1 / "
+                       f"(16 x mean seconds per route + the rest per token); extrapolated to {tokens} tokens"),
+            "repeat": {"values": values, "spread": abs(values[0] - values[1]) / max(values)},
+            "seconds": round(time.perf_counter() - t_all, 2)}
 
 
 # ------------------------------------------------------------ reference arm
@@ -193,10 +238,13 @@ def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
+    if args.workload in ("stress", "decode_stack", "latent8k"):
+        print(json.dumps({"impl": "reference", "unavailable": "the CPU arm times prefill8k, prefill512 and decode"}))
+        return
     cfg, tokens = workload_config(args.workload, args)
     values = []
     for step in range(args.warmup + args.steps):
-        r = cpu_baseline(cfg, tokens, budget_s=6.0)
+        r = cpu_baseline(cfg, tokens, full=args.workload in ("prefill512", "decode"))
         if step >= args.warmup:
             values.append(r)
     value = statistics.mean(v["value"] for v in values)
@@ -206,16 +254,25 @@ def run_reference(args):
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * tokens / value,
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
         "data": "synthetic",
-        "config": {"workload": args.workload, "tokens": tokens, "experts": cfg["experts"],
-                   "top_k": cfg["top_k"], "hidden": cfg["hidden"],
-                   "expert_hidden": cfg["expert_hidden"]},
+        "config": run_config(args, cfg, tokens, 1),
         "cpu_baseline": {"value": value, "unit": UNIT, "cores": last["cores"], "kind": "port",
-                         "sample": last["sample"]},
+                         "sample": last["sample"], "per_step_values": [v["value"] for v in values]},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "note": "CPU restatement of the reference's host MoE path (the reference's HIP build "
-                "cannot run here); throughput extrapolated from a bounded sample",
+                "cannot run here), all host threads",
     }
     print(json.dumps(line))
+
+
+def run_config(args, cfg, tokens, world):
+    """The `config` object of a bench line: the same keys in both arms."""
+    return {"workload": args.workload, "tokens": tokens, "experts": cfg["experts"],
+            "top_k": cfg["top_k"], "hidden": cfg["hidden"], "expert_hidden": cfg["expert_hidden"],
+            "shared_hidden": cfg["shared_hidden"], "router_bias": cfg["bias_mode"],
+            "parallelism": (f"ep{world}: tokens data-parallel, experts sharded, exact rank-ordered combine"
+                            + (f" x {args.ep_pieces} pipelined row ranges" if args.ep_pieces > 1 else ""))
+            if world > 1 else "single",
+            "l2": "inputs larger than L2 (expert weights 20.96 GB per pass)"}
 
 
 # DRAM bytes per launch measured with ncu on these workloads (one-pass metrics,
@@ -235,15 +292,15 @@ def launches_per_step(tokens: int, shared: bool) -> int:
     return route + shared_k + dispatch + experts + combine
 
 
-def time_decode(layer, cfg, torch, iters: int = 40):
+def time_decode(call, cfg, device, torch, iters: int = 40):
     """One-token decode with a cold L2: distinct tokens round-robin and a buffer
     larger than L2 rewritten between iterations; each iteration timed by its own
-    pair of events on the launching stream."""
+    pair of events on the launching stream.  `call(x)` runs one token."""
     d = cfg["hidden"]
-    xs = torch.from_numpy(synth.activations(7, 8, d).view(np.int16)).to(layer.device).view(torch.bfloat16)
-    flush = torch.empty(2 * L2_BYTES, dtype=torch.uint8, device=layer.device)
+    xs = torch.from_numpy(synth.activations(7, 8, d).view(np.int16)).to(device).view(torch.bfloat16)
+    flush = torch.empty(2 * L2_BYTES, dtype=torch.uint8, device=device)
     for i in range(5):
-        layer.forward(xs[i % 8:i % 8 + 1])
+        call(xs[i % 8:i % 8 + 1])
     # every iteration has its own pair of events; the host does not wait inside the
     # loop, so launch overhead overlaps the previous iteration's flush and layer
     starts = [torch.cuda.Event(enable_timing=True) for _ in range(iters)]
@@ -251,18 +308,106 @@ def time_decode(layer, cfg, torch, iters: int = 40):
     for i in range(iters):
         flush.fill_(i & 0xFF)
         starts[i].record()
-        layer.forward(xs[i % 8:i % 8 + 1])
+        call(xs[i % 8:i % 8 + 1])
         stops[i].record()
     torch.cuda.synchronize()
     times = [a.elapsed_time(b) for a, b in zip(starts, stops)]
-    ms = statistics.median(times)
-    # per-kernel times from events the library records between its launches
+    return statistics.median(times), min(times)
+
+
+def decode_kernels(layer, cfg, device, torch):
+    """Per-kernel times of the one-token layer from events the library records between
+    its launches (single GPU)."""
+    xs = torch.from_numpy(synth.activations(7, 1, cfg["hidden"]).view(np.int16)).to(device).view(torch.bfloat16)
     ph = layer.phase_times(xs[0:1], 10)
-    kernels = {"front_ms": ph["router_ms"] + ph["shared_ms"], "gate_up_ms": ph["dispatch_ms"],
-               "down_ms": ph["experts_ms"], "combine_ms": ph["combine_ms"],
-               "note": "events between launches on the main stream; the shared expert runs beside them on a "
-                       "side stream; front includes host launch latency after an idle device"}
-    return ms, min(times), kernels
+    return {"front_ms": ph["router_ms"] + ph["shared_ms"], "gate_up_ms": ph["dispatch_ms"],
+            "down_ms": ph["experts_ms"], "combine_ms": ph["combine_ms"],
+            "note": "events between launches on the main stream; the shared expert runs beside them on a "
+                    "side stream; front includes host launch latency after an idle device"}
+
+
+def kind_peaks(torch) -> dict:
+    """Measured tensor-pipe peaks of the MMA kinds (operands resident in shared memory,
+    M = 128, N = 256, one CTA per SM): best launch (burst) and the mean over about one
+    second of back-to-back launches (sustained, under the power cap)."""
+    import ctypes as C
+
+    from moonshine_b200 import ops
+    out = {}
+    for name, kind in (("bf16", 0), ("mxf8f6f4", 1), ("mxf4", 2)):
+        flop = C.c_double()
+        iterations = 8000 if kind == 0 else 16000 if kind == 1 else 16000
+        for _ in range(2):
+            if not ops.k3_moe_peak_launch(kind, iterations, C.byref(flop)):
+                raise RuntimeError("k3_moe_peak_launch failed")
+        torch.cuda.synchronize()
+        best = 0.0
+        for _ in range(5):
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            ops.k3_moe_peak_launch(kind, iterations, C.byref(flop))
+            b.record()
+            torch.cuda.synchronize()
+            best = max(best, flop.value / (a.elapsed_time(b) * 1e-3) / 1e12)
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        launches = max(4, int(1.0 / (flop.value / (best * 1e12))))
+        a.record()
+        for _ in range(launches):
+            ops.k3_moe_peak_launch(kind, iterations, C.byref(flop))
+        b.record()
+        torch.cuda.synchronize()
+        out[name] = {"burst_tflops": best, "sustained_tflops": launches * flop.value / (a.elapsed_time(b) * 1e-3) / 1e12}
+    return out
+
+
+def parity_check(world, rank, device, torch, dist):
+    """The layer against the CPU oracle on the small case the smoke check uses (hidden 1024,
+    64 experts, top-8, shared expert), one token and 40 tokens, through the same entry
+    points the timed region uses at this N (expert-parallel exchange included)."""
+    from __graft_entry__ import SMOKE_SHAPE, compare_with_oracle
+    from moonshine_b200.layer import MoELayer
+    cfg = synth.baseline_config(**SMOKE_SHAPE)
+    weights = synth.make_layer(cfg, seed=3)
+    worst = {"ids_exact": True, "near_ties": 0, "rel_l2": 0.0, "tokens_checked": 0}
+    if world > 1:
+        from moonshine_b200.ep import ExpertParallelLayer
+        layer = ExpertParallelLayer(cfg, seed=3, device=device, tokens=40, weights=weights)
+    else:
+        layer = MoELayer(cfg, weights, seed=3, device=device, max_tokens=40)
+    for tokens in (1, 40):
+        x = synth.activations(40 + tokens, tokens, cfg["hidden"])
+        if world > 1 and tokens == 1:
+            xd = torch.from_numpy(x.view(np.int16)).to(device).view(torch.bfloat16)
+            out, ids, w = layer.decode(xd), None, None
+            rows = x
+        elif world > 1:
+            per = tokens // world
+            rows = x[rank * per:(rank + 1) * per]
+            xd = torch.from_numpy(rows.view(np.int16).copy()).to(device).view(torch.bfloat16)
+            out, ids, w = layer.forward(xd, want_routes=True)
+        else:
+            rows = x
+            xd = torch.from_numpy(x.view(np.int16)).to(device).view(torch.bfloat16)
+            out, ids, w = layer.forward(xd, want_routes=True)
+        torch.cuda.synchronize()
+        r = compare_with_oracle(weights, cfg, rows, out, ids)
+        worst["ids_exact"] = worst["ids_exact"] and r["ids_exact"]
+        worst["near_ties"] += r["near_ties"]
+        worst["rel_l2"] = max(worst["rel_l2"], r["rel_l2"])
+        worst["tokens_checked"] += r["tokens_checked"]
+    if world > 1:
+        layer.close()
+        t = torch.tensor([0.0 if worst["ids_exact"] else 1.0, float(worst["near_ties"]), float(worst["tokens_checked"])],
+                         device=device)
+        dist.all_reduce(t)
+        m = torch.tensor([worst["rel_l2"]], device=device)
+        dist.all_reduce(m, op=dist.ReduceOp.MAX)
+        worst = {"ids_exact": t[0].item() == 0.0, "near_ties": int(t[1].item()), "rel_l2": float(m.item()),
+                 "tokens_checked": int(t[2].item())}
+    worst["case"] = ("hidden 1024, 64 experts, top-8, shared 512; 1 token and 40 tokens against the CPU oracle; "
+                     "ids exact except near-ties (score gap < 1e-6), rel-L2 bar 1e-2")
+    worst["pass"] = bool(worst["ids_exact"] and worst["rel_l2"] <= 1e-2)
+    return worst
 
 
 def run_latent(args, cfg, tokens, device, peaks, torch):
@@ -302,11 +447,171 @@ def run_latent(args, cfg, tokens, device, peaks, torch):
         "e2e": None, "cpu_baseline": None}))
 
 
+def make_barrier(world, torch, dist):
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+    return barrier
+
+
+def timed_passes(layer_call, steps, warmup, barrier, torch, device, world, dist, rank, local_rank, lean=False):
+    """W warm-up passes, then K passes between events; max over ranks.  -> (ms per pass, clocks)"""
+    for _ in range(warmup if lean else max(warmup, 3)):
+        layer_call()
+    barrier()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    start.record()
+    for _ in range(steps):
+        layer_call()
+    stop.record()
+    barrier()
+    ms_total = start.elapsed_time(stop)
+    clocks = sampler.stop() if rank == 0 else None
+    if world > 1:
+        t = torch.tensor([ms_total], device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms_total = float(t.item())
+    return ms_total / steps, clocks
+
+
+def run_stress(args, device, peaks, torch, dist, world, rank, local_rank):
+    """Token counts 1 .. 16384 on the stress layer: four experts every token selects,
+    10 % of the router rows duplicated (exact ties), E8M0 scale bytes 0..127."""
+    from moonshine_b200.layer import MoELayer
+    cfg = synth.baseline_config(bias_mode="hot4", duplicate_router_rows=45, scale_low=0, scale_span=128)
+    barrier = make_barrier(world, torch, dist)
+    flops = synth.prefill_flops_per_token(cfg)
+    d = cfg["hidden"]
+    sweep = []
+    layer = None
+    if world == 1:
+        layer = MoELayer(cfg, None, seed=0, device=device, max_tokens=16384)
+    for tokens in (1, 16, 128, 1024, 4096, 16384):
+        x_all = synth.activations(1, tokens, d)
+        if world > 1:
+            from moonshine_b200.ep import ExpertParallelLayer
+            ep = ExpertParallelLayer(cfg, seed=0, device=device, tokens=max(tokens, world))
+            if tokens < world:                           # one token: replicated, experts sharded
+                xd = torch.from_numpy(x_all.view(np.int16).copy()).to(device).view(torch.bfloat16)
+                call = lambda: ep.decode(xd)
+            else:
+                per = tokens // world
+                xd = torch.from_numpy(x_all[rank * per:(rank + 1) * per].view(np.int16).copy()).to(device).view(torch.bfloat16)
+                call = lambda: ep.forward(xd)
+        else:
+            xd = torch.from_numpy(x_all.view(np.int16).copy()).to(device).view(torch.bfloat16)
+            call = lambda: layer.forward(xd)
+        steps = args.steps if tokens >= 1024 else max(args.steps, 20)
+        ms, clocks = timed_passes(call, steps, args.warmup, barrier, torch, device, world, dist, rank, local_rank)
+        if world > 1:
+            ep.close()
+            del ep
+            torch.cuda.empty_cache()
+        entry = {"tokens": tokens, "ms_per_pass": ms, "tokens_per_s": tokens / (ms * 1e-3),
+                 "clocks_mhz": clocks["sm_mhz"] if clocks else None}
+        if tokens >= 1024:
+            tf = flops["routed"] * tokens / (ms * 1e-3) / 1e12
+            entry["whole_pass_tflops"] = tf
+            entry["frac_of_bf16_sustained"] = tf / peaks["bf16_tflops_sustained"] / world
+        else:
+            # few tokens: weight streaming bound; every selected expert's tables are read once
+            entry["note"] = "weight-streaming bound at this size"
+        sweep.append(entry)
+    if rank == 0:
+        big = sweep[-1]
+        print(json.dumps({
+            "metric": METRIC, "value": big["tokens_per_s"], "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": big["ms_per_pass"], "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": dict(run_config(args, cfg, 16384, world),
+                           note="value is the 16384-token point; four experts take 4/16 of all routes (a token "
+                                "selects an expert once), 45 duplicated router row pairs, scale bytes 0..127; "
+                                "L2 is not flushed between passes of the 1..128 token points: their selected "
+                                "experts (up to 2048 tables, 374 MB at one token) exceed L2 from 16 tokens up"),
+            "sweep": sweep, "e2e": None, "cpu_baseline": None, "roofline": None,
+            "gpu_launches": sum(launches_per_step(e["tokens"], True) for e in sweep) * args.steps,
+            "parity": "per token count against the CPU oracle in tests/test_gpu_bench_shapes.py"}))
+
+
+def run_decode_stack(args, device, peaks, torch, dist, world, rank, local_rank):
+    """256 tokens, one at a time, through 92 layer positions (MoE section only); as many
+    distinct weight sets as fit in HBM, used round-robin."""
+    from moonshine_b200.ep import DecodeStack
+    cfg = synth.baseline_config()
+    layers, steps = args.layers, args.tokens or 256
+    per_set = (cfg["experts"] // world) * 23_396_352 + 12_845_056 + 46_792_704
+    free, _total = torch.cuda.mem_get_info(device)
+    distinct = args.distinct or int(min(layers, max(1, (free - (12 << 30)) // per_set)))
+    stack = DecodeStack(cfg, layers, distinct, device, seed=0)
+    d = cfg["hidden"]
+    xs = torch.from_numpy(synth.activations(11, 8, d).view(np.int16)).to(device).view(torch.bfloat16)
+    out = torch.empty((1, d), dtype=torch.bfloat16, device=device)
+    barrier = make_barrier(world, torch, dist)
+    for i in range(3):
+        stack.step(xs[i:i + 1], out)
+    barrier()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    start.record()
+    for i in range(steps):
+        stack.step(xs[i % 8:i % 8 + 1], out)
+    stop.record()
+    barrier()
+    ms = start.elapsed_time(stop)
+    clocks = sampler.stop() if rank == 0 else None
+    if world > 1:
+        t = torch.tensor([ms], device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    finite = bool(torch.isfinite(out.float()).all().item())
+    ms_token = ms / steps
+    nbytes = synth.decode_bytes_per_token(cfg)
+    # per GPU: its share of the 16 experts + the replicated router and shared expert
+    per_gpu = (nbytes - 16 * 23_396_352) + 16 * 23_396_352 / world
+    if rank == 0:
+        print(json.dumps({
+            "metric": "routed_moe_stack_ms_per_token", "value": ms_token, "unit": "ms/token", "n_gpus": world,
+            "steps": steps, "warmup": 3, "ms_per_step": ms_token, "higher_is_better": False, "scaling": "strong",
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": "decode_stack", "layers": layers, "distinct_weight_sets": stack.distinct,
+                       "experts": cfg["experts"], "top_k": cfg["top_k"], "hidden": d,
+                       "expert_hidden": cfg["expert_hidden"], "shared_hidden": cfg["shared_hidden"],
+                       "parallelism": f"ep{world}: token replicated, experts sharded, one all-reduce of the 16 "
+                                      "expert rows per layer" if world > 1 else "single",
+                       "residency": f"{stack.distinct} distinct layer weight sets of {per_set / 1e9:.2f} GB per GPU, "
+                                    f"position l uses set l mod {stack.distinct}; 92 distinct sets need "
+                                    f"{92 * per_set / 1e9:.0f} GB per GPU",
+                       "layer_input": "h = h + moe(rms_norm(h)) per position (unit norm weight), which keeps the "
+                                      "activations finite over 92 layers",
+                       "l2": f"a layer's weights are revisited after {stack.distinct} layers "
+                             f"({stack.distinct * per_set / 1e9:.0f} GB later): nothing stays in L2"},
+            "us_per_layer": 1e3 * ms_token / layers, "outputs_finite": finite,
+            "roofline": {"bound": "hbm", "achieved": nbytes * layers / (ms_token * 1e-3) / 1e9,
+                         "peak": peaks["hbm_gbs"] * world, "unit": "GB/s",
+                         "frac": nbytes * layers / (ms_token * 1e-3) / 1e9 / (peaks["hbm_gbs"] * world),
+                         "per_gpu_bytes_per_layer": per_gpu,
+                         "per_gpu_frac_with_communication": per_gpu * layers / (ms_token * 1e-3) / 1e9 / peaks["hbm_gbs"],
+                         "note": "algorithmic bytes of one copy of the layer (434.0 MB) over the aggregate peak; "
+                                 "per GPU the replicated router and shared expert are read on every rank",
+                         "peak_source": peaks["source"], "traffic": None},
+            "gpu_launches": steps * layers * (8 if world > 1 else 6), "clocks": clocks, "e2e": None,
+            "cpu_baseline": None}))
+    stack.close()
+
+
 def run_native(args):
     import torch
     import torch.distributed as dist
 
-    from moonshine_b200 import _native, ops
+    from moonshine_b200 import _native
     from moonshine_b200.layer import MoELayer
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -322,55 +627,48 @@ def run_native(args):
     _native.lib()                                   # fail loudly if the extension is missing
     if world > 1:
         dist.init_process_group("nccl", device_id=device)
-
-    cfg, tokens = workload_config(args.workload, args)
     peaks = measured_peaks()
+    try:
+        if args.workload == "stress":
+            return run_stress(args, device, peaks, torch, dist, world, rank, local_rank)
+        if args.workload == "decode_stack":
+            return run_decode_stack(args, device, peaks, torch, dist, world, rank, local_rank)
+        return run_layer(args, device, peaks, torch, dist, world, rank, local_rank, MoELayer)
+    finally:
+        if world > 1:
+            dist.barrier()
+            dist.destroy_process_group()
+
+
+def run_layer(args, device, peaks, torch, dist, world, rank, local_rank, MoELayer):
+    cfg, tokens = workload_config(args.workload, args)
     d, k = cfg["hidden"], cfg["top_k"]
     flops = synth.prefill_flops_per_token(cfg)
+    barrier = make_barrier(world, torch, dist)
 
     if "latent" in cfg:
         if world > 1:
             raise SystemExit("the latent workload runs on one GPU")
         return run_latent(args, cfg, tokens, device, peaks, torch)
+    parity = None if args.lean else parity_check(world, rank, device, torch, dist)
+    one_token = tokens == 1
     if world > 1:
         from moonshine_b200.ep import ExpertParallelLayer
-        layer = ExpertParallelLayer(cfg, seed=0, device=device, tokens=tokens, pieces=args.ep_pieces)
-        local_tokens = layer.local_tokens
+        layer = ExpertParallelLayer(cfg, seed=0, device=device, tokens=max(tokens, world), pieces=args.ep_pieces)
+        local_tokens = 1 if one_token else layer.local_tokens
     else:
         layer = MoELayer(cfg, None, seed=0, device=device, max_tokens=tokens)
         local_tokens = tokens
+    first_row = 0 if one_token else rank * local_tokens
     x_host = torch.from_numpy(
-        synth.activations(0, tokens, d)[rank * local_tokens:(rank + 1) * local_tokens].view(np.int16).copy()
+        synth.activations(0, tokens, d)[first_row:first_row + local_tokens].view(np.int16).copy()
     ).view(torch.bfloat16).pin_memory()
     x_dev = x_host.to(device)
     out_host = torch.empty_like(x_host).pin_memory()
+    forward = (lambda x: layer.decode(x)) if (world > 1 and one_token) else (lambda x: layer.forward(x))
 
-    def barrier():
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
-
-    for _ in range(args.warmup if args.lean else max(args.warmup, 3)):
-        layer.forward(x_dev)
-    barrier()
-
-    sampler = ClockSampler(local_rank)
-    if rank == 0:
-        sampler.start()
-    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    barrier()
-    start.record()
-    for _ in range(args.steps):
-        layer.forward(x_dev)
-    stop.record()
-    barrier()
-    ms_total = start.elapsed_time(stop)
-    clocks = sampler.stop() if rank == 0 else None
-    if world > 1:
-        t = torch.tensor([ms_total], device=device)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms_total = float(t.item())
-    ms_step = ms_total / args.steps
+    ms_step, clocks = timed_passes(lambda: forward(x_dev), args.steps, args.warmup, barrier, torch, device, world,
+                                   dist, rank, local_rank, lean=args.lean)
     value = tokens / (ms_step * 1e-3)
 
     if args.lean:           # profiler capture: timed region only
@@ -378,14 +676,13 @@ def run_native(args):
             print(json.dumps({"metric": METRIC, "value": value, "unit": UNIT, "ms_per_step": ms_step,
                               "config": {"workload": args.workload, "tokens": tokens,
                                          "experts": cfg["experts"]}, "lean": True}))
-        if world > 1:
-            dist.destroy_process_group()
         return
 
     # ---- end to end: pinned host input -> device -> layer -> pinned host output, every
     # step.  The three legs of consecutive steps overlap as in a serving loop: step i+1's
     # input is copied while step i computes and step i-1's output goes back; two buffers
     # per direction, ordering by events, all of it inside the timed region.
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     copy_in, copy_out = torch.cuda.Stream(device), torch.cuda.Stream(device)
     main = torch.cuda.current_stream(device)
     x_in = [x_dev, torch.empty_like(x_dev)]
@@ -404,7 +701,7 @@ def run_native(args):
             x_in[i % 2].copy_(x_host, non_blocking=True)
             in_ready[i].record(copy_in)
         main.wait_event(in_ready[i])
-        out = layer.forward(x_in[i % 2])
+        out = forward(x_in[i % 2])
         computed[i].record(main)
         with torch.cuda.stream(copy_out):
             copy_out.wait_event(computed[i])
@@ -426,74 +723,132 @@ def run_native(args):
 
     # ---- phase timing of the dominant kernel (grouped expert products), CUDA events on
     # the launching stream, same inputs, measured in this process after the timed region
-    phases = layer.phase_times(x_dev, args.steps)
-    experts_ms = phases["experts_ms"]
-    if world > 1:
-        t = torch.tensor([experts_ms], device=device)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        experts_ms = float(t.item())
+    phases = None
+    experts_ms = None
+    if not one_token:
+        phases = layer.phase_times(x_dev, args.steps)
+        experts_ms = phases["experts_ms"]
+        if world > 1:
+            t = torch.tensor([experts_ms], device=device)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            experts_ms = float(t.item())
+            r = torch.tensor([float(phases["recv_rows"])], device=device)
+            dist.all_reduce(r, op=dist.ReduceOp.MAX)
+            phases["max_recv_rows_over_ranks"] = int(r.item())
+            phases["experts_ms_max_over_ranks"] = experts_ms
 
-    line = None
+    # ---- the one-token layer at this N (every rank takes part; rank 0 reports)
+    decode = None
+    if not one_token:
+        dcfg = synth.baseline_config()
+        nbytes = synth.decode_bytes_per_token(dcfg)
+        if world == 1:
+            if args.workload == "prefill8k":
+                del layer
+                torch.cuda.empty_cache()
+                dlayer = MoELayer(dcfg, None, seed=0, device=device)
+            else:
+                dlayer = layer
+            dms, dmin = time_decode(lambda x: dlayer.forward(x), dcfg, device, torch)
+            dkernels = decode_kernels(dlayer, dcfg, device, torch)
+            launches = launches_per_step(1, bool(dcfg["shared_hidden"]))
+        else:
+            # the same tensors as the prefill layer apart from the router bias: reuse the shard
+            dms, dmin = time_decode(lambda x: layer.decode(x), dcfg, device, torch)
+            t = torch.tensor([dms], device=device)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            dms = float(t.item())
+            dkernels, launches = None, 8
+        gbs = nbytes / (dms * 1e-3) / 1e9
+        per_gpu = (nbytes - 16 * 23_396_352) + 16 * 23_396_352 / world
+        decode = {"tokens_per_s": 1e3 / dms, "ms_per_token": dms, "ms_min": dmin,
+                  "roofline": {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"] * world,
+                               "unit": "GB/s", "frac": gbs / (peaks["hbm_gbs"] * world),
+                               "bytes_per_token": nbytes, "traffic": DECODE_TRAFFIC_BYTES if world == 1 else None,
+                               "per_gpu_bytes": per_gpu,
+                               "per_gpu_frac_with_communication": per_gpu / (dms * 1e-3) / 1e9 / peaks["hbm_gbs"],
+                               "peak_source": peaks["source"]},
+                  "kernels_ms": dkernels,
+                  "router_bias": cfg["bias_mode"] if world > 1 else "uniform",
+                  "l2": "flushed between iterations (252 MiB buffer rewritten), 8 tokens round-robin",
+                  "gpu_launches_per_token": launches}
+        if world > 1:
+            decode["parallelism"] = ("token replicated, router and shared expert on every rank, the selected experts "
+                                     "where they live, one all-reduce (exact integer sum) of the 16 expert rows")
+
+    # ---- 512-token prefill (weight-streaming bound: ~9 rows per expert), single GPU
+    prefill512 = None
+    if world == 1 and args.workload == "prefill8k":
+        x512 = torch.from_numpy(synth.activations(0, 512, d).view(np.int16).copy()).view(torch.bfloat16).to(device)
+        pms, _ = timed_passes(lambda: dlayer.forward(x512), max(args.steps, 5), 3, barrier, torch, device, 1, dist, 0,
+                              local_rank)
+        pph = dlayer.phase_times(x512, 5)
+        _o, ids512, _w = dlayer.forward(x512, want_routes=True)
+        touched = int(torch.unique(ids512).numel())
+        # sigmoid saturates for the few experts a token prefers (logit std 1.7), so the +-0.1 bias
+        # decides among them and the 8192 routes land on about half of the 896 experts
+        weight_bytes = touched * 23_396_352
+        prefill512 = {"tokens": 512, "ms_per_pass": pms, "tokens_per_s": 512 / (pms * 1e-3), "phases_ms": pph,
+                      "roofline": {"bound": "hbm", "kernel": "grouped expert products (weights streamed once)",
+                                   "achieved": weight_bytes / (pph["experts_ms"] * 1e-3) / 1e9,
+                                   "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                                   "frac": weight_bytes / (pph["experts_ms"] * 1e-3) / 1e9 / peaks["hbm_gbs"],
+                                   "whole_pass_frac": weight_bytes / (pms * 1e-3) / 1e9 / peaks["hbm_gbs"],
+                                   "bytes": weight_bytes, "experts_touched": touched, "traffic": None,
+                                   "peak_source": peaks["source"],
+                                   "tensor_frac": flops["routed"] * 512 / (pph["experts_ms"] * 1e-3) / 1e12 /
+                                   peaks["bf16_tflops_sustained"]},
+                      "router_bias": "uniform", "l2": f"expert weights {weight_bytes / 1e9:.2f} GB per pass: larger than L2"}
+
+    kinds = None
+    if rank == 0 and world == 1 and not one_token:
+        kinds = kind_peaks(torch)
     if rank == 0:
-        if tokens > 1:
+        if not one_token:
             routed_flops = flops["routed"] * tokens / world     # per GPU when balanced
             achieved = routed_flops / (experts_ms * 1e-3) / 1e12
             weight_bytes = cfg["experts"] * (3 * cfg["hidden"] * cfg["expert_hidden"] // 2 * 17 // 16) / world
             roofline = {"bound": "tensor", "kernel": "grouped expert products (gate+up+act, down)",
                         "achieved": achieved, "peak": peaks["bf16_tflops_sustained"],
                         "unit": "TFLOP/s", "frac": achieved / peaks["bf16_tflops_sustained"],
+                        "frac_of_burst": achieved / peaks["bf16_tflops"],
                         "traffic": PREFILL_TRAFFIC_BYTES if args.workload == "prefill8k" and world == 1 else None,
                         "traffic_note": "DRAM read+write of the two grouped GEMM launches, ncu one-pass capture "
                                         "of this workload (summary under profiles/); algorithmic 26.2 GB",
                         "peak_source": peaks["source"] + " bf16 sustained",
                         "launch_ms": experts_ms,
                         "hbm_floor_gbs": weight_bytes / (experts_ms * 1e-3) / 1e9}
+            if kinds:
+                # the expert kernels issue two block-scaled MMAs (hi and lo activation term) per
+                # weight block: executed operations = 2 x the algorithmic ones counted in `achieved`
+                roofline["kind_peaks_tflops"] = kinds
+                roofline["peak_kind"] = kinds["mxf8f6f4"]["sustained_tflops"]
+                roofline["peak_mxfp4"] = kinds["mxf4"]["sustained_tflops"]
+                roofline["frac_of_kind_peak_executed"] = 2.0 * achieved / kinds["mxf8f6f4"]["sustained_tflops"]
+                roofline["frac_of_mxfp4_peak"] = achieved / kinds["mxf4"]["sustained_tflops"]
+                roofline["frac_of_measured_bf16_kind"] = achieved / kinds["bf16"]["sustained_tflops"]
         else:
             nbytes = synth.decode_bytes_per_token(cfg)
             achieved = nbytes / (ms_step * 1e-3) / 1e9
             roofline = {"bound": "hbm", "kernel": "one-token layer", "achieved": achieved,
-                        "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"],
-                        "traffic": DECODE_TRAFFIC_BYTES, "peak_source": peaks["source"]}
-        decode = None
-        if world == 1:
-            dcfg = synth.baseline_config()
-            dlayer = layer if args.workload != "prefill8k" else MoELayer(dcfg, None, seed=0, device=device)
-            if args.workload == "prefill8k":
-                del layer
-                torch.cuda.empty_cache()
-            dms, dmin, dkernels = time_decode(dlayer, dcfg, torch)
-            nbytes = synth.decode_bytes_per_token(dcfg)
-            gbs = nbytes / (dms * 1e-3) / 1e9
-            decode = {"tokens_per_s": 1e3 / dms, "ms_per_token": dms, "ms_min": dmin,
-                      "roofline": {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"],
-                                   "unit": "GB/s", "frac": gbs / peaks["hbm_gbs"],
-                                   "bytes_per_token": nbytes, "traffic": DECODE_TRAFFIC_BYTES,
-                                   "peak_source": peaks["source"]},
-                      "kernels_ms": dkernels,
-                      "l2": "flushed between iterations (252 MiB buffer rewritten), 8 tokens round-robin",
-                      "gpu_launches_per_token": launches_per_step(1, bool(dcfg["shared_hidden"]))}
+                        "peak": peaks["hbm_gbs"] * world, "unit": "GB/s", "frac": achieved / (peaks["hbm_gbs"] * world),
+                        "traffic": DECODE_TRAFFIC_BYTES if world == 1 else None, "peak_source": peaks["source"],
+                        "note": "back to back on one token: L2 not flushed (the decode block of the default "
+                                "workload flushes it)"}
         cpu = cpu_baseline(cfg, tokens) if world == 1 else None
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": args.workload, "tokens": tokens, "experts": cfg["experts"],
-                       "top_k": k, "hidden": d, "expert_hidden": cfg["expert_hidden"],
-                       "shared_hidden": cfg["shared_hidden"], "router_bias": cfg["bias_mode"],
-                       "parallelism": (f"ep{world}" + (f" x {args.ep_pieces} pipelined row ranges" if args.ep_pieces > 1 else ""))
-                       if world > 1 else "single",
-                       "l2": "inputs larger than L2 (expert weights 20.96 GB per pass)"},
+            "config": run_config(args, cfg, tokens, world),
             "e2e": {"value": e2e_value, "unit": UNIT,
                     "h2d_bytes_per_step": local_tokens * d * 2 * world,
                     "d2h_bytes_per_step": local_tokens * d * 2 * world},
-            "gpu_launches": launches_per_step(tokens, bool(cfg["shared_hidden"])) * args.steps,
+            "gpu_launches": (launches_per_step(tokens, bool(cfg["shared_hidden"])) + (4 if world > 1 else 0)) * args.steps,
             "clocks": clocks, "roofline": roofline, "phases_ms": phases, "decode": decode,
-            "cpu_baseline": cpu,
+            "prefill512": prefill512, "parity": parity, "cpu_baseline": cpu,
         }
         print(json.dumps(line))
-    if world > 1:
-        dist.barrier()
-        dist.destroy_process_group()
 
 
 def main():
@@ -502,12 +857,16 @@ def main():
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="native", choices=["native", "reference"])
-    ap.add_argument("--workload", default="prefill8k", choices=["prefill8k", "prefill512", "decode", "latent8k"])
+    ap.add_argument("--workload", default="prefill8k",
+                    choices=["prefill8k", "prefill512", "decode", "latent8k", "stress", "decode_stack"])
+    ap.add_argument("--layers", type=int, default=92, help="decode_stack: layer positions")
+    ap.add_argument("--distinct", type=int, default=0,
+                    help="decode_stack: resident weight sets (default: as many as fit in HBM)")
     ap.add_argument("--lean", action="store_true", help="timed region only (for profiler captures)")
     ap.add_argument("--ep-pieces", type=int, default=1,
                     help="expert-parallel runs: row ranges per pass pipelined against each other")
     ap.add_argument("--experts", type=int, default=0, help="override the expert count (profiler captures)")
-    ap.add_argument("--tokens", type=int, default=0, help="override the token count (profiler captures)")
+    ap.add_argument("--tokens", type=int, default=0, help="override the token count (profiler captures; decode_stack: tokens decoded)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

@@ -282,6 +282,15 @@ bool k3_moe_device_status_clear(void);
  * counterpart in the reference. */
 bool k3_moe_selftest_bounded_wait(uint32_t limit_us, void *gave_up, void *stream);
 
+/* Tensor-pipe peak of an MMA kind, for roofline denominators measured on the
+ * GPU at hand: one CTA per SM issues 4 * iterations tcgen05.mma instructions of
+ * M = 128, N = 256 on operand tiles that stay in shared memory.  kind: 0 = bf16
+ * (kind::f16), 1 = block-scaled E2M1 x E4M3 (kind::mxf8f6f4, what the expert
+ * kernels issue), 2 = block-scaled E2M1 x E2M1 (kind::mxf4, the MXFP4 peak).
+ * *flop_per_launch (optional) receives the operations of the launch; time the
+ * launch with events.  No counterpart in the reference. */
+bool k3_moe_peak_launch(int kind, uint32_t iterations, double *flop_per_launch, void *stream);
+
 /* Event helpers for hosts without CUDA runtime bindings: create / destroy a
  * timing event and read the milliseconds between two recorded events (waits
  * for `end`; negative on error). */

@@ -356,58 +356,163 @@ def ep_forward_pipelined(backends, x, cfg: dict, group=None, streams=None):
     return out, ids, weights
 
 
+def _bf16_ptr_ok(t: torch.Tensor) -> bool:
+    return t.is_cuda and t.is_contiguous() and t.element_size() == 2
+
+
 class ExpertParallelLayer:
-    """The benchmark's layer sharded over the default process group (one rank per GPU)."""
+    """The benchmark's layer sharded over the default process group (one rank per GPU).
+
+    The pass itself is one call of ``k3_moe_ep_layer_forward``: the count exchange, both
+    grouped send/recv steps and every kernel are issued by the library from C++ on the
+    current stream.  ``torch.distributed`` is used once, to hand rank 0's NCCL identifier
+    to the other ranks.  ``pieces`` > 1 selects the Python-driven pipelined form instead
+    (``ep_forward_pipelined``; same results, kept for comparison)."""
 
     def __init__(self, cfg: dict, seed: int, device, tokens: int, weights: dict | None = None, pieces: int = 1):
-        """``pieces`` > 1 cuts every pass into that many consecutive row ranges that are
-        pipelined against each other (``ep_forward_pipelined``); same results."""
+        import ctypes as C
         self.world, self.rank = dist.get_world_size(), dist.get_rank()
         if tokens % self.world != 0:
             raise ValueError("token count must divide evenly over the ranks")
         self.cfg = dict(cfg)
+        self.tokens = tokens
         self.local_tokens = tokens // self.world
         first, per = shard_range(cfg["experts"], self.world, self.rank)
         self.layer = MoELayer(cfg, weights, seed=seed, device=device, local=(first, per), max_tokens=1)
-        self.backends = [NativeBackend(self.layer) for _ in range(max(1, pieces))]
-        self.backend = self.backends[0]
         self.device = self.layer.device
-        self.streams = [torch.cuda.Stream(self.device) for _ in self.backends] if len(self.backends) > 1 else None
+        self.backends = [NativeBackend(self.layer) for _ in range(max(1, pieces))] if pieces > 1 else []
+        self.streams = [torch.cuda.Stream(self.device) for _ in self.backends] if pieces > 1 else None
+        # NCCL identifier from rank 0
+        ident = torch.zeros(128, dtype=torch.uint8, device=self.device)
+        err = C.create_string_buffer(256)
+        if self.rank == 0:
+            host = (C.c_uint8 * 128)()
+            if not ops.k3_moe_ep_unique_id(C.addressof(host), err, 256):
+                raise RuntimeError("k3_moe_ep_unique_id: " + err.value.decode())
+            ident.copy_(torch.frombuffer(bytearray(host), dtype=torch.uint8))
+        dist.broadcast(ident, 0)
+        ident_host = (C.c_uint8 * 128).from_buffer_copy(ident.cpu().numpy().tobytes())
+        handle = C.c_void_p()
+        with torch.cuda.device(self.device):
+            if not ops.k3_moe_ep_create(C.byref(handle), C.addressof(ident_host), self.rank, self.world, err, 256):
+                raise RuntimeError("k3_moe_ep_create: " + err.value.decode())
+        self.handle = handle
+        # every route of the batch may land on one rank: the sure bound
+        self.max_recv = tokens * cfg["top_k"]
+        need = ops.k3_moe_ep_workspace_bytes(self.handle, self.layer.desc, self.local_tokens, self.max_recv)
+        if need == 0:
+            raise RuntimeError("k3_moe_ep_workspace_bytes rejected the shard description")
+        self.workspace = torch.empty(need, dtype=torch.uint8, device=self.device)
+        self.decode_workspace = None
+
+    def close(self):
+        if getattr(self, "handle", None):
+            torch.cuda.synchronize(self.device)
+            ops.k3_moe_ep_destroy(self.handle)
+            self.handle = None
 
     def forward(self, x: torch.Tensor, want_routes: bool = False):
-        if len(self.backends) > 1:
+        import ctypes as C
+        if self.backends:
             out, ids, w = ep_forward_pipelined(self.backends, x, self.cfg, streams=self.streams)
-        else:
-            out, ids, w = ep_forward(self.backend, x, self.cfg)
+            return (out, ids, w) if want_routes else out
+        t, k = x.shape[0], self.cfg["top_k"]
+        assert t <= self.local_tokens and _bf16_ptr_ok(x)
+        out = torch.empty_like(x)
+        ids = torch.empty((t, k), dtype=torch.int32, device=self.device) if want_routes else None
+        w = torch.empty((t, k), dtype=torch.float32, device=self.device) if want_routes else None
+        err = C.create_string_buffer(256)
+        if not ops.k3_moe_ep_layer_forward(self.handle, self.layer.desc, out, x, t, self.max_recv, self.workspace,
+                                           self.workspace.numel(), ids, w, err, 256):
+            raise RuntimeError("k3_moe_ep_layer_forward: " + err.value.decode())
         return (out, ids, w) if want_routes else out
 
+    def decode(self, x: torch.Tensor, residual: torch.Tensor | None = None) -> torch.Tensor:
+        """One token, the same on every rank: x bf16 [1, d] -> out bf16 [1, d] on every rank."""
+        if self.decode_workspace is None:
+            need = ops.k3_moe_ep_decode_workspace_bytes(self.handle, self.layer.desc)
+            if need == 0:
+                raise RuntimeError("the one-token path does not take this layer shape")
+            self.decode_workspace = torch.empty(need, dtype=torch.uint8, device=self.device)
+        out = torch.empty_like(x)
+        if not ops.k3_moe_ep_decode(self.handle, self.layer.desc, out, x, residual, self.decode_workspace,
+                                    self.decode_workspace.numel()):
+            raise RuntimeError("k3_moe_ep_decode failed")
+        return out
+
     def phase_times(self, x: torch.Tensor, steps: int = 5) -> dict:
-        """Device time of the grouped expert products on this rank's received rows,
-        plus the whole-pass time, averaged over ``steps`` passes."""
-        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        originals = [b.experts for b in self.backends]
-        spans = []
+        """Device time of the grouped expert products on this rank's received rows and of
+        the whole pass, averaged over ``steps`` passes (events recorded by the library)."""
+        import ctypes as C
+        experts = total = 0.0
+        rows = 0
+        e, p, n = C.c_float(), C.c_float(), C.c_uint32()
+        for _ in range(steps):
+            self.forward(x)
+            if not ops.k3_moe_ep_last_pass(self.handle, C.byref(e), C.byref(p), C.byref(n)):
+                raise RuntimeError("k3_moe_ep_last_pass failed")
+            experts += e.value
+            total += p.value
+            rows = n.value
+        return {"experts_ms": experts / steps, "pass_ms": total / steps, "recv_rows": rows}
 
-        def timed_call(orig):
-            def timed(*args):
-                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-                a.record()
-                r = orig(*args)
-                b.record()
-                spans.append((a, b))
-                return r
-            return timed
 
-        for backend, orig in zip(self.backends, originals):
-            backend.experts = timed_call(orig)
-        try:
-            start.record()
-            for _ in range(steps):
-                self.forward(x)
-            stop.record()
-            torch.cuda.synchronize()
-        finally:
-            for backend, orig in zip(self.backends, originals):
-                backend.experts = orig
-        experts_ms = sum(a.elapsed_time(b) for a, b in spans) / steps
-        return {"experts_ms": experts_ms, "pass_ms": start.elapsed_time(stop) / steps}
+class DecodeStack:
+    """A stack of routed-MoE layers decoding one token at a time, expert-parallel over
+    the default process group (or on one GPU without one): ``layers`` layer positions
+    backed by ``distinct`` resident weight sets used round-robin (position l uses set
+    l % distinct).  One call of ``k3_moe_ep_decode_stack`` per token."""
+
+    def __init__(self, cfg: dict, layers: int, distinct: int, device, seed: int = 0):
+        import ctypes as C
+        from . import _native
+        if dist.is_available() and dist.is_initialized():
+            self.world, self.rank = dist.get_world_size(), dist.get_rank()
+        else:
+            self.world, self.rank = 1, 0
+        self.cfg, self.layers, self.distinct = dict(cfg), layers, min(distinct, layers)
+        self.device = torch.device(device)
+        first, per = shard_range(cfg["experts"], self.world, self.rank)
+        self.sets = [MoELayer(cfg, None, seed=seed + i, device=device, local=(first, per), max_tokens=1)
+                     for i in range(self.distinct)]
+        err = C.create_string_buffer(256)
+        handle = C.c_void_p()
+        ident_host = None
+        if self.world > 1:
+            ident = torch.zeros(128, dtype=torch.uint8, device=self.device)
+            if self.rank == 0:
+                host = (C.c_uint8 * 128)()
+                if not ops.k3_moe_ep_unique_id(C.addressof(host), err, 256):
+                    raise RuntimeError("k3_moe_ep_unique_id: " + err.value.decode())
+                ident.copy_(torch.frombuffer(bytearray(host), dtype=torch.uint8))
+            dist.broadcast(ident, 0)
+            ident_host = (C.c_uint8 * 128).from_buffer_copy(ident.cpu().numpy().tobytes())
+        with torch.cuda.device(self.device):
+            if not ops.k3_moe_ep_create(C.byref(handle), C.addressof(ident_host) if ident_host else None,
+                                        self.rank, self.world, err, 256):
+                raise RuntimeError("k3_moe_ep_create: " + err.value.decode())
+        self.handle = handle
+        self.table = (C.POINTER(_native.LayerDesc) * layers)(
+            *[C.pointer(self.sets[l % self.distinct].desc) for l in range(layers)])
+        need = ops.k3_moe_ep_decode_workspace_bytes(self.handle, self.sets[0].desc)
+        if need == 0:
+            raise RuntimeError("the one-token path does not take this layer shape")
+        d = cfg["hidden"]
+        self.workspace = torch.empty(need + 3 * (2 * d + 256) + 1024, dtype=torch.uint8, device=self.device)
+        self.norm_weight = torch.ones(d, dtype=torch.bfloat16, device=self.device)
+
+    def step(self, x: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+        out = torch.empty_like(x) if out is None else out
+        if not ops.k3_moe_ep_decode_stack(self.handle, self.table, self.layers, out, x, self.norm_weight, 1e-5,
+                                          self.workspace, self.workspace.numel()):
+            raise RuntimeError("k3_moe_ep_decode_stack failed")
+        return out
+
+    def weight_bytes(self) -> int:
+        return sum(s.weight_bytes() for s in self.sets)
+
+    def close(self):
+        if getattr(self, "handle", None):
+            torch.cuda.synchronize(self.device)
+            ops.k3_moe_ep_destroy(self.handle)
+            self.handle = None

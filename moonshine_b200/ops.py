@@ -22,6 +22,8 @@ from . import _native
 def _ptr(a):
     if a is None:
         return None
+    if isinstance(a, C.c_void_p):          # an opaque handle returned through an out parameter
+        return a.value
     if isinstance(a, torch.Tensor):
         if not a.is_contiguous():
             raise ValueError("operator arguments must be contiguous")

@@ -43,9 +43,10 @@ def main():
         rel = float(np.sqrt(((g - r) ** 2).sum() / (r ** 2).sum()))
         verdicts.append((bias_mode, same_ids, bool(np.array_equal(got, want)), rel))
         # both forms of the exchange (a row per route / a row per destination): same bits
-        from moonshine_b200.ep import ep_forward
+        from moonshine_b200.ep import NativeBackend, ep_forward
+        python_path = NativeBackend(ep_layer.layer)      # the same pass driven from Python
         for form in (False, True):
-            out1, ids1, _ = ep_forward(ep_layer.backend, xl, cfg, once_per_destination=form)
+            out1, ids1, _ = ep_forward(python_path, xl, cfg, once_per_destination=form)
             torch.cuda.synchronize()
             same = bool(np.array_equal(bf16_tensor_to_bits(out1), got)) and bool(torch.equal(ids1, ids))
             verdicts.append((bias_mode + ("/row per destination" if form else "/row per route"), same, same,
@@ -57,6 +58,40 @@ def main():
         torch.cuda.synchronize()
         same = bool(np.array_equal(bf16_tensor_to_bits(out2), got)) and bool(torch.equal(ids2, ids))
         verdicts.append((bias_mode + "/pipelined", same, same, 0.0 if same else 1.0))
+        # one token, replicated: every rank must end with the single-GPU layer's row
+        for t in (0, 3):
+            one = ep_layer.decode(xs[t:t + 1])
+            want_one = single.forward(xs[t:t + 1])
+            torch.cuda.synchronize()
+            same = bool(torch.equal(one, want_one))
+            verdicts.append((f"{bias_mode}/one token {t}", same, same, 0.0 if same else 1.0))
+        ep_layer.close()
+    # a stack of 6 layer positions over 3 weight sets, one token at a time, against the
+    # same stack on one GPU (a handle of world size 1 in this process)
+    from moonshine_b200.ep import DecodeStack
+    cfg = synth.baseline_config(hidden=1024, expert_hidden=512, experts=64, top_k=8, shared_hidden=512)
+    stack = DecodeStack(cfg, layers=6, distinct=3, device=device, seed=40)
+    x0 = torch.from_numpy(synth.activations(41, 2, cfg["hidden"]).view(np.int16).copy()).to(device).view(torch.bfloat16)
+    got_stack = [stack.step(x0[t:t + 1]).clone() for t in range(2)]
+    torch.cuda.synchronize()
+    stack.close()
+    h = [x0[t:t + 1].clone() for t in range(2)]
+    import ctypes as C
+    from moonshine_b200 import ops
+    norm_w = torch.ones(cfg["hidden"], dtype=torch.bfloat16, device=device)
+    for l in range(6):
+        full = MoELayer(cfg, None, seed=40 + l % 3, device=device, max_tokens=1)
+        ws_bytes = ops.k3_moe_block_workspace_bytes(full.desc, 1)
+        ws = torch.empty(ws_bytes, dtype=torch.uint8, device=device)
+        for t in range(2):
+            nxt = torch.empty_like(h[t])
+            assert ops.k3_moe_block_forward(full.desc, nxt, h[t], norm_w, 1e-5, 1, ws, ws_bytes)
+            h[t] = nxt
+        torch.cuda.synchronize()
+        del full, ws
+    for t in range(2):
+        same = bool(torch.equal(got_stack[t], h[t]))
+        verdicts.append((f"stack token {t}", same, same, 0.0 if same else 1.0))
     ok = all(v[1] and v[3] <= 1e-3 for v in verdicts)
     sys.stderr.write(f"rank {rank}: {verdicts}\n")
     # one verdict line for the whole job (lines of several ranks could interleave)

@@ -151,3 +151,54 @@ def test_destination_splits():
     assert ep.shard_range(896, 8, 3) == (336, 112)
     with pytest.raises(ValueError):
         ep.shard_range(10, 4, 0)
+
+
+def c_plan(offsets_all, world, rank, experts):
+    import ctypes as C
+    from moonshine_b200 import _native
+    per = experts // world
+    u32 = lambda n: (C.c_uint32 * n)()
+    flat = (C.c_uint32 * offsets_all.size)(*offsets_all.ravel().tolist())
+    send, recv, brs, bds, br, off = u32(world), u32(world), u32(per * world), u32(per * world), u32(per * world), u32(per + 1)
+    assert _native.lib().k3_moe_ep_plan(flat, world, rank, experts, send, recv, brs, bds, br, off)
+    return [list(a) for a in (send, recv, brs, bds, br, off)]
+
+
+@pytest.mark.parametrize("world,experts", [(2, 4), (4, 16), (8, 896)])
+def test_library_plan_matches_python_plan_and_regroups_to_single_gpu_order(world, experts):
+    """k3_moe_ep_plan (the host step of the C entry point) against ep.exchange_plan, and the
+    property the layer relies on: reading the received rows through the plan's blocks gives
+    the single-GPU grouping order (expert asc, global route asc)."""
+    from moonshine_b200 import ep
+    rng = np.random.default_rng(world)
+    per, tokens_per_rank, k = experts // world, 9, min(4, experts)
+    ids = np.stack([rng.permutation(experts)[:k] for _ in range(world * tokens_per_rank)]).astype(np.uint32)
+    if world == 4:
+        ids[ids >= 12] = 0                        # the last rank receives nothing at all
+    counts = np.zeros((world, experts), np.int64)
+    offsets_all = np.zeros((world, experts + 1), np.uint32)
+    for r in range(world):
+        local = ids[r * tokens_per_rank:(r + 1) * tokens_per_rank]
+        counts[r] = np.bincount(local.ravel(), minlength=experts)
+        offsets_all[r, 1:] = np.cumsum(counts[r])
+    for rank in range(world):
+        send, recv, brs, bds, br, off = c_plan(offsets_all, world, rank, experts)
+        psend, precv, starts, lengths, poff = ep.exchange_plan(torch.from_numpy(counts), rank, rank * per, per)
+        assert send == psend and recv == precv and off == poff.tolist()
+        assert brs == starts.tolist() and br == lengths.tolist()
+        assert bds == (np.cumsum(lengths.numpy()) - lengths.numpy()).tolist()
+        # emulate: what each source sends (its routes sorted expert asc, route asc, restricted to
+        # this rank's experts), concatenated source by source, then read through the blocks
+        received = []
+        for s in range(world):
+            local = ids[s * tokens_per_rank:(s + 1) * tokens_per_rank].ravel()
+            routes = np.arange(local.size) + s * tokens_per_rank * k           # global route numbers
+            order = np.lexsort((routes, local))
+            keep = [(int(local[i]), int(routes[i])) for i in order if rank * per <= local[i] < (rank + 1) * per]
+            received += keep
+        grouped = [None] * len(received)
+        for b in range(per * world):
+            for i in range(br[b]):
+                grouped[bds[b] + i] = received[brs[b] + i]
+        assert grouped == sorted(received)                                      # expert asc, global route asc
+        assert off[-1] == len(received)

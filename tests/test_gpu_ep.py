@@ -1,4 +1,4 @@
-"""Expert-parallel layer on real GPUs (2 ranks over NCCL): every rank's output
+"""Expert-parallel layer on real GPUs (2, 4 and 8 ranks over NCCL, as many as the machine has): every rank's output
 must match the single-GPU layer on the same seeded inputs - routing exactly,
 outputs bit for bit where both take the same kernels (rel-L2 <= 1e-3 otherwise)."""
 import os
@@ -16,8 +16,11 @@ if not torch.cuda.is_available() or torch.cuda.device_count() < 2:
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
-def test_two_gpu_expert_parallel_matches_single_gpu():
-    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2",
+@pytest.mark.parametrize("ranks", [2, 4, 8])
+def test_expert_parallel_matches_single_gpu(ranks):
+    if torch.cuda.device_count() < ranks:
+        pytest.skip(f"needs {ranks} CUDA devices")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", str(ranks),
            "--master-addr", "127.0.0.1", "--master-port", "29711",
            os.path.join(ROOT, "tests", "ep_gpu_worker.py")]
     res = subprocess.run(cmd, capture_output=True, text=True, timeout=600, cwd=ROOT)
