@@ -739,7 +739,7 @@ def run_layer(args, device, peaks, torch, dist, world, rank, local_rank, MoELaye
 
     # ---- the one-token layer at this N (every rank takes part; rank 0 reports)
     decode = None
-    if not one_token:
+    if True:
         dcfg = synth.baseline_config()
         nbytes = synth.decode_bytes_per_token(dcfg)
         if world == 1:

@@ -2,7 +2,7 @@
 // on a side stream, no host round trip.
 //
 //   front    router logits (one 256-thread block per BF16 row, the reference's
-//            reduction order) and the token's two-term E4M3 form; the last block
+//            reduction order) and the token's E2M1 terms; the last block
 //            to finish routes the token (sigmoid + bias top-k).  On shapes the
 //            block-scaled expert kernels do not take it also carries the shared
 //            expert's gate/up rows and activation.
@@ -28,6 +28,7 @@
 // converts nibbles to f16 with byte-permute lookups and accumulates per 32-column
 // scale group on mma.sync (see k3_gemv.cuh for the fragment layout).
 #include "k3_decode_tail.cuh"
+#include "k3_e2m1_terms.cuh"
 #include "k3_gemv.cuh"
 #include "k3_grouped.h"
 #include "k3_rowdot.cuh"
@@ -39,7 +40,6 @@
 #include <map>
 #include <mutex>
 
-#include <cuda_fp8.h>
 
 using namespace k3;
 
@@ -59,7 +59,7 @@ struct DecodeArgs {
     uint16_t *act;            // [top_k, I]
     uint16_t *rows_out;       // [top_k, hidden]
     uint32_t skip_shared;     // down kernel: the shared expert's rows are computed elsewhere
-    uint8_t *x_hl, *x_sf;     // front: two-term E4M3 form of x ([2, hidden], [hidden/32]) or null
+    uint8_t *x_terms, *x_sf;  // front: E2M1 terms of x ([kTerms, hidden/2] packed, [kTerms, hidden/32]) or null
     float *route_words;       // front: [2][1024] scores and choices written by the row tasks, or null
     unsigned int *ticket;     // front: completion counter of this call
     uint32_t shared_elsewhere;  // front: the shared expert runs in its own kernels (side stream)
@@ -81,24 +81,10 @@ K3_DEVINL uint32_t order_key(float f) {
     return b ^ ((b >> 31) ? 0xffffffffu : 0x80000000u);
 }
 
-// Block of 32 values (one per lane) -> two E4M3 terms and the E8M0 block scale:
-// value = 2^(scale - 127) * (hi + lo).
-K3_DEVINL void split_block(float val, uint8_t &hi, uint8_t &lo, uint8_t &scale_byte) {
-    const float mx = warp_max(fabsf(val));
-    int e = 0;
-    if (mx > 0.f && mx < 3.0e38f) e = (int)((__float_as_uint(mx) >> 23) & 0xffu) - 127 - 7;
-    e = max(-127, min(127, e));
-    const float scaled = val * __uint_as_float((uint32_t)(127 - e) << 23);      // |scaled| < 256
-    hi = __nv_cvt_float_to_fp8(scaled, __NV_SATFINITE, __NV_E4M3);
-    const float hi_f = __half2float(__half(__nv_cvt_fp8_to_halfraw(hi, __NV_E4M3)));
-    lo = __nv_cvt_float_to_fp8(scaled - hi_f, __NV_SATFINITE, __NV_E4M3);
-    scale_byte = (uint8_t)(e + 127);
-}
-
 // One 256-thread block per row task: router rows and the shared expert's gate
 // and up rows (reference reduction order, thread v = the reference's lane v, the
-// whole row in flight at once), plus the 32-column blocks of the token's two-term
-// E4M3 form.  The last block to finish then routes the token (sigmoid + bias
+// whole row in flight at once), plus the 32-column blocks of the token's E2M1
+// terms.  The last block to finish then routes the token (sigmoid + bias
 // top-k in the reference's order: larger choice first, lower expert id on ties)
 // and applies the shared expert's activation.
 template <bool kWithShared>
@@ -115,7 +101,7 @@ decode_front_kernel(DecodeArgs a) {
     __shared__ uint32_t is_last;
     const uint32_t warp = threadIdx.x / kWarp, lane = threadIdx.x % kWarp;
     const uint32_t E = a.d.expert_count, S = a.d.shared_hidden, H = a.d.hidden, k = a.d.top_k;
-    const uint32_t split_tasks = a.x_hl ? (H / 32u + 7u) / 8u : 0u;        // 8 blocks (one per warp) each
+    const uint32_t split_tasks = a.x_terms ? (H / 32u + 7u) / 8u : 0u;        // 8 blocks (one per warp) each
     if ((reinterpret_cast<uintptr_t>(a.x) & 15u) == 0u && H % 8u == 0u) {
         // 16 bytes per load: the whole token is in flight after at most four loads per thread
         for (uint32_t i = threadIdx.x; i < H / 8u; i += blockDim.x) {
@@ -184,11 +170,9 @@ decode_front_kernel(DecodeArgs a) {
         } else {
             const uint32_t blk = (task - E - groups) * 8u + warp;
             if (blk < H / 32u) {
-                uint8_t hi, lo, sb;
-                split_block(xf[blk * 32u + lane], hi, lo, sb);
-                a.x_hl[blk * 32u + lane] = hi;
-                a.x_hl[H + blk * 32u + lane] = lo;
-                if (lane == 0) a.x_sf[blk] = sb;
+                uint32_t code[kTerms], sbyte[kTerms];
+                split_block_e2m1(xf[blk * 32u + lane], code, sbyte);
+                store_block_e2m1(a.x_terms, a.x_sf, H / 2u, H / 32u, blk, code, sbyte, lane);
             }
         }
         __syncthreads();            // `red` is reused by the next task
@@ -654,7 +638,7 @@ bool k3_decode_layer(const k3_moe_layer_desc *d, const void *x, void *logits, vo
     const bool mx = scratch != nullptr && k3_decode_mx_supported(d) && d->top_k < 32u &&
                     scratch_bytes >= k3_decode_mx_scratch_bytes(d);
     if (mx) {
-        k3_decode_mx_vector_scratch(d, scratch, (void **)&a.x_hl, (void **)&a.x_sf);
+        k3_decode_mx_vector_scratch(d, scratch, (void **)&a.x_terms, (void **)&a.x_sf);
         a.route_words = (float *)k3_decode_mx_route_words(d, scratch);
     }
     static std::atomic<uint32_t> next_ticket{0};

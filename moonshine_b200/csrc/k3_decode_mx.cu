@@ -1,36 +1,35 @@
-// One-token expert products on the block-scaled tensor-core path
-// (tcgen05.mma kind::mxf8f6f4, scale_vec::1X).
+// One-token expert products on the packed block-scaled tensor-core path
+// (tcgen05.mma kind::mxf4, 32-element blocks with E8M0 scales).
 //
-// The MXFP4 weights are consumed as they are: packed E2M1 nibbles arrive by TMA
-// (tensor-map type 16U4_ALIGN16B expands them into the 8-bit containers the MMA
-// reads) and the E8M0 scales are written into tensor memory with tcgen05.st, so
-// no thread touches a weight.  The activation vector is split once into two
-// E4M3 terms with a shared E8M0 scale per 32 elements, x = 2^s * (hi + lo):
-// bf16 has 8 significant bits, each E4M3 term carries 4, so every element within
-// 2^10 of its block maximum is represented exactly and the rest to 2^-17 of the
-// block maximum.  hi and lo are rows 0 and 1 of the N=16 operand, so accumulator
-// columns 0 and 1 hold the two partial dot products and their sum is the result.
+// The MXFP4 weights are consumed as they are stored: packed E2M1 nibbles arrive by
+// TMA as plain bytes (128 rows x 128 bytes = 256 K elements per box, the layout the
+// MMA reads) and the E8M0 scales are written into tensor memory with tcgen05.st, so
+// no thread touches a weight and shared memory holds exactly the bytes HBM delivered.
+// The activation vector is split once into kTerms E2M1 terms with a block scale per
+// term (k3_e2m1_terms.cuh), exact for bf16 inputs; the terms are rows 0..7 of the
+// N = 16 operand, so accumulator columns 0..7 hold the partial dot products and
+// their sum is the result.
 //
 // One CTA per SM, persistent over (expert rank, 128-row tile) items:
-//   warp 0      TMA producer (A: 128 rows x 128 K, B: 16 rows x 128 K per step)
-//   warp 1      MMA issuer: 4 MMAs of K=32 per step, scale ids 0..3
-//   warps 2-5   scale writers: per step the tile's 128x4 E8M0 bytes -> 4 TMEM
-//               columns (lane = row % 32, column = row / 32, copied into every
-//               lane quadrant) plus the activation block scales
-//   warps 6-9   epilogue: tcgen05.ld columns 0/1 (+16/17), sum, bf16, activation;
+//   warp 0      TMA producer (A: 128 rows x 256 K, B: 8 term rows x 256 K per stage)
+//   warp 1      MMA issuer: 4 MMAs of K=64 per stage, even stages
+//   warps 2-5   scale writers: per batch the tile's 128x16 E8M0 bytes (512 K, two
+//               stages) -> 16 TMEM columns (lane = row % 32, column = row / 32,
+//               copied into every lane quadrant) plus the terms' block scales
+//   warps 6-9   epilogue: tcgen05.ld of the term columns, sum, bf16, activation;
 //               the gate/up epilogue also splits the activation it produces into
-//               the two E4M3 terms the down projection reads
-//   warp 10     scale producer: block scales of four K steps into a shared-memory ring
-//   warp 11     second MMA issuer (odd K steps, its own accumulator columns)
+//               the E2M1 terms the down projection reads
+//   warp 10     scale producer: block scales of two stages into a shared-memory ring
+//   warp 11     second MMA issuer (odd stages, its own accumulator columns)
 // Every barrier wait is bounded (see k3_tc_ptx.cuh).
 #include "k3_decode_tail.cuh"
+#include "k3_e2m1_terms.cuh"
 #include "k3_grouped.h"
 #include "k3_rowdot.cuh"
 #include "k3_tc_ptx.cuh"
 
 #include <cuda.h>
 #include <cudaTypedefs.h>
-#include <cuda_fp8.h>
 
 #include <algorithm>
 #include <atomic>
@@ -43,24 +42,25 @@ using namespace k3::tc;
 
 namespace {
 
-constexpr uint32_t kStages = 12;            // TMA ring of weight / vector tiles
-constexpr uint32_t kSfBatches = 6;          // scale ring in tensor memory: batches of 4 steps
+constexpr uint32_t kStages = 12;            // TMA ring of weight / term tiles
+constexpr uint32_t kKStage = 256;           // K elements per stage (128 packed bytes per row)
+constexpr uint32_t kSfBatches = 6;          // scale ring in tensor memory: batches of 2 stages (512 K)
 constexpr uint32_t kSfSlots = 4;            // scale ring in shared memory (one batch per slot)
-constexpr uint32_t kSfaBytes = 128 * 16;    // 128 rows x 16 scale bytes (4 steps)
-constexpr uint32_t kSfSlotBytes = kSfaBytes + 128;   // + the vector's 16 scale bytes
-constexpr uint32_t kSfStages = 4 * kSfBatches;
-constexpr uint32_t kATile = 128 * 128;     // bytes in shared memory (8-bit containers)
-constexpr uint32_t kATx = 128 * 64;        // bytes the TMA transaction counts (packed)
-constexpr uint32_t kBTile = 16 * 128;
+constexpr uint32_t kSfaBytes = 128 * 16;    // 128 rows x 16 scale bytes (512 K)
+constexpr uint32_t kSfSlotBytes = kSfaBytes + 128;   // + the 8 term rows' 16 scale bytes each
+constexpr uint32_t kATile = 128 * 128;     // bytes in shared memory = bytes the TMA brings
+constexpr uint32_t kBTile = 16 * 128;      // N = 16 rows; the TMA fills rows 0..7, rows 8..15 stay zero
+constexpr uint32_t kBTx = kTerms * 128;
 constexpr uint32_t kStageBytes = kATile + kBTile;
 constexpr uint32_t kThreads = 384;          // 12 warps, see the role list above
 constexpr uint32_t kTmemCols = 512;
 constexpr uint32_t kAccCol = 0;            // 2 buffers x 2 issuers x 2 phases x 16 columns
-constexpr uint32_t kSfaCol = 128;          // kSfStages x 4 columns
-constexpr uint32_t kSfbCol = 128 + 4 * kSfStages;  // kSfStages x 4 columns
+constexpr uint32_t kSfaCol = 128;          // kSfBatches x 16 columns
+constexpr uint32_t kSfbCol = 128 + 16 * kSfBatches;  // kSfBatches x 16 columns
 constexpr uint32_t kBarrierBytes = 512;
 constexpr uint32_t kSmemBytes =
     kStages * kStageBytes + kSfSlots * kSfSlotBytes + 1024 + kBarrierBytes;   // 1024: alignment slack
+static_assert(kTerms == 8, "one swizzle atom of term rows per stage");
 
 __device__ uint32_t g_mx_status = 0;
 
@@ -78,23 +78,33 @@ K3_DEVINL void tmem_st_32x16(uint32_t taddr, const uint32_t (&v)[16]) {
 }
 K3_DEVINL void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
-K3_DEVINL void tmem_ld_32x2(uint32_t taddr, uint32_t &r0, uint32_t &r1) {
-    asm volatile("tcgen05.ld.sync.aligned.32x32b.x2.b32 {%0, %1}, [%2];" : "=r"(r0), "=r"(r1) : "r"(taddr) : "memory");
+// eight consecutive 32-bit columns of this warp's lane quadrant
+K3_DEVINL void tmem_ld_32x8(uint32_t taddr, uint32_t (&r)[8]) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+                 : "r"(taddr)
+                 : "memory");
 }
 
-K3_DEVINL void mma_mx(uint32_t d, uint64_t a, uint64_t b, uint32_t idesc, uint32_t sfa, uint32_t sfb,
-                      uint32_t acc) {
+K3_DEVINL float sum_terms(const uint32_t (&r)[8]) {
+    return ((__uint_as_float(r[0]) + __uint_as_float(r[1])) + (__uint_as_float(r[2]) + __uint_as_float(r[3]))) +
+           ((__uint_as_float(r[4]) + __uint_as_float(r[5])) + (__uint_as_float(r[6]) + __uint_as_float(r[7])));
+}
+
+K3_DEVINL void mma_mx4(uint32_t d, uint64_t a, uint64_t b, uint32_t idesc, uint32_t sfa, uint32_t sfb,
+                       uint32_t acc) {
     asm volatile(
         "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %6, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::mxf8f6f4.block_scale.scale_vec::1X [%0], %1, %2, %3, [%4], [%5], p;\n\t}" ::
+        "tcgen05.mma.cta_group::1.kind::mxf4.block_scale.scale_vec::2X [%0], %1, %2, %3, [%4], [%5], p;\n\t}" ::
             "r"(d), "l"(a), "l"(b), "r"(idesc), "r"(sfa), "r"(sfb), "r"(acc)
         : "memory");
 }
 
-// Block-scaled instruction descriptor: A = E2M1 (5), B = E4M3 (0), UE8M0 scales,
-// M = 128, N = 16, K-major operands; sf = which byte of the 32-bit scale column.
-K3_DEVINL uint32_t make_idesc_mx(uint32_t sf) {
-    return (5u << 7) | (0u << 10) | ((16u >> 3) << 17) | (1u << 23) | ((128u >> 4) << 24) | (sf << 29) |
+// Block-scaled instruction descriptor: A = B = E2M1 (1), UE8M0 scales, M = 128, N = 16,
+// K = 64, K-major operands; sf = first of the two scale bytes (0 or 2) of the 32-bit
+// scale column that this MMA's two 32-element blocks use.
+K3_DEVINL uint32_t make_idesc_mx4(uint32_t sf) {
+    return (1u << 7) | (1u << 10) | ((16u >> 3) << 17) | (1u << 23) | ((128u >> 4) << 24) | (sf << 29) |
            (sf << 4);
 }
 
@@ -107,33 +117,19 @@ struct MxArgs {
     uint32_t shared_vector;     // 1: every rank uses activation vector 0 (gate/up)
     int activation;
     float beta, linear_beta;
-    uint8_t *act_hl;            // gate/up: E4M3 split of the produced activation [2*ranks, w_rows]
-    uint8_t *act_sf;            //          and its block scales [ranks, w_rows/32]
+    uint8_t *act_terms;         // gate/up: E2M1 terms of the produced activation [ranks * kTerms, w_rows / 2]
+    uint8_t *act_sf;            //          and their block scales [ranks * kTerms, w_rows / 32]
     DecodeTail tail;            // down: the layer's tail (tail.out null: none)
 };
 
-// value -> (hi, lo) E4M3 pair and block scale of a 32-element block held one
-// element per lane
-K3_DEVINL void split_block_e4m3(float val, uint8_t &hi, uint8_t &lo, uint8_t &scale_byte) {
-    const float mx = warp_max(fabsf(val));
-    int e = 0;
-    if (mx > 0.f && mx < 3.0e38f) e = (int)((__float_as_uint(mx) >> 23) & 0xffu) - 127 - 7;
-    e = max(-126, min(127, e));
-    const float scaled = val * __uint_as_float((uint32_t)(127 - e) << 23);      // |scaled| < 256
-    hi = __nv_cvt_float_to_fp8(scaled, __NV_SATFINITE, __NV_E4M3);
-    const float hi_f = __half2float(__half(__nv_cvt_fp8_to_halfraw(hi, __NV_E4M3)));
-    lo = __nv_cvt_float_to_fp8(scaled - hi_f, __NV_SATFINITE, __NV_E4M3);
-    scale_byte = (uint8_t)(e + 127);
-}
-
 struct MxMaps {
-    CUtensorMap a0, a1;        // packed E2M1 weights of phase 0 / phase 1
-    CUtensorMap b;             // vector terms (E4M3), rows 2v = hi, 2v+1 = lo
+    CUtensorMap a0, a1;        // packed E2M1 weights of phase 0 / phase 1, as bytes [rows, K/2]
+    CUtensorMap b;             // vector terms, packed E2M1: rows kTerms*v .. kTerms*v + 7 of [vectors*kTerms, K/2]
     CUtensorMap sfa0, sfa1;    // weight block scales [rows, K/32]
-    CUtensorMap sfb;           // vector block scales [vectors, K/32]
+    CUtensorMap sfb;           // term block scales [vectors*kTerms, K/32]
 };
 
-// kGateUp: two phases (w1 then w3) into accumulator columns [0,16) and [16,32),
+// kGateUp: two phases (w1 then w3) into accumulator columns [0,16) and [16,32) per issuer,
 // fused activation.  Otherwise one phase, plain bf16 output.
 template <bool kGateUp>
 __global__ void __launch_bounds__(kThreads, 1)
@@ -151,7 +147,7 @@ decode_mx_kernel(const __grid_constant__ MxMaps maps, MxArgs a) {
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(acc_empty + 2);
     volatile uint32_t *abort_flag = tmem_slot + 1;
     const uint32_t warp = threadIdx.x / kWarp, lane = threadIdx.x % kWarp;
-    const uint32_t steps = a.k / 128u;
+    const uint32_t steps = a.k / kKStage;
     const uint32_t phases = kGateUp ? 2u : 1u;
     const uint32_t tiles = a.w_rows / 128u;
     const uint32_t items = a.ranks * tiles;
@@ -176,6 +172,13 @@ decode_mx_kernel(const __grid_constant__ MxMaps maps, MxArgs a) {
         }
         fence_barrier_init();
     }
+    // rows 8..15 of every stage's N = 16 operand (its second swizzle atom) are never
+    // written by the TMA: zero them once
+    for (uint32_t i = threadIdx.x; i < kStages * (kBTile - kBTx) / 16u; i += blockDim.x) {
+        const uint32_t stage = i / ((kBTile - kBTx) / 16u), unit = i % ((kBTile - kBTx) / 16u);
+        reinterpret_cast<uint4 *>(base + stage * kStageBytes + kATile + kBTx)[unit] = make_uint4(0u, 0u, 0u, 0u);
+    }
+    fence_proxy_async();
     if (warp == 1) {
         tmem_alloc(tmem_slot, kTmemCols);
         tmem_relinquish();
@@ -186,7 +189,7 @@ decode_mx_kernel(const __grid_constant__ MxMaps maps, MxArgs a) {
     const uint32_t tmem = *tmem_slot;
 
     if (warp == 0) {
-        // weight tile + vector tile of every K step
+        // weight tile + term tile of every stage
         if (lane == 0) {
             prefetch_tensormap(&maps.a0);
             prefetch_tensormap(&maps.a1);
@@ -198,14 +201,14 @@ decode_mx_kernel(const __grid_constant__ MxMaps maps, MxArgs a) {
                 const uint32_t id = a.ids[rank];
                 if (id < a.first_local || id >= a.first_local + a.local_count) continue;
                 const int32_t y = (int32_t)((id - a.first_local) * a.w_rows + tile * 128u);
-                const int32_t yb = a.shared_vector ? 0 : (int32_t)(2u * rank);
+                const int32_t yb = a.shared_vector ? 0 : (int32_t)(kTerms * rank);
                 for (uint32_t p = 0; ok && p < phases; p++) {
                     const void *map_a = p == 0 ? (const void *)&maps.a0 : (const void *)&maps.a1;
                     for (uint32_t st = 0; st < steps; st++) {
                         if (!mbar_wait(&empty[s], ph ^ 1u, abort_flag)) { ok = false; break; }
                         unsigned char *dst = base + s * kStageBytes;
-                        mbar_arrive_expect_tx(&full[s], kATx + kBTile);
-                        tma_load_2d(dst, map_a, &full[s], (int32_t)(st * 128u), y);
+                        mbar_arrive_expect_tx(&full[s], kATile + kBTx);
+                        tma_load_2d(dst, map_a, &full[s], (int32_t)(st * 128u), y);            // x in bytes
                         tma_load_2d(dst + kATile, &maps.b, &full[s], (int32_t)(st * 128u), yb);
                         if (++s == kStages) { s = 0; ph ^= 1u; }
                     }
@@ -213,8 +216,8 @@ decode_mx_kernel(const __grid_constant__ MxMaps maps, MxArgs a) {
             }
         }
     } else if (warp == 10) {
-        // block scales of four K steps at a time: 128 weight rows x 16 bytes and the
-        // vector's 16 bytes, into the shared-memory scale ring
+        // block scales of two stages (512 K) at a time: 128 weight rows x 16 bytes and the
+        // 8 term rows x 16 bytes, into the shared-memory scale ring
         if (lane == 0) {
             prefetch_tensormap(&maps.sfa0);
             prefetch_tensormap(&maps.sfa1);
@@ -226,15 +229,15 @@ decode_mx_kernel(const __grid_constant__ MxMaps maps, MxArgs a) {
                 const uint32_t id = a.ids[rank];
                 if (id < a.first_local || id >= a.first_local + a.local_count) continue;
                 const int32_t y = (int32_t)((id - a.first_local) * a.w_rows + tile * 128u);
-                const int32_t yb = a.shared_vector ? 0 : (int32_t)rank;
+                const int32_t yb = a.shared_vector ? 0 : (int32_t)(kTerms * rank);
                 for (uint32_t p = 0; ok && p < phases; p++) {
                     const void *map_s = p == 0 ? (const void *)&maps.sfa0 : (const void *)&maps.sfa1;
-                    for (uint32_t st = 0; st < steps; st += 4u) {
+                    for (uint32_t st = 0; st < steps; st += 2u) {
                         if (!mbar_wait(&sfs_empty[s], ph ^ 1u, abort_flag)) { ok = false; break; }
                         unsigned char *dst = sf_smem + s * kSfSlotBytes;
-                        mbar_arrive_expect_tx(&sfs_full[s], kSfaBytes + 16u);
-                        tma_load_2d(dst, map_s, &sfs_full[s], (int32_t)(st * 4u), y);
-                        tma_load_2d(dst + kSfaBytes, &maps.sfb, &sfs_full[s], (int32_t)(st * 4u), yb);
+                        mbar_arrive_expect_tx(&sfs_full[s], kSfaBytes + kTerms * 16u);
+                        tma_load_2d(dst, map_s, &sfs_full[s], (int32_t)(st * 8u), y);
+                        tma_load_2d(dst + kSfaBytes, &maps.sfb, &sfs_full[s], (int32_t)(st * 8u), yb);
                         if (++s == kSfSlots) { s = 0; ph ^= 1u; }
                     }
                 }
@@ -242,8 +245,9 @@ decode_mx_kernel(const __grid_constant__ MxMaps maps, MxArgs a) {
         }
     } else if (warp == 1 || warp == 11) {
         // Two MMA issuers: the issue loop of one thread, not the tensor pipe, bounds
-        // the rate of these small MMAs, so warp 1 takes the even K steps and warp 11
+        // the rate of these small MMAs, so warp 1 takes the even stages and warp 11
         // the odd ones, each into its own accumulator columns (summed in the epilogue).
+        // A scale batch covers two stages, one per issuer.
         if (lane == 0) {
             const uint32_t q = warp == 1 ? 0u : 1u;
             uint32_t s = q, ph = 0, buf = 0, pacc = 0, sb = 0, sph = 0;
@@ -257,8 +261,7 @@ decode_mx_kernel(const __grid_constant__ MxMaps maps, MxArgs a) {
                 for (uint32_t p = 0; ok && p < phases; p++) {
                     const uint32_t d = tmem + kAccCol + buf * 64u + q * 32u + p * 16u;
                     for (uint32_t st = q; st < steps; st += 2u) {
-                        if (!mbar_wait(&full[s], ph, abort_flag) ||
-                            ((st & 3u) == q && !mbar_wait(&sf_full[sb], sph, abort_flag))) {
+                        if (!mbar_wait(&full[s], ph, abort_flag) || !mbar_wait(&sf_full[sb], sph, abort_flag)) {
                             ok = false;
                             break;
                         }
@@ -266,19 +269,19 @@ decode_mx_kernel(const __grid_constant__ MxMaps maps, MxArgs a) {
                         unsigned char *src = base + s * kStageBytes;
                         const uint64_t da = make_desc_sw128(smem_u32(src));
                         const uint64_t db = make_desc_sw128(smem_u32(src + kATile));
-                        const uint32_t sfs = (sb * 4u + (st & 3u)) * 4u;
 #pragma unroll
                         for (uint32_t j = 0; j < 4u; j++) {
-                            mma_mx(d, da + 2u * j, db + 2u * j, make_idesc_mx(j), tmem + kSfaCol + sfs,
-                                   tmem + kSfbCol + sfs, (st != q || j != 0u) ? 1u : 0u);
+                            // stage q of the batch holds the 128-K chunks 2q and 2q + 1 (4 columns
+                            // each); MMA j takes scale bytes 2 (j & 1), 2 (j & 1) + 1 of chunk 2q + j / 2
+                            const uint32_t sfs = sb * 16u + (2u * q + (j >> 1)) * 4u;
+                            mma_mx4(d, da + 2u * j, db + 2u * j, make_idesc_mx4(2u * (j & 1u)), tmem + kSfaCol + sfs,
+                                    tmem + kSfbCol + sfs, (st != q || j != 0u) ? 1u : 0u);
                         }
                         mma_commit(&empty[s]);
                         s += 2u;
                         if (s >= kStages) { s -= kStages; ph ^= 1u; }
-                        if ((st & 3u) == q + 2u) {
-                            mma_commit(&sf_empty[sb]);
-                            if (++sb == kSfBatches) { sb = 0; sph ^= 1u; }
-                        }
+                        mma_commit(&sf_empty[sb]);
+                        if (++sb == kSfBatches) { sb = 0; sph ^= 1u; }
                     }
                 }
                 if (!ok) break;
@@ -295,17 +298,19 @@ decode_mx_kernel(const __grid_constant__ MxMaps maps, MxArgs a) {
         for (uint32_t it = blockIdx.x; ok && it < items; it += gridDim.x) {
             const uint32_t id = a.ids[it / tiles];
             if (id < a.first_local || id >= a.first_local + a.local_count) continue;
-            for (uint32_t st = 0; st < phases * steps; st += 4u) {
+            for (uint32_t st = 0; st < phases * steps; st += 2u) {
                 if (!mbar_wait(&sfs_full[ss], ssph, abort_flag)) { ok = false; break; }
                 const unsigned char *src = sf_smem + ss * kSfSlotBytes;
                 uint4 cur[4];
 #pragma unroll
                 for (uint32_t c = 0; c < 4u; c++)
                     cur[c] = *reinterpret_cast<const uint4 *>(src + (32u * c + lane) * 16u);
-                const uint4 curb = *reinterpret_cast<const uint4 *>(src + kSfaBytes);
+                // scale rows of the N operand sit in lanes 0..15 of the first column of a group:
+                // term rows 0..7 (lanes 8.. repeat them: those operand rows are zero)
+                const uint4 curb = *reinterpret_cast<const uint4 *>(src + kSfaBytes + (lane & (kTerms - 1u)) * 16u);
                 if (!mbar_wait(&sf_empty[sb], sph ^ 1u, abort_flag)) { ok = false; break; }
                 tc_fence_after();
-                // column (step q, row group c) = q * 4 + c of the batch's 16 columns
+                // column (128-K chunk q, row group c) = q * 4 + c of the batch's 16 columns
                 const uint32_t va[16] = {cur[0].x, cur[1].x, cur[2].x, cur[3].x, cur[0].y, cur[1].y,
                                          cur[2].y, cur[3].y, cur[0].z, cur[1].z, cur[2].z, cur[3].z,
                                          cur[0].w, cur[1].w, cur[2].w, cur[3].w};
@@ -338,33 +343,32 @@ decode_mx_kernel(const __grid_constant__ MxMaps maps, MxArgs a) {
             if (!mbar_wait(&acc_full[buf], pacc, abort_flag)) break;
             tc_fence_after();
             const uint32_t t0 = tmem + ((32u * quad) << 16) + kAccCol + buf * 64u;
-            uint32_t h0, l0, h1 = 0, l1 = 0, h2, l2, h3 = 0, l3 = 0;
-            tmem_ld_32x2(t0, h0, l0);                       // even K steps
-            tmem_ld_32x2(t0 + 32u, h2, l2);                 // odd K steps
+            uint32_t e0[8], o0[8], e1[8], o1[8];
+            tmem_ld_32x8(t0, e0);                           // even stages
+            tmem_ld_32x8(t0 + 32u, o0);                     // odd stages
             if (kGateUp) {
-                tmem_ld_32x2(t0 + 16u, h1, l1);
-                tmem_ld_32x2(t0 + 48u, h3, l3);
+                tmem_ld_32x8(t0 + 16u, e1);
+                tmem_ld_32x8(t0 + 48u, o1);
             }
             tmem_ld_wait();
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(&acc_empty[buf]);
             if (++buf == 2u) { buf = 0; pacc ^= 1u; }
-            const float v0 = (__uint_as_float(h0) + __uint_as_float(l0)) + (__uint_as_float(h2) + __uint_as_float(l2));
+            const float v0 = sum_terms(e0) + sum_terms(o0);
             uint16_t *dst = a.out + (uint64_t)rank * a.w_rows + tile * 128u + m;
             if (kGateUp) {
-                const float v1 = (__uint_as_float(h1) + __uint_as_float(l1)) + (__uint_as_float(h3) + __uint_as_float(l3));
+                const float v1 = sum_terms(e1) + sum_terms(o1);
                 const float g = bf16_bits_to_float(float_to_bf16_bits(v0));
                 const float u = bf16_bits_to_float(float_to_bf16_bits(v1));
                 const uint16_t act_bits = float_to_bf16_bits(activation(g, u, a.activation, a.beta, a.linear_beta));
                 *dst = act_bits;
-                if (a.act_hl != nullptr) {
-                    uint8_t hi, lo, sb;
-                    split_block_e4m3(bf16_bits_to_float(act_bits), hi, lo, sb);
-                    const uint32_t col = tile * 128u + m;
-                    a.act_hl[(uint64_t)(2u * rank) * a.w_rows + col] = hi;
-                    a.act_hl[(uint64_t)(2u * rank + 1u) * a.w_rows + col] = lo;
-                    if (lane == 0) a.act_sf[(uint64_t)rank * (a.w_rows / 32u) + col / 32u] = sb;
+                if (a.act_terms != nullptr) {
+                    uint32_t code[kTerms], sbyte[kTerms];
+                    split_block_e2m1(bf16_bits_to_float(act_bits), code, sbyte);
+                    store_block_e2m1(a.act_terms + (uint64_t)rank * kTerms * (a.w_rows / 2u),
+                                     a.act_sf + (uint64_t)rank * kTerms * (a.w_rows / 32u), a.w_rows / 2u,
+                                     a.w_rows / 32u, tile * 4u + quad, code, sbyte, lane);
                 }
             } else {
                 *dst = float_to_bf16_bits(v0);
@@ -398,31 +402,20 @@ PFN_cuTensorMapEncodeTiled_v12000 encode_fn() {
     return fn;
 }
 
-bool map_fp4(CUtensorMap *map, const void *ptr, uint64_t rows, uint64_t k) {
+// bytes [rows, row_bytes], box = 128 bytes x box_rows rows, 128-byte swizzle
+bool map_bytes(CUtensorMap *map, const void *ptr, uint64_t rows, uint64_t row_bytes, uint32_t box_rows) {
     auto fn = encode_fn();
-    if (!fn || (((uintptr_t)ptr) & 31u) != 0) return false;
-    const cuuint64_t dims[2] = {k, rows};
-    const cuuint64_t strides[1] = {k / 2u};
-    const cuuint32_t box[2] = {128, 128};
-    const cuuint32_t es[2] = {1, 1};
-    return fn(map, CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B, 2, const_cast<void *>(ptr), dims, strides, box,
-              es, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-              CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
-}
-
-bool map_u8(CUtensorMap *map, const void *ptr, uint64_t rows, uint64_t k) {
-    auto fn = encode_fn();
-    if (!fn || (((uintptr_t)ptr) & 15u) != 0) return false;
-    const cuuint64_t dims[2] = {k, rows};
-    const cuuint64_t strides[1] = {k};
-    const cuuint32_t box[2] = {128, 16};
+    if (!fn || (((uintptr_t)ptr) & 15u) != 0 || row_bytes % 16u != 0) return false;
+    const cuuint64_t dims[2] = {row_bytes, rows};
+    const cuuint64_t strides[1] = {row_bytes};
+    const cuuint32_t box[2] = {128, box_rows};
     const cuuint32_t es[2] = {1, 1};
     return fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void *>(ptr), dims, strides, box, es,
               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-// block scales [rows, K/32] bytes, box = 16 bytes (four K steps) x box_rows rows
+// block scales [rows, K/32] bytes, box = 16 bytes (512 K) x box_rows rows
 bool map_sf(CUtensorMap *map, const void *ptr, uint64_t rows, uint64_t k, uint32_t box_rows) {
     auto fn = encode_fn();
     if (!fn || (((uintptr_t)ptr) & 15u) != 0) return false;
@@ -455,31 +448,32 @@ bool k3_decode_mx_status_clear() {
 size_t k3_decode_mx_scratch_bytes(const k3_moe_layer_desc *d) {
     // token terms and scales, activation terms and scales, arrival words of the tail,
     // scores and choices of the routing step
-    return (size_t)2 * d->hidden + d->hidden / 32u + (size_t)2 * d->top_k * d->expert_hidden +
-           (size_t)d->top_k * d->expert_hidden / 32u + (size_t)d->hidden / 32u * 4u + 2u * 1024u * 4u + 6u * 256u;
+    return (size_t)kTerms * d->hidden / 2u + (size_t)kTerms * d->hidden / 32u +
+           (size_t)kTerms * d->top_k * d->expert_hidden / 2u + (size_t)kTerms * d->top_k * d->expert_hidden / 32u +
+           (size_t)d->hidden / 32u * 4u + 2u * 1024u * 4u + 6u * 256u;
 }
 
 bool k3_decode_mx_supported(const k3_moe_layer_desc *d) {
     return d->hidden % 512u == 0 && d->expert_hidden % 512u == 0 && d->top_k <= 32u && encode_fn() != nullptr &&
            d->shared_hidden <= 8192u &&
-           ((((uintptr_t)d->w1_packed) | ((uintptr_t)d->w3_packed) | ((uintptr_t)d->w2_packed)) & 31u) == 0 &&
+           ((((uintptr_t)d->w1_packed) | ((uintptr_t)d->w3_packed) | ((uintptr_t)d->w2_packed)) & 15u) == 0 &&
            ((((uintptr_t)d->w1_scales) | ((uintptr_t)d->w3_scales) | ((uintptr_t)d->w2_scales)) & 15u) == 0;
 }
 
-void k3_decode_mx_vector_scratch(const k3_moe_layer_desc *d, void *scratch, void **x_hl, void **x_sf) {
+void k3_decode_mx_vector_scratch(const k3_moe_layer_desc *d, void *scratch, void **x_terms, void **x_sf) {
     auto align = [](uint8_t *p) { return (uint8_t *)(((uintptr_t)p + 255u) & ~(uintptr_t)255u); };
-    uint8_t *hl = align((uint8_t *)scratch);
-    *x_hl = hl;
-    *x_sf = align(hl + (size_t)2 * d->hidden);
+    uint8_t *terms = align((uint8_t *)scratch);
+    *x_terms = terms;
+    *x_sf = align(terms + (size_t)kTerms * d->hidden / 2u);
 }
 
 void *k3_decode_mx_tail_words(const k3_moe_layer_desc *d, void *scratch) {
     auto align = [](uint8_t *p) { return (uint8_t *)(((uintptr_t)p + 255u) & ~(uintptr_t)255u); };
-    uint8_t *x_hl = nullptr, *x_sf = nullptr;
-    k3_decode_mx_vector_scratch(d, scratch, (void **)&x_hl, (void **)&x_sf);
-    uint8_t *a_hl = align(x_sf + d->hidden / 32u);
-    uint8_t *a_sf = align(a_hl + (size_t)2 * d->top_k * d->expert_hidden);
-    return align(a_sf + (size_t)d->top_k * d->expert_hidden / 32u);
+    uint8_t *x_terms = nullptr, *x_sf = nullptr;
+    k3_decode_mx_vector_scratch(d, scratch, (void **)&x_terms, (void **)&x_sf);
+    uint8_t *a_terms = align(x_sf + (size_t)kTerms * d->hidden / 32u);
+    uint8_t *a_sf = align(a_terms + (size_t)kTerms * d->top_k * d->expert_hidden / 2u);
+    return align(a_sf + (size_t)kTerms * d->top_k * d->expert_hidden / 32u);
 }
 
 void *k3_decode_mx_route_words(const k3_moe_layer_desc *d, void *scratch) {
@@ -488,15 +482,15 @@ void *k3_decode_mx_route_words(const k3_moe_layer_desc *d, void *scratch) {
 }
 
 // Routed experts of one token: act [top_k, I] and rows_out [top_k, hidden] in rank
-// order (ids on the device) from the token's E4M3 form in `scratch`.
+// order (ids on the device) from the token's E2M1 terms in `scratch`.
 bool k3_decode_mx_experts(const k3_moe_layer_desc *d, const void *ids, void *act, void *rows_out,
                           void *scratch, void *between, const k3_decode_tail *tail, cudaStream_t stream) {
     const uint32_t H = d->hidden, I = d->expert_hidden, k = d->top_k;
     auto align = [](uint8_t *p) { return (uint8_t *)(((uintptr_t)p + 255u) & ~(uintptr_t)255u); };
-    uint8_t *x_hl = nullptr, *x_sf = nullptr;
-    k3_decode_mx_vector_scratch(d, scratch, (void **)&x_hl, (void **)&x_sf);
-    uint8_t *a_hl = align(x_sf + H / 32u);
-    uint8_t *a_sf = align(a_hl + (size_t)2 * k * I);
+    uint8_t *x_terms = nullptr, *x_sf = nullptr;
+    k3_decode_mx_vector_scratch(d, scratch, (void **)&x_terms, (void **)&x_sf);
+    uint8_t *a_terms = align(x_sf + (size_t)kTerms * H / 32u);
+    uint8_t *a_sf = align(a_terms + (size_t)kTerms * k * I / 2u);
     const size_t smem = kSmemBytes;
     if (!set_max_dynamic_smem((const void *)decode_mx_kernel<true>, smem) ||
         !set_max_dynamic_smem((const void *)decode_mx_kernel<false>, smem)) {
@@ -533,11 +527,14 @@ bool k3_decode_mx_experts(const k3_moe_layer_desc *d, const void *ids, void *act
         auto it = cached.find(key);
         if (it == cached.end()) {
             const uint64_t total = (uint64_t)d->local_expert_count;
-            if (!map_fp4(&gu.a0, d->w1_packed, total * I, H) || !map_fp4(&gu.a1, d->w3_packed, total * I, H) ||
-                !map_u8(&gu.b, x_hl, 2, H) || !map_sf(&gu.sfa0, d->w1_scales, total * I, H, 128) ||
-                !map_sf(&gu.sfa1, d->w3_scales, total * I, H, 128) || !map_sf(&gu.sfb, x_sf, 1, H, 1) ||
-                !map_fp4(&dn.a0, d->w2_packed, total * H, I) || !map_u8(&dn.b, a_hl, 2ull * k, I) ||
-                !map_sf(&dn.sfa0, d->w2_scales, total * H, I, 128) || !map_sf(&dn.sfb, a_sf, k, I, 1)) {
+            if (!map_bytes(&gu.a0, d->w1_packed, total * I, H / 2u, 128) ||
+                !map_bytes(&gu.a1, d->w3_packed, total * I, H / 2u, 128) ||
+                !map_bytes(&gu.b, x_terms, kTerms, H / 2u, kTerms) || !map_sf(&gu.sfa0, d->w1_scales, total * I, H, 128) ||
+                !map_sf(&gu.sfa1, d->w3_scales, total * I, H, 128) || !map_sf(&gu.sfb, x_sf, kTerms, H, kTerms) ||
+                !map_bytes(&dn.a0, d->w2_packed, total * H, I / 2u, 128) ||
+                !map_bytes(&dn.b, a_terms, (uint64_t)kTerms * k, I / 2u, kTerms) ||
+                !map_sf(&dn.sfa0, d->w2_scales, total * H, I, 128) ||
+                !map_sf(&dn.sfb, a_sf, (uint64_t)kTerms * k, I, kTerms)) {
                 return false;
             }
             dn.a1 = dn.a0;
@@ -560,7 +557,7 @@ bool k3_decode_mx_experts(const k3_moe_layer_desc *d, const void *ids, void *act
     const int sms = sm_count();
     // gate/up + activation
     a.out = (uint16_t *)act;
-    a.act_hl = a_hl;
+    a.act_terms = a_terms;
     a.act_sf = a_sf;
     a.w_rows = I;
     a.k = H;
@@ -583,7 +580,7 @@ bool k3_decode_mx_experts(const k3_moe_layer_desc *d, const void *ids, void *act
         a.tail.hidden = H;
     }
     a.out = (uint16_t *)rows_out;
-    a.act_hl = nullptr;
+    a.act_terms = nullptr;
     a.act_sf = nullptr;
     a.w_rows = H;
     a.k = I;

@@ -56,10 +56,10 @@ bool k3_decode_layer(const k3_moe_layer_desc *desc, const void *x, void *logits,
 // Block-scaled tensor-core expert products for one token (k3_decode_mx.cu).
 bool k3_decode_mx_supported(const k3_moe_layer_desc *desc);
 size_t k3_decode_mx_scratch_bytes(const k3_moe_layer_desc *desc);
-// where the token's two-term E4M3 form lives inside `scratch`: x_hl [2, hidden]
-// (row 0 = hi terms, row 1 = lo terms) and x_sf [hidden / 32] block scales
-void k3_decode_mx_vector_scratch(const k3_moe_layer_desc *desc, void *scratch, void **x_hl, void **x_sf);
-// Expert products of one token from its E4M3 form already in `scratch`;
+// where the token's E2M1 terms live inside `scratch`: x_terms [8, hidden / 2] packed
+// nibbles (one row per term) and x_sf [8, hidden / 32] block scales
+void k3_decode_mx_vector_scratch(const k3_moe_layer_desc *desc, void *scratch, void **x_terms, void **x_sf);
+// Expert products of one token from its E2M1 terms already in `scratch`;
 // `between` (a CUDA event or null) is recorded between gate/up and down.
 // With `tail` the down kernel's epilogue takes part in the layer's tail
 // (k3_decode_tail.cuh): it counts an arrival per finished row and 32-column group in
