@@ -62,6 +62,8 @@ struct DecodeArgs {
     uint8_t *x_terms, *x_sf;  // front: E2M1 terms of x ([kTerms, hidden/2] packed, [kTerms, hidden/32]) or null
     float *route_words;       // front: [2][1024] scores and choices written by the row tasks, or null
     unsigned int *ticket;     // front: completion counter of this call
+    uint32_t *control;        // front: words the expert kernel needs zeroed (64), or null
+    uint32_t route_elsewhere; // front: only the row tasks; the expert kernel routes from the scores
     uint32_t shared_elsewhere;  // front: the shared expert runs in its own kernels (side stream)
     DecodeTail tail;            // shared down: its share of the layer's tail (tail.out null: none)
 };
@@ -102,6 +104,7 @@ decode_front_kernel(DecodeArgs a) {
     const uint32_t warp = threadIdx.x / kWarp, lane = threadIdx.x % kWarp;
     const uint32_t E = a.d.expert_count, S = a.d.shared_hidden, H = a.d.hidden, k = a.d.top_k;
     const uint32_t split_tasks = a.x_terms ? (H / 32u + 7u) / 8u : 0u;        // 8 blocks (one per warp) each
+    if (blockIdx.x == 0 && a.control != nullptr && threadIdx.x < 64u) a.control[threadIdx.x] = 0u;
     if ((reinterpret_cast<uintptr_t>(a.x) & 15u) == 0u && H % 8u == 0u) {
         // 16 bytes per load: the whole token is in flight after at most four loads per thread
         for (uint32_t i = threadIdx.x; i < H / 8u; i += blockDim.x) {
@@ -127,8 +130,12 @@ decode_front_kernel(DecodeArgs a) {
     // on stale data without storing anything, so that those instructions are already
     // cached when the last worker block needs them - on its own they cost a chain of
     // instruction fetches from memory several times longer than the arithmetic.
-    const bool warmer = blockIdx.x == gridDim.x - 1u;
-    const uint32_t workers = gridDim.x - 1u;
+    // (when the routing is done by the expert kernel there is no such block and no last-block step)
+    const bool warmer = a.route_elsewhere == 0u && blockIdx.x == gridDim.x - 1u;
+    const uint32_t workers = a.route_elsewhere != 0u ? gridDim.x : gridDim.x - 1u;
+    // the kernel queued behind this one with programmatic serialization may be placed as
+    // soon as every block of this grid has started
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     for (uint32_t task = blockIdx.x; !warmer && task < tasks_total; task += workers) {
         if (task < E) {
             // the row's bias is fetched with the row, so the routing step finds score and
@@ -177,6 +184,7 @@ decode_front_kernel(DecodeArgs a) {
         }
         __syncthreads();            // `red` is reused by the next task
     }
+    if (a.route_elsewhere != 0u) return;
     if (!warmer) {
         __threadfence();
         __syncthreads();
@@ -551,6 +559,7 @@ decode_shared_down_kernel(DecodeArgs a) {
     }
 }
 
+
 }  // namespace
 
 uint32_t k3_decode_status() {
@@ -640,6 +649,8 @@ bool k3_decode_layer(const k3_moe_layer_desc *d, const void *x, void *logits, vo
     if (mx) {
         k3_decode_mx_vector_scratch(d, scratch, (void **)&a.x_terms, (void **)&a.x_sf);
         a.route_words = (float *)k3_decode_mx_route_words(d, scratch);
+        a.control = (uint32_t *)k3_decode_mx_control_words(d, scratch);
+        a.route_elsewhere = 1u;
     }
     static std::atomic<uint32_t> next_ticket{0};
     // address of the ticket array on the current device (looked up once per device)
@@ -718,8 +729,8 @@ bool k3_decode_layer(const k3_moe_layer_desc *d, const void *x, void *logits, vo
     };
     if (side) {
         if (!set_max_dynamic_smem((const void *)decode_front_kernel<false>, front_smem)) return false;
-        decode_front_kernel<false><<<std::min<uint32_t>(front_tasks, (uint32_t)sms * 4u - 1u) + 1u, 256, front_smem,
-                                     stream>>>(a);
+        decode_front_kernel<false><<<std::min<uint32_t>(front_tasks, (uint32_t)sms * 4u - 1u) + (mx ? 0u : 1u), 256,
+                                     front_smem, stream>>>(a);
     } else {
         if (!set_max_dynamic_smem((const void *)decode_front_kernel<true>, front_smem)) return false;
         decode_front_kernel<true><<<std::min<uint32_t>(front_tasks, (uint32_t)sms * 2u - 1u) + 1u, 256, front_smem,
@@ -732,7 +743,7 @@ bool k3_decode_layer(const k3_moe_layer_desc *d, const void *x, void *logits, vo
     if (!mark(1) || !mark(2)) return false;
     if (mx) {
         k3_decode_tail tail{out, weights, a.tail.shared, residual, a.tail.epoch, a.tail.expected};
-        if (!k3_decode_mx_experts(d, ids, act, rows_out, scratch, events ? events[3] : nullptr,
+        if (!k3_decode_mx_experts(d, ids, weights, a.route_words, act, rows_out, scratch, events ? events[3] : nullptr,
                                   fused_tail ? &tail : nullptr, stream) ||
             !mark(4)) {
             return false;

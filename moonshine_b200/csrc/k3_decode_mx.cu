@@ -1,5 +1,6 @@
 // One-token expert products on the packed block-scaled tensor-core path
-// (tcgen05.mma kind::mxf4, 32-element blocks with E8M0 scales).
+// (tcgen05.mma kind::mxf4, 32-element blocks with E8M0 scales), gate/up and down in
+// ONE persistent launch.
 //
 // The MXFP4 weights are consumed as they are stored: packed E2M1 nibbles arrive by
 // TMA as plain bytes (128 rows x 128 bytes = 256 K elements per box, the layout the
@@ -10,21 +11,26 @@
 // N = 16 operand, so accumulator columns 0..7 hold the partial dot products and
 // their sum is the result.
 //
-// One CTA per SM, persistent over (expert rank, 128-row tile) items:
-//   warp 0      TMA producer (A: 128 rows x 256 K, B: 8 term rows x 256 K per stage)
-//   warp 1      MMA issuer: 4 MMAs of K=64 per stage, even stages
-//   warps 2-5   scale writers: per batch the tile's 128x16 E8M0 bytes (512 K, two
-//               stages) -> 16 TMEM columns (lane = row % 32, column = row / 32,
-//               copied into every lane quadrant) plus the terms' block scales
-//   warps 6-9   epilogue: tcgen05.ld of the term columns, sum, bf16, activation;
-//               the gate/up epilogue also splits the activation it produces into
-//               the E2M1 terms the down projection reads
-//   warp 10     scale producer: block scales of two stages into a shared-memory ring
-//   warp 11     second MMA issuer (odd stages, its own accumulator columns)
-// Every barrier wait is bounded (see k3_tc_ptx.cuh).
+// Work items: G = (rank, 128-row tile) of gate and up over the hidden width, with the
+// activation fused; D = (rank, 128-row tile) of down over the expert width.  All G
+// items come first in the numbering, then the D items rank by rank.  One CTA per SM
+// draws items from a global counter, so the byte load evens out whatever the item mix;
+// a D item needs its rank's activation, which the G items' epilogues publish through a
+// per-rank arrival counter - only the (small) term loads of a D item wait for it, the
+// weight stream never does.  Warps:
+//   0       weight producer: draws items, streams 16 KB weight tiles through a TMA ring
+//   1, 11   MMA issuers: 4 MMAs of K=64 per stage, even / odd stages, own accumulators
+//   2-5     scale writers: weight scales shared memory -> tensor memory, term scales too
+//   6-9     epilogue: tcgen05.ld of the term columns, sum, bf16; G: activation, its
+//           E2M1 terms, arrival; D: output row and the layer's tail
+//   10      weight-scale producer (TMA, 512 K per box)
+//   12      term producer: the token's terms once (they serve every G item), then per D
+//           item the rank's activation terms and scales, after its arrival count is full
+// Every wait is bounded (see k3_tc_ptx.cuh).
 #include "k3_decode_tail.cuh"
 #include "k3_e2m1_terms.cuh"
 #include "k3_grouped.h"
+#include "k3_route_block.cuh"
 #include "k3_rowdot.cuh"
 #include "k3_tc_ptx.cuh"
 
@@ -42,31 +48,28 @@ using namespace k3::tc;
 
 namespace {
 
-constexpr uint32_t kStages = 12;            // TMA ring of weight / term tiles
+constexpr uint32_t kStages = 8;             // TMA ring of weight tiles
 constexpr uint32_t kKStage = 256;           // K elements per stage (128 packed bytes per row)
 constexpr uint32_t kSfBatches = 6;          // scale ring in tensor memory: batches of 2 stages (512 K)
-constexpr uint32_t kSfSlots = 4;            // scale ring in shared memory (one batch per slot)
+constexpr uint32_t kSfSlots = 4;            // weight-scale ring in shared memory (one batch per slot)
 constexpr uint32_t kSfaBytes = 128 * 16;    // 128 rows x 16 scale bytes (512 K)
-constexpr uint32_t kSfSlotBytes = kSfaBytes + 128;   // + the 8 term rows' 16 scale bytes each
 constexpr uint32_t kATile = 128 * 128;     // bytes in shared memory = bytes the TMA brings
-constexpr uint32_t kBTile = 16 * 128;      // N = 16 rows; the TMA fills rows 0..7, rows 8..15 stay zero
-constexpr uint32_t kBTx = kTerms * 128;
-constexpr uint32_t kStageBytes = kATile + kBTile;
-constexpr uint32_t kThreads = 384;          // 12 warps, see the role list above
+constexpr uint32_t kBAtom = kTerms * 128;   // one stage of term rows: one 8-row swizzle atom
+constexpr uint32_t kSfbBatch = kTerms * 16; // term scales of one batch: 8 rows x 16 bytes
+constexpr uint32_t kThreads = 416;          // 13 warps, see the role list above
 constexpr uint32_t kTmemCols = 512;
 constexpr uint32_t kAccCol = 0;            // 2 buffers x 2 issuers x 2 phases x 16 columns
 constexpr uint32_t kSfaCol = 128;          // kSfBatches x 16 columns
 constexpr uint32_t kSfbCol = 128 + 16 * kSfBatches;  // kSfBatches x 16 columns
-constexpr uint32_t kBarrierBytes = 512;
-constexpr uint32_t kSmemBytes =
-    kStages * kStageBytes + kSfSlots * kSfSlotBytes + 1024 + kBarrierBytes;   // 1024: alignment slack
+constexpr uint32_t kBarrierBytes = 1024;     // barriers, mailbox, the token's ids and weights
+constexpr uint32_t kItemSlots = 4;          // mailbox of drawn items, weight producer -> other roles
+constexpr uint32_t kItemReaders = 12;       // 2 issuers, 4 writers, 4 epilogue warps, scale and term producers
+constexpr uint32_t kNoItem = 0xffffffffu;
+constexpr uint32_t kControlWords = 64;      // [0] item counter, [16 + rank] arrivals of the rank's G epilogues
 static_assert(kTerms == 8, "one swizzle atom of term rows per stage");
 
 __device__ uint32_t g_mx_status = 0;
 
-K3_DEVINL void tmem_st_32x1(uint32_t taddr, uint32_t v) {
-    asm volatile("tcgen05.st.sync.aligned.32x32b.x1.b32 [%0], {%1};" ::"r"(taddr), "r"(v) : "memory");
-}
 // 16 consecutive 32-bit columns of this warp's lane quadrant in one instruction
 K3_DEVINL void tmem_st_32x16(uint32_t taddr, const uint32_t (&v)[16]) {
     asm volatile(
@@ -109,48 +112,96 @@ K3_DEVINL uint32_t make_idesc_mx4(uint32_t sf) {
 }
 
 struct MxArgs {
-    const uint32_t *ids;        // expert id per rank
-    uint16_t *out;              // [ranks, out_width] bf16
+    uint32_t *ids;              // expert id per rank: read, or written when the kernel routes
+    float *weights;             // route weights, written when the kernel routes
+    const float *route_words;   // scores [1024] and choices [1024] of the router rows, or null
+    uint32_t experts;
+    float route_scale;
+    uint16_t *act;              // [ranks, I] bf16 activation (also kept as bf16 for callers)
+    uint16_t *rows_out;         // [ranks, H] bf16 expert rows
     uint32_t ranks, first_local, local_count;
-    uint32_t w_rows;            // rows per expert per matrix
-    uint32_t k;
-    uint32_t shared_vector;     // 1: every rank uses activation vector 0 (gate/up)
+    uint32_t hidden, expert_hidden;
     int activation;
     float beta, linear_beta;
-    uint8_t *act_terms;         // gate/up: E2M1 terms of the produced activation [ranks * kTerms, w_rows / 2]
-    uint8_t *act_sf;            //          and their block scales [ranks * kTerms, w_rows / 32]
-    DecodeTail tail;            // down: the layer's tail (tail.out null: none)
+    uint8_t *act_terms;         // E2M1 terms of the activation [ranks * kTerms, I / 2]
+    uint8_t *act_sf;            // and their block scales [ranks * kTerms, I / 32]
+    uint32_t *control;          // kControlWords words, zero at launch
+    DecodeTail tail;            // the layer's tail, run by the D epilogues (tail.out null: none)
 };
 
 struct MxMaps {
-    CUtensorMap a0, a1;        // packed E2M1 weights of phase 0 / phase 1, as bytes [rows, K/2]
-    CUtensorMap b;             // vector terms, packed E2M1: rows kTerms*v .. kTerms*v + 7 of [vectors*kTerms, K/2]
-    CUtensorMap sfa0, sfa1;    // weight block scales [rows, K/32]
-    CUtensorMap sfb;           // term block scales [vectors*kTerms, K/32]
+    CUtensorMap w1, w3, w2;            // packed E2M1 weights as bytes [rows, K/2]
+    CUtensorMap s1, s3, s2;            // weight block scales [rows, K/32]
+    CUtensorMap x_terms, x_sf;         // the token: [kTerms, H/2], [kTerms, H/32]
+    CUtensorMap a_terms, a_sf;         // the activations: [ranks*kTerms, I/2], [ranks*kTerms, I/32]
 };
 
-// kGateUp: two phases (w1 then w3) into accumulator columns [0,16) and [16,32) per issuer,
-// fused activation.  Otherwise one phase, plain bf16 output.
-template <bool kGateUp>
-__global__ void __launch_bounds__(kThreads, 1)
-decode_mx_kernel(const __grid_constant__ MxMaps maps, MxArgs a) {
+// Shared-memory layout, derived the same way on the host (bytes) and in the kernel.
+struct MxSmem {
+    uint32_t ring, bg, bd, zero, sfb_g, sfb_d, sfa, bars, total;
+};
+__host__ __device__ inline MxSmem mx_smem_layout(uint32_t steps_g, uint32_t steps_d) {
+    MxSmem m;
+    uint32_t off = 0;
+    m.ring = off;  off += kStages * kATile;
+    m.bg = off;    off += steps_g * kBAtom;                 // the token's terms, every stage resident
+    m.bd = off;    off += 2u * steps_d * kBAtom;            // two D items' activation terms
+    m.zero = off;  off += kBAtom;                           // rows 8..15 of every N = 16 operand
+    m.sfb_g = off; off += (steps_g / 2u) * kSfbBatch;
+    m.sfb_d = off; off += 2u * (steps_d / 2u) * kSfbBatch;
+    m.sfa = off;   off += kSfSlots * kSfaBytes;
+    m.bars = off;  off += kBarrierBytes;
+    m.total = off + 1024u;                                  // alignment slack
+    return m;
+}
+
+// K-major 128-byte-swizzled operand of N = 16 rows whose second 8-row atom lives at
+// `second` (any 1024-byte aligned address above `first`): the stride between the atoms
+// is a field of the descriptor.
+K3_DEVINL uint64_t make_desc_sw128_split(uint32_t first, uint32_t second) {
+    uint64_t d = 0;
+    d |= (uint64_t)((first & 0x3FFFFu) >> 4);
+    d |= (uint64_t)1 << 16;
+    d |= (uint64_t)(((second - first) & 0x3FFFFu) >> 4) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)2 << 61;
+    return d;
+}
+
+K3_DEVINL void fence_proxy_async_global() { asm volatile("fence.proxy.async.global;" ::: "memory"); }
+
+K3_DEVINL uint32_t ld_acquire(const uint32_t *p) {
+    uint32_t v;
+    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+
+// (72 registers: a 256-thread block of the shared expert's kernels, which run beside this
+// one on another stream, still fits in the register file of the SM)
+__global__ void __maxnreg__(72)
+decode_experts_kernel(const __grid_constant__ MxMaps maps, MxArgs a) {
     extern __shared__ unsigned char smem_raw[];
     unsigned char *base = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
-    unsigned char *sf_smem = base + kStages * kStageBytes;
-    uint64_t *bars = reinterpret_cast<uint64_t *>(sf_smem + kSfSlots * kSfSlotBytes);
+    const uint32_t steps_g = a.hidden / kKStage, steps_d = a.expert_hidden / kKStage;
+    const MxSmem lay = mx_smem_layout(steps_g, steps_d);
+    uint64_t *bars = reinterpret_cast<uint64_t *>(base + lay.bars);
     uint64_t *full = bars, *empty = bars + kStages;
-    uint64_t *sf_full = bars + 2 * kStages;            // [kSfBatches]
-    uint64_t *sf_empty = sf_full + kSfBatches;         // [kSfBatches]
-    uint64_t *sfs_full = sf_empty + kSfBatches;        // [kSfSlots]
-    uint64_t *sfs_empty = sfs_full + kSfSlots;         // [kSfSlots]
+    uint64_t *sf_full = empty + kStages;               // [kSfBatches] scales in tensor memory
+    uint64_t *sf_empty = sf_full + kSfBatches;
+    uint64_t *sfs_full = sf_empty + kSfBatches;        // [kSfSlots] weight scales in shared memory
+    uint64_t *sfs_empty = sfs_full + kSfSlots;
     uint64_t *acc_full = sfs_empty + kSfSlots, *acc_empty = acc_full + 2;
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(acc_empty + 2);
+    uint64_t *item_full = acc_empty + 2, *item_empty = item_full + kItemSlots;
+    uint64_t *bg_full = item_empty + kItemSlots;       // the token's terms and scales have landed
+    uint64_t *bd_full = bg_full + 1, *bd_empty = bd_full + 2;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bd_empty + 2);
     volatile uint32_t *abort_flag = tmem_slot + 1;
+    volatile uint32_t *item_box = tmem_slot + 2;       // [kItemSlots]
+    uint32_t *ids_s = tmem_slot + 8;                   // [32]
+    float *weights_s = reinterpret_cast<float *>(tmem_slot + 40);   // [32]
     const uint32_t warp = threadIdx.x / kWarp, lane = threadIdx.x % kWarp;
-    const uint32_t steps = a.k / kKStage;
-    const uint32_t phases = kGateUp ? 2u : 1u;
-    const uint32_t tiles = a.w_rows / 128u;
-    const uint32_t items = a.ranks * tiles;
+    const uint32_t tiles_g = a.expert_hidden / 128u, tiles_d = a.hidden / 128u;
+    const uint32_t items_g = a.ranks * tiles_g, items = items_g + a.ranks * tiles_d;
 
     if (threadIdx.x == 0) {
         *abort_flag = 0u;
@@ -169,15 +220,19 @@ decode_mx_kernel(const __grid_constant__ MxMaps maps, MxArgs a) {
         for (uint32_t b = 0; b < 2; b++) {
             mbar_init(&acc_full[b], 2);
             mbar_init(&acc_empty[b], 4);
+            mbar_init(&bd_full[b], 1);
+            mbar_init(&bd_empty[b], 6);               // two issuers, four scale writers
         }
+        for (uint32_t b = 0; b < kItemSlots; b++) {
+            mbar_init(&item_full[b], 1);
+            mbar_init(&item_empty[b], kItemReaders);
+        }
+        mbar_init(bg_full, 1);
         fence_barrier_init();
     }
-    // rows 8..15 of every stage's N = 16 operand (its second swizzle atom) are never
-    // written by the TMA: zero them once
-    for (uint32_t i = threadIdx.x; i < kStages * (kBTile - kBTx) / 16u; i += blockDim.x) {
-        const uint32_t stage = i / ((kBTile - kBTx) / 16u), unit = i % ((kBTile - kBTx) / 16u);
-        reinterpret_cast<uint4 *>(base + stage * kStageBytes + kATile + kBTx)[unit] = make_uint4(0u, 0u, 0u, 0u);
-    }
+    // the atom of zeros that stands for rows 8..15 of every N = 16 operand
+    for (uint32_t i = threadIdx.x; i < kBAtom / 16u; i += blockDim.x)
+        reinterpret_cast<uint4 *>(base + lay.zero)[i] = make_uint4(0u, 0u, 0u, 0u);
     fence_proxy_async();
     if (warp == 1) {
         tmem_alloc(tmem_slot, kTmemCols);
@@ -188,75 +243,205 @@ decode_mx_kernel(const __grid_constant__ MxMaps maps, MxArgs a) {
     tc_fence_after();
     const uint32_t tmem = *tmem_slot;
 
-    if (warp == 0) {
-        // weight tile + term tile of every stage
+    // Everything above needed nothing from the front kernel; what follows does (scores,
+    // token terms, cleared control words).
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    if (a.route_words != nullptr) {
+        // every CTA routes the token itself (the ring is still free: it serves as scratch)
+        RouteScratch &rs = *reinterpret_cast<RouteScratch *>(base + lay.ring);
+        route_topk_block(rs, ids_s, weights_s, a.route_words, a.experts, a.ranks, a.route_scale);
+        // the same values from every CTA: whoever reads them later (the tail, the caller)
+        // is ordered behind at least one of these stores
+        if (threadIdx.x < a.ranks) {
+            a.ids[threadIdx.x] = ids_s[threadIdx.x];
+            a.weights[threadIdx.x] = weights_s[threadIdx.x];
+        }
+        __threadfence();
+    } else if (threadIdx.x < a.ranks) {
+        ids_s[threadIdx.x] = a.ids[threadIdx.x];
+    }
+    __syncthreads();
+
+    struct Item {
+        bool valid, down, local;
+        uint32_t rank, tile, expert;
+    };
+    auto decode = [&](uint32_t w) {
+        Item it;
+        it.valid = w != kNoItem;
+        it.down = it.valid && w >= items_g;
+        const uint32_t j = it.down ? w - items_g : w;
+        const uint32_t tiles = it.down ? tiles_d : tiles_g;
+        it.rank = it.valid ? j / tiles : 0u;
+        it.tile = it.valid ? j % tiles : 0u;
+        const uint32_t id = it.valid ? ids_s[it.rank] : 0u;
+        it.local = it.valid && id >= a.first_local && id < a.first_local + a.local_count;
+        it.expert = id - a.first_local;
+        return it;
+    };
+    // Reader side of the item mailbox: the n-th call returns the n-th item this CTA drew.
+    uint32_t item_seq = 0;
+    auto next_item = [&]() -> uint32_t {
+        const uint32_t slot = item_seq % kItemSlots, parity = (item_seq / kItemSlots) & 1u;
+        item_seq++;
+        uint32_t w = kNoItem;
         if (lane == 0) {
-            prefetch_tensormap(&maps.a0);
-            prefetch_tensormap(&maps.a1);
-            prefetch_tensormap(&maps.b);
-            uint32_t s = 0, ph = 0;
-            bool ok = true;
-            for (uint32_t it = blockIdx.x; ok && it < items; it += gridDim.x) {
-                const uint32_t rank = it / tiles, tile = it % tiles;
-                const uint32_t id = a.ids[rank];
-                if (id < a.first_local || id >= a.first_local + a.local_count) continue;
-                const int32_t y = (int32_t)((id - a.first_local) * a.w_rows + tile * 128u);
-                const int32_t yb = a.shared_vector ? 0 : (int32_t)(kTerms * rank);
+            if (mbar_wait(&item_full[slot], parity, abort_flag)) {
+                w = item_box[slot];
+                mbar_arrive(&item_empty[slot]);
+            }
+        }
+        return __shfl_sync(0xffffffffu, w, 0);
+    };
+
+    if (warp == 0) {
+        // ===================================== weight producer; draws the items
+        uint32_t s = 0, ph = 0, seq = 0;
+        bool ok = true;
+        uint32_t w = 0;
+        if (lane == 0) {
+            prefetch_tensormap(&maps.w1);
+            prefetch_tensormap(&maps.w3);
+            prefetch_tensormap(&maps.w2);
+            w = atomicAdd(a.control, 1u);
+        }
+        while (ok) {
+            const uint32_t slot = seq % kItemSlots, parity = (seq / kItemSlots) & 1u;
+            seq++;
+            uint32_t cur = kNoItem;
+            if (lane == 0) {
+                if (mbar_wait(&item_empty[slot], parity ^ 1u, abort_flag)) {
+                    cur = w < items ? w : kNoItem;
+                    item_box[slot] = cur;
+                    mbar_arrive(&item_full[slot]);
+                    if (cur != kNoItem) w = atomicAdd(a.control, 1u);   // travels while this item streams
+                }
+            }
+            cur = __shfl_sync(0xffffffffu, cur, 0);
+            if (cur == kNoItem) break;
+            const Item it = decode(cur);
+            if (!it.local) continue;
+            if (lane == 0) {
+                const uint32_t w_rows = it.down ? a.hidden : a.expert_hidden;
+                const int32_t y = (int32_t)(it.expert * w_rows + it.tile * 128u);
+                const uint32_t phases = it.down ? 1u : 2u, steps = it.down ? steps_d : steps_g;
                 for (uint32_t p = 0; ok && p < phases; p++) {
-                    const void *map_a = p == 0 ? (const void *)&maps.a0 : (const void *)&maps.a1;
+                    const void *map = it.down ? (const void *)&maps.w2
+                                              : (p == 0 ? (const void *)&maps.w1 : (const void *)&maps.w3);
                     for (uint32_t st = 0; st < steps; st++) {
                         if (!mbar_wait(&empty[s], ph ^ 1u, abort_flag)) { ok = false; break; }
-                        unsigned char *dst = base + s * kStageBytes;
-                        mbar_arrive_expect_tx(&full[s], kATile + kBTx);
-                        tma_load_2d(dst, map_a, &full[s], (int32_t)(st * 128u), y);            // x in bytes
-                        tma_load_2d(dst + kATile, &maps.b, &full[s], (int32_t)(st * 128u), yb);
+                        mbar_arrive_expect_tx(&full[s], kATile);
+                        tma_load_2d(base + lay.ring + s * kATile, map, &full[s], (int32_t)(st * 128u), y);
                         if (++s == kStages) { s = 0; ph ^= 1u; }
                     }
                 }
             }
+            ok = __shfl_sync(0xffffffffu, ok ? 1u : 0u, 0) != 0u;
+        }
+    } else if (warp == 12) {
+        // ===================================== term producer
+        bool ok = true;
+        if (lane == 0) {
+            prefetch_tensormap(&maps.x_terms);
+            prefetch_tensormap(&maps.x_sf);
+            prefetch_tensormap(&maps.a_terms);
+            prefetch_tensormap(&maps.a_sf);
+            // the token's terms serve every G item: all stages resident
+            mbar_arrive_expect_tx(bg_full, steps_g * kBAtom + (steps_g / 2u) * kSfbBatch);
+            for (uint32_t st = 0; st < steps_g; st++)
+                tma_load_2d(base + lay.bg + st * kBAtom, &maps.x_terms, bg_full, (int32_t)(st * 128u), 0);
+            for (uint32_t bt = 0; bt < steps_g / 2u; bt++)
+                tma_load_2d(base + lay.sfb_g + bt * kSfbBatch, &maps.x_sf, bg_full, (int32_t)(bt * 16u), 0);
+        }
+        uint32_t dcount = 0;
+        for (uint32_t w = next_item(); ok && w != kNoItem; w = next_item()) {
+            const Item it = decode(w);
+            if (!it.local || !it.down) continue;
+            const uint32_t buf = dcount & 1u, par = (dcount >> 1) & 1u;
+            dcount++;
+            if (lane == 0) {
+                // the rank's activation is complete when all its G epilogue warps have arrived
+                const uint32_t need = 4u * tiles_g;
+                const uint32_t *word = a.control + 16u + it.rank;
+                const unsigned long long t0 = global_timer_ns();
+                uint32_t spins = 0;
+                while (ld_acquire(word) < need) {
+                    if ((++spins & 63u) == 0u && (*abort_flag != 0u || global_timer_ns() - t0 > kWaitLimitNs)) {
+                        *abort_flag = 1u;
+                        ok = false;
+                        break;
+                    }
+                }
+                fence_proxy_async_global();      // what other SMs stored is now ordered before this TMA read
+                if (ok && !mbar_wait(&bd_empty[buf], par ^ 1u, abort_flag)) ok = false;
+                if (ok) {
+                    mbar_arrive_expect_tx(&bd_full[buf], steps_d * kBAtom + (steps_d / 2u) * kSfbBatch);
+                    const int32_t y = (int32_t)(kTerms * it.rank);
+                    for (uint32_t st = 0; st < steps_d; st++)
+                        tma_load_2d(base + lay.bd + (buf * steps_d + st) * kBAtom, &maps.a_terms, &bd_full[buf],
+                                    (int32_t)(st * 128u), y);
+                    for (uint32_t bt = 0; bt < steps_d / 2u; bt++)
+                        tma_load_2d(base + lay.sfb_d + (buf * (steps_d / 2u) + bt) * kSfbBatch, &maps.a_sf,
+                                    &bd_full[buf], (int32_t)(bt * 16u), y);
+                }
+            }
+            ok = __shfl_sync(0xffffffffu, ok ? 1u : 0u, 0) != 0u;
         }
     } else if (warp == 10) {
-        // block scales of two stages (512 K) at a time: 128 weight rows x 16 bytes and the
-        // 8 term rows x 16 bytes, into the shared-memory scale ring
+        // ===================================== weight-scale producer: 512 K per box
+        uint32_t s = 0, ph = 0;
+        bool ok = true;
         if (lane == 0) {
-            prefetch_tensormap(&maps.sfa0);
-            prefetch_tensormap(&maps.sfa1);
-            prefetch_tensormap(&maps.sfb);
-            uint32_t s = 0, ph = 0;
-            bool ok = true;
-            for (uint32_t it = blockIdx.x; ok && it < items; it += gridDim.x) {
-                const uint32_t rank = it / tiles, tile = it % tiles;
-                const uint32_t id = a.ids[rank];
-                if (id < a.first_local || id >= a.first_local + a.local_count) continue;
-                const int32_t y = (int32_t)((id - a.first_local) * a.w_rows + tile * 128u);
-                const int32_t yb = a.shared_vector ? 0 : (int32_t)(kTerms * rank);
+            prefetch_tensormap(&maps.s1);
+            prefetch_tensormap(&maps.s3);
+            prefetch_tensormap(&maps.s2);
+        }
+        for (uint32_t w = next_item(); ok && w != kNoItem; w = next_item()) {
+            const Item it = decode(w);
+            if (!it.local) continue;
+            if (lane == 0) {
+                const uint32_t w_rows = it.down ? a.hidden : a.expert_hidden;
+                const int32_t y = (int32_t)(it.expert * w_rows + it.tile * 128u);
+                const uint32_t phases = it.down ? 1u : 2u, steps = it.down ? steps_d : steps_g;
                 for (uint32_t p = 0; ok && p < phases; p++) {
-                    const void *map_s = p == 0 ? (const void *)&maps.sfa0 : (const void *)&maps.sfa1;
-                    for (uint32_t st = 0; st < steps; st += 2u) {
+                    const void *map = it.down ? (const void *)&maps.s2
+                                              : (p == 0 ? (const void *)&maps.s1 : (const void *)&maps.s3);
+                    for (uint32_t bt = 0; bt < steps / 2u; bt++) {
                         if (!mbar_wait(&sfs_empty[s], ph ^ 1u, abort_flag)) { ok = false; break; }
-                        unsigned char *dst = sf_smem + s * kSfSlotBytes;
-                        mbar_arrive_expect_tx(&sfs_full[s], kSfaBytes + kTerms * 16u);
-                        tma_load_2d(dst, map_s, &sfs_full[s], (int32_t)(st * 8u), y);
-                        tma_load_2d(dst + kSfaBytes, &maps.sfb, &sfs_full[s], (int32_t)(st * 8u), yb);
+                        mbar_arrive_expect_tx(&sfs_full[s], kSfaBytes);
+                        tma_load_2d(base + lay.sfa + s * kSfaBytes, map, &sfs_full[s], (int32_t)(bt * 16u), y);
                         if (++s == kSfSlots) { s = 0; ph ^= 1u; }
                     }
                 }
             }
+            ok = __shfl_sync(0xffffffffu, ok ? 1u : 0u, 0) != 0u;
         }
     } else if (warp == 1 || warp == 11) {
-        // Two MMA issuers: the issue loop of one thread, not the tensor pipe, bounds
-        // the rate of these small MMAs, so warp 1 takes the even stages and warp 11
-        // the odd ones, each into its own accumulator columns (summed in the epilogue).
-        // A scale batch covers two stages, one per issuer.
-        if (lane == 0) {
-            const uint32_t q = warp == 1 ? 0u : 1u;
-            uint32_t s = q, ph = 0, buf = 0, pacc = 0, sb = 0, sph = 0;
-            bool ok = true;
-            for (uint32_t it = blockIdx.x; ok && it < items; it += gridDim.x) {
-                const uint32_t rank = it / tiles;
-                const uint32_t id = a.ids[rank];
-                if (id < a.first_local || id >= a.first_local + a.local_count) continue;
-                if (!mbar_wait(&acc_empty[buf], pacc ^ 1u, abort_flag)) break;
+        // ===================================== MMA issuers
+        // The issue loop of one thread, not the tensor pipe, bounds the rate of these small
+        // MMAs, so warp 1 takes the even stages and warp 11 the odd ones, each into its own
+        // accumulator columns (summed in the epilogue).  A scale batch covers two stages,
+        // one per issuer.
+        const uint32_t q = warp == 1 ? 0u : 1u;
+        uint32_t s = q, ph = 0, buf = 0, pacc = 0, sb = 0, sph = 0, dcount = 0;
+        bool ok = true;
+        for (uint32_t w = next_item(); ok && w != kNoItem; w = next_item()) {
+            const Item it = decode(w);
+            if (!it.local) continue;
+            uint32_t dbuf = 0;
+            if (it.down) {
+                dbuf = dcount & 1u;
+                dcount++;
+            }
+            if (lane == 0) {
+                const uint32_t dpar = ((dcount - 1u) >> 1) & 1u;
+                const uint32_t phases = it.down ? 1u : 2u, steps = it.down ? steps_d : steps_g;
+                const uint32_t b_base = smem_u32(base + (it.down ? lay.bd + dbuf * steps_d * kBAtom : lay.bg));
+                const uint32_t zero_atom = smem_u32(base + lay.zero);
+                if (!mbar_wait(&acc_empty[buf], pacc ^ 1u, abort_flag) ||
+                    !(it.down ? mbar_wait(&bd_full[dbuf], dpar, abort_flag) : mbar_wait(bg_full, 0u, abort_flag))) {
+                    ok = false;
+                }
                 tc_fence_after();
                 for (uint32_t p = 0; ok && p < phases; p++) {
                     const uint32_t d = tmem + kAccCol + buf * 64u + q * 32u + p * 16u;
@@ -266,9 +451,8 @@ decode_mx_kernel(const __grid_constant__ MxMaps maps, MxArgs a) {
                             break;
                         }
                         tc_fence_after();
-                        unsigned char *src = base + s * kStageBytes;
-                        const uint64_t da = make_desc_sw128(smem_u32(src));
-                        const uint64_t db = make_desc_sw128(smem_u32(src + kATile));
+                        const uint64_t da = make_desc_sw128(smem_u32(base + lay.ring + s * kATile));
+                        const uint64_t db = make_desc_sw128_split(b_base + st * kBAtom, zero_atom);
 #pragma unroll
                         for (uint32_t j = 0; j < 4u; j++) {
                             // stage q of the batch holds the 128-K chunks 2q and 2q + 1 (4 columns
@@ -284,69 +468,89 @@ decode_mx_kernel(const __grid_constant__ MxMaps maps, MxArgs a) {
                         if (++sb == kSfBatches) { sb = 0; sph ^= 1u; }
                     }
                 }
-                if (!ok) break;
-                mma_commit(&acc_full[buf]);
-                if (++buf == 2u) { buf = 0; pacc ^= 1u; }
+                if (ok) {
+                    mma_commit(&acc_full[buf]);
+                    if (it.down) mma_commit(&bd_empty[dbuf]);      // the MMAs have read the activation terms
+                }
             }
+            if (++buf == 2u) { buf = 0; pacc ^= 1u; }
+            ok = __shfl_sync(0xffffffffu, ok ? 1u : 0u, 0) != 0u;
         }
     } else if (warp < 6) {
-        // scale writers: shared memory -> tensor memory, warp w fills lane quadrant w % 4
+        // ===================================== scale writers: shared memory -> tensor memory,
+        // warp w fills lane quadrant w % 4
         const uint32_t quad = warp & 3u;
         const uint32_t lane_base = (32u * quad) << 16;
-        uint32_t sb = 0, sph = 0, ss = 0, ssph = 0;
+        uint32_t sb = 0, sph = 0, ss = 0, ssph = 0, dcount = 0;
         bool ok = true;
-        for (uint32_t it = blockIdx.x; ok && it < items; it += gridDim.x) {
-            const uint32_t id = a.ids[it / tiles];
-            if (id < a.first_local || id >= a.first_local + a.local_count) continue;
-            for (uint32_t st = 0; st < phases * steps; st += 2u) {
-                if (!mbar_wait(&sfs_full[ss], ssph, abort_flag)) { ok = false; break; }
-                const unsigned char *src = sf_smem + ss * kSfSlotBytes;
-                uint4 cur[4];
+        for (uint32_t w = next_item(); ok && w != kNoItem; w = next_item()) {
+            const Item it = decode(w);
+            if (!it.local) continue;
+            uint32_t dbuf = 0, dpar = 0;
+            if (it.down) {
+                dbuf = dcount & 1u;
+                dpar = (dcount >> 1) & 1u;
+                dcount++;
+            }
+            if (!(it.down ? mbar_wait(&bd_full[dbuf], dpar, abort_flag) : mbar_wait(bg_full, 0u, abort_flag))) break;
+            const uint32_t phases = it.down ? 1u : 2u, steps = it.down ? steps_d : steps_g;
+            const unsigned char *sfb =
+                base + (it.down ? lay.sfb_d + dbuf * (steps_d / 2u) * kSfbBatch : lay.sfb_g);
+            for (uint32_t p = 0; ok && p < phases; p++) {
+                for (uint32_t bt = 0; bt < steps / 2u; bt++) {
+                    if (!mbar_wait(&sfs_full[ss], ssph, abort_flag)) { ok = false; break; }
+                    const unsigned char *src = base + lay.sfa + ss * kSfaBytes;
+                    uint4 cur[4];
 #pragma unroll
-                for (uint32_t c = 0; c < 4u; c++)
-                    cur[c] = *reinterpret_cast<const uint4 *>(src + (32u * c + lane) * 16u);
-                // scale rows of the N operand sit in lanes 0..15 of the first column of a group:
-                // term rows 0..7 (lanes 8.. repeat them: those operand rows are zero)
-                const uint4 curb = *reinterpret_cast<const uint4 *>(src + kSfaBytes + (lane & (kTerms - 1u)) * 16u);
-                if (!mbar_wait(&sf_empty[sb], sph ^ 1u, abort_flag)) { ok = false; break; }
-                tc_fence_after();
-                // column (128-K chunk q, row group c) = q * 4 + c of the batch's 16 columns
-                const uint32_t va[16] = {cur[0].x, cur[1].x, cur[2].x, cur[3].x, cur[0].y, cur[1].y,
-                                         cur[2].y, cur[3].y, cur[0].z, cur[1].z, cur[2].z, cur[3].z,
-                                         cur[0].w, cur[1].w, cur[2].w, cur[3].w};
-                const uint32_t vbb[16] = {curb.x, curb.x, curb.x, curb.x, curb.y, curb.y, curb.y, curb.y,
-                                          curb.z, curb.z, curb.z, curb.z, curb.w, curb.w, curb.w, curb.w};
-                tmem_st_32x16(tmem + lane_base + kSfaCol + sb * 16u, va);
-                tmem_st_32x16(tmem + lane_base + kSfbCol + sb * 16u, vbb);
-                // The shared-memory slot goes back to the TMA producer only now: the
-                // stores above consumed every loaded register, so the loads have
-                // completed (an arrive right after issuing them would not wait for that).
+                    for (uint32_t c = 0; c < 4u; c++)
+                        cur[c] = *reinterpret_cast<const uint4 *>(src + (32u * c + lane) * 16u);
+                    // scale rows of the N operand sit in lanes 0..15 of the first column of a group:
+                    // term rows 0..7 (lanes 8.. repeat them: those operand rows are zero)
+                    const uint4 curb =
+                        *reinterpret_cast<const uint4 *>(sfb + bt * kSfbBatch + (lane & (kTerms - 1u)) * 16u);
+                    if (!mbar_wait(&sf_empty[sb], sph ^ 1u, abort_flag)) { ok = false; break; }
+                    tc_fence_after();
+                    // column (128-K chunk q, row group c) = q * 4 + c of the batch's 16 columns
+                    const uint32_t va[16] = {cur[0].x, cur[1].x, cur[2].x, cur[3].x, cur[0].y, cur[1].y,
+                                             cur[2].y, cur[3].y, cur[0].z, cur[1].z, cur[2].z, cur[3].z,
+                                             cur[0].w, cur[1].w, cur[2].w, cur[3].w};
+                    const uint32_t vbb[16] = {curb.x, curb.x, curb.x, curb.x, curb.y, curb.y, curb.y, curb.y,
+                                              curb.z, curb.z, curb.z, curb.z, curb.w, curb.w, curb.w, curb.w};
+                    tmem_st_32x16(tmem + lane_base + kSfaCol + sb * 16u, va);
+                    tmem_st_32x16(tmem + lane_base + kSfbCol + sb * 16u, vbb);
+                    // The shared-memory slot goes back to the TMA producer only now: the
+                    // stores above consumed every loaded register, so the loads have
+                    // completed (an arrive right after issuing them would not wait for that).
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&sfs_empty[ss]);
+                    if (++ss == kSfSlots) { ss = 0; ssph ^= 1u; }
+                    tmem_st_wait();
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&sf_full[sb]);
+                    if (++sb == kSfBatches) { sb = 0; sph ^= 1u; }
+                }
+            }
+            if (ok && it.down) {
                 __syncwarp();
-                if (lane == 0) mbar_arrive(&sfs_empty[ss]);
-                if (++ss == kSfSlots) { ss = 0; ssph ^= 1u; }
-                tmem_st_wait();
-                tc_fence_before();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(&sf_full[sb]);
-                if (++sb == kSfBatches) { sb = 0; sph ^= 1u; }
+                if (lane == 0) mbar_arrive(&bd_empty[dbuf]);       // this warp has read the item's term scales
             }
         }
     } else if (warp < 10) {
-        // epilogue: warp w reads lane quadrant w % 4
+        // ===================================== epilogue: warp w reads lane quadrant w % 4
         const uint32_t quad = warp & 3u;
         const uint32_t m = 32u * quad + lane;
         uint32_t buf = 0, pacc = 0;
-        for (uint32_t it = blockIdx.x; it < items; it += gridDim.x) {
-            const uint32_t rank = it / tiles, tile = it % tiles;
-            const uint32_t id = a.ids[rank];
-            if (id < a.first_local || id >= a.first_local + a.local_count) continue;
+        for (uint32_t w = next_item(); w != kNoItem; w = next_item()) {
+            const Item it = decode(w);
+            if (!it.local) continue;
             if (!mbar_wait(&acc_full[buf], pacc, abort_flag)) break;
             tc_fence_after();
             const uint32_t t0 = tmem + ((32u * quad) << 16) + kAccCol + buf * 64u;
             uint32_t e0[8], o0[8], e1[8], o1[8];
             tmem_ld_32x8(t0, e0);                           // even stages
             tmem_ld_32x8(t0 + 32u, o0);                     // odd stages
-            if (kGateUp) {
+            if (!it.down) {
                 tmem_ld_32x8(t0 + 16u, e1);
                 tmem_ld_32x8(t0 + 48u, o1);
             }
@@ -356,23 +560,26 @@ decode_mx_kernel(const __grid_constant__ MxMaps maps, MxArgs a) {
             if (lane == 0) mbar_arrive(&acc_empty[buf]);
             if (++buf == 2u) { buf = 0; pacc ^= 1u; }
             const float v0 = sum_terms(e0) + sum_terms(o0);
-            uint16_t *dst = a.out + (uint64_t)rank * a.w_rows + tile * 128u + m;
-            if (kGateUp) {
+            if (!it.down) {
                 const float v1 = sum_terms(e1) + sum_terms(o1);
                 const float g = bf16_bits_to_float(float_to_bf16_bits(v0));
                 const float u = bf16_bits_to_float(float_to_bf16_bits(v1));
                 const uint16_t act_bits = float_to_bf16_bits(activation(g, u, a.activation, a.beta, a.linear_beta));
-                *dst = act_bits;
-                if (a.act_terms != nullptr) {
-                    uint32_t code[kTerms], sbyte[kTerms];
-                    split_block_e2m1(bf16_bits_to_float(act_bits), code, sbyte);
-                    store_block_e2m1(a.act_terms + (uint64_t)rank * kTerms * (a.w_rows / 2u),
-                                     a.act_sf + (uint64_t)rank * kTerms * (a.w_rows / 32u), a.w_rows / 2u,
-                                     a.w_rows / 32u, tile * 4u + quad, code, sbyte, lane);
-                }
+                const uint32_t I = a.expert_hidden;
+                a.act[(uint64_t)it.rank * I + it.tile * 128u + m] = act_bits;
+                uint32_t code[kTerms], sbyte[kTerms];
+                split_block_e2m1(bf16_bits_to_float(act_bits), code, sbyte);
+                store_block_e2m1(a.act_terms + (uint64_t)it.rank * kTerms * (I / 2u),
+                                 a.act_sf + (uint64_t)it.rank * kTerms * (I / 32u), I / 2u, I / 32u,
+                                 it.tile * 4u + quad, code, sbyte, lane);
+                // publish: these 32 activation elements are in memory for every SM's TMA reads
+                fence_proxy_async_global();
+                __threadfence();
+                __syncwarp();
+                if (lane == 0) atomicAdd(a.control + 16u + it.rank, 1u);
             } else {
-                *dst = float_to_bf16_bits(v0);
-                if (a.tail.out != nullptr && !tail_arrive(a.tail, tile * 4u + quad, lane)) *abort_flag = 1u;
+                a.rows_out[(uint64_t)it.rank * a.hidden + it.tile * 128u + m] = float_to_bf16_bits(v0);
+                if (a.tail.out != nullptr && !tail_arrive(a.tail, it.tile * 4u + quad, lane)) *abort_flag = 1u;
             }
         }
     }
@@ -450,7 +657,7 @@ size_t k3_decode_mx_scratch_bytes(const k3_moe_layer_desc *d) {
     // scores and choices of the routing step
     return (size_t)kTerms * d->hidden / 2u + (size_t)kTerms * d->hidden / 32u +
            (size_t)kTerms * d->top_k * d->expert_hidden / 2u + (size_t)kTerms * d->top_k * d->expert_hidden / 32u +
-           (size_t)d->hidden / 32u * 4u + 2u * 1024u * 4u + 6u * 256u;
+           (size_t)d->hidden / 32u * 4u + 2u * 1024u * 4u + 2u * kControlWords * 4u + 7u * 256u;
 }
 
 bool k3_decode_mx_supported(const k3_moe_layer_desc *d) {
@@ -481,23 +688,28 @@ void *k3_decode_mx_route_words(const k3_moe_layer_desc *d, void *scratch) {
     return (void *)(((uintptr_t)(tail + (size_t)d->hidden / 32u * 4u) + 255u) & ~(uintptr_t)255u);
 }
 
+void *k3_decode_mx_control_words(const k3_moe_layer_desc *d, void *scratch) {
+    uint8_t *route = (uint8_t *)k3_decode_mx_route_words(d, scratch);
+    return (void *)(((uintptr_t)(route + 2u * 1024u * 4u) + 255u) & ~(uintptr_t)255u);
+}
+
 // Routed experts of one token: act [top_k, I] and rows_out [top_k, hidden] in rank
 // order (ids on the device) from the token's E2M1 terms in `scratch`.
-bool k3_decode_mx_experts(const k3_moe_layer_desc *d, const void *ids, void *act, void *rows_out,
-                          void *scratch, void *between, const k3_decode_tail *tail, cudaStream_t stream) {
+bool k3_decode_mx_experts(const k3_moe_layer_desc *d, void *ids, void *weights, const void *route_words,
+                          void *act, void *rows_out, void *scratch, void *between, const k3_decode_tail *tail,
+                          cudaStream_t stream) {
+    if (route_words != nullptr && (d->expert_count > 1024u || !weights)) return false;
     const uint32_t H = d->hidden, I = d->expert_hidden, k = d->top_k;
     auto align = [](uint8_t *p) { return (uint8_t *)(((uintptr_t)p + 255u) & ~(uintptr_t)255u); };
     uint8_t *x_terms = nullptr, *x_sf = nullptr;
     k3_decode_mx_vector_scratch(d, scratch, (void **)&x_terms, (void **)&x_sf);
     uint8_t *a_terms = align(x_sf + (size_t)kTerms * H / 32u);
     uint8_t *a_sf = align(a_terms + (size_t)kTerms * k * I / 2u);
-    const size_t smem = kSmemBytes;
-    if (!set_max_dynamic_smem((const void *)decode_mx_kernel<true>, smem) ||
-        !set_max_dynamic_smem((const void *)decode_mx_kernel<false>, smem)) {
-        return false;
-    }
+    const MxSmem lay = mx_smem_layout(H / kKStage, I / kKStage);
+    if (lay.total > 227u * 1024u) return false;
+    if (!set_max_dynamic_smem((const void *)decode_experts_kernel, lay.total)) return false;
     // Tensor maps depend only on the tables, the scratch block and the shape.  Encoding
-    // ten maps costs more host time than the launches, so the sets of the most recent
+    // ten maps costs more host time than the launch, so the sets of the most recent
     // layers are kept (a model alternates between its layers' descriptors token by
     // token); when the table is full it starts over.
     struct MapKey {
@@ -510,62 +722,55 @@ bool k3_decode_mx_experts(const k3_moe_layer_desc *d, const void *ids, void *act
             return c != 0 ? c < 0 : memcmp(dims, o.dims, sizeof(dims)) < 0;
         }
     };
-    struct MapSet {
-        MxMaps gu, dn;
-    };
     constexpr size_t kCachedLayers = 256;
     static std::mutex map_lock;
-    static std::map<MapKey, MapSet> cached;
+    static std::map<MapKey, MxMaps> cached;
     MapKey key{};
     key.device = current_device();
     const void *ptrs[7] = {d->w1_packed, d->w3_packed, d->w2_packed, d->w1_scales, d->w3_scales, d->w2_scales, scratch};
     memcpy(key.p, ptrs, sizeof(ptrs));
     key.dims[0] = H; key.dims[1] = I; key.dims[2] = k; key.dims[3] = d->local_expert_count;
-    MxMaps gu, dn;
+    MxMaps maps;
     {
         std::lock_guard<std::mutex> guard(map_lock);
         auto it = cached.find(key);
         if (it == cached.end()) {
             const uint64_t total = (uint64_t)d->local_expert_count;
-            if (!map_bytes(&gu.a0, d->w1_packed, total * I, H / 2u, 128) ||
-                !map_bytes(&gu.a1, d->w3_packed, total * I, H / 2u, 128) ||
-                !map_bytes(&gu.b, x_terms, kTerms, H / 2u, kTerms) || !map_sf(&gu.sfa0, d->w1_scales, total * I, H, 128) ||
-                !map_sf(&gu.sfa1, d->w3_scales, total * I, H, 128) || !map_sf(&gu.sfb, x_sf, kTerms, H, kTerms) ||
-                !map_bytes(&dn.a0, d->w2_packed, total * H, I / 2u, 128) ||
-                !map_bytes(&dn.b, a_terms, (uint64_t)kTerms * k, I / 2u, kTerms) ||
-                !map_sf(&dn.sfa0, d->w2_scales, total * H, I, 128) ||
-                !map_sf(&dn.sfb, a_sf, (uint64_t)kTerms * k, I, kTerms)) {
+            if (!map_bytes(&maps.w1, d->w1_packed, total * I, H / 2u, 128) ||
+                !map_bytes(&maps.w3, d->w3_packed, total * I, H / 2u, 128) ||
+                !map_bytes(&maps.w2, d->w2_packed, total * H, I / 2u, 128) ||
+                !map_sf(&maps.s1, d->w1_scales, total * I, H, 128) || !map_sf(&maps.s3, d->w3_scales, total * I, H, 128) ||
+                !map_sf(&maps.s2, d->w2_scales, total * H, I, 128) ||
+                !map_bytes(&maps.x_terms, x_terms, kTerms, H / 2u, kTerms) || !map_sf(&maps.x_sf, x_sf, kTerms, H, kTerms) ||
+                !map_bytes(&maps.a_terms, a_terms, (uint64_t)kTerms * k, I / 2u, kTerms) ||
+                !map_sf(&maps.a_sf, a_sf, (uint64_t)kTerms * k, I, kTerms)) {
                 return false;
             }
-            dn.a1 = dn.a0;
-            dn.sfa1 = dn.sfa0;
             if (cached.size() >= kCachedLayers) cached.clear();
-            cached.emplace(key, MapSet{gu, dn});
+            cached.emplace(key, maps);
         } else {
-            gu = it->second.gu;
-            dn = it->second.dn;
+            maps = it->second;
         }
     }
     MxArgs a{};
-    a.ids = (const uint32_t *)ids;
+    a.ids = (uint32_t *)ids;
+    a.weights = (float *)weights;
+    a.route_words = (const float *)route_words;
+    a.experts = d->expert_count;
+    a.route_scale = d->route_scale;
+    a.act = (uint16_t *)act;
+    a.rows_out = (uint16_t *)rows_out;
     a.ranks = k;
     a.first_local = d->local_expert_first;
     a.local_count = d->local_expert_count;
+    a.hidden = H;
+    a.expert_hidden = I;
     a.activation = d->activation;
     a.beta = d->beta;
     a.linear_beta = d->linear_beta;
-    const int sms = sm_count();
-    // gate/up + activation
-    a.out = (uint16_t *)act;
     a.act_terms = a_terms;
     a.act_sf = a_sf;
-    a.w_rows = I;
-    a.k = H;
-    a.shared_vector = 1u;
-    decode_mx_kernel<true><<<sms, kThreads, smem, stream>>>(gu, a);
-    if (!launch_ok()) return false;
-    if (between && cudaEventRecord((cudaEvent_t)between, stream) != cudaSuccess) return false;
-    // down (+ its share of the layer's tail)
+    a.control = (uint32_t *)k3_decode_mx_control_words(d, scratch);
     if (tail != nullptr) {
         if (d->local_expert_first != 0u || d->local_expert_count != d->expert_count) return false;
         a.tail.out = (uint16_t *)tail->out;
@@ -579,12 +784,21 @@ bool k3_decode_mx_experts(const k3_moe_layer_desc *d, const void *ids, void *act
         a.tail.ranks = k;
         a.tail.hidden = H;
     }
-    a.out = (uint16_t *)rows_out;
-    a.act_terms = nullptr;
-    a.act_sf = nullptr;
-    a.w_rows = H;
-    a.k = I;
-    a.shared_vector = 0u;
-    decode_mx_kernel<false><<<sms, kThreads, smem, stream>>>(dn, a);
-    return launch_ok();
+    cudaLaunchConfig_t config{};
+    config.gridDim = dim3((unsigned)sm_count());
+    config.blockDim = dim3(kThreads);
+    config.dynamicSmemBytes = lay.total;
+    config.stream = stream;
+    cudaLaunchAttribute attribute{};
+    attribute.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attribute.val.programmaticStreamSerializationAllowed = 1;
+    config.attrs = &attribute;
+    // behind the front kernel: blocks may take their places (and set up barriers and tensor
+    // memory) while the front grid drains; they wait for it before they read its results
+    config.numAttrs = route_words != nullptr ? 1u : 0u;
+    if (cudaLaunchKernelEx(&config, decode_experts_kernel, maps, a) != cudaSuccess) {
+        (void)cudaGetLastError();
+        return false;
+    }
+    return !between || cudaEventRecord((cudaEvent_t)between, stream) == cudaSuccess;
 }

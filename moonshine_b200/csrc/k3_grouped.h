@@ -60,7 +60,7 @@ size_t k3_decode_mx_scratch_bytes(const k3_moe_layer_desc *desc);
 // nibbles (one row per term) and x_sf [8, hidden / 32] block scales
 void k3_decode_mx_vector_scratch(const k3_moe_layer_desc *desc, void *scratch, void **x_terms, void **x_sf);
 // Expert products of one token from its E2M1 terms already in `scratch`;
-// `between` (a CUDA event or null) is recorded between gate/up and down.
+// `between` (a CUDA event or null) is recorded after the one expert launch.
 // With `tail` the down kernel's epilogue takes part in the layer's tail
 // (k3_decode_tail.cuh): it counts an arrival per finished row and 32-column group in
 // the words k3_decode_mx_tail_words() returns, and the arrival that completes
@@ -76,8 +76,16 @@ struct k3_decode_tail {
 void *k3_decode_mx_tail_words(const k3_moe_layer_desc *desc, void *scratch);
 // f32 [2][1024] inside `scratch`: sigmoid scores and score + bias per expert (front kernel)
 void *k3_decode_mx_route_words(const k3_moe_layer_desc *desc, void *scratch);
-bool k3_decode_mx_experts(const k3_moe_layer_desc *desc, const void *ids, void *act, void *rows_out,
-                          void *scratch, void *between, const k3_decode_tail *tail, cudaStream_t stream);
+// 64 words inside `scratch` that must be zero when the expert kernel starts (its item
+// counter and the per-rank arrival counts); the front kernel clears them
+void *k3_decode_mx_control_words(const k3_moe_layer_desc *desc, void *scratch);
+// With route_words (the scores and choices the front kernel's row tasks wrote) the kernel
+// routes the token itself in its prologue and writes ids / weights [top_k]; it is then
+// launched with programmatic stream serialization behind the front kernel.  With
+// route_words null it reads ids (weights untouched).
+bool k3_decode_mx_experts(const k3_moe_layer_desc *desc, void *ids, void *weights, const void *route_words,
+                          void *act, void *rows_out, void *scratch, void *between, const k3_decode_tail *tail,
+                          cudaStream_t stream);
 uint32_t k3_decode_mx_status();
 uint32_t k3_decode_status();
 uint32_t k3_dispatch_status();

@@ -14,8 +14,13 @@
 //
 // Work item = two 128-row weight tiles x up to 128 token rows of one group over
 // the whole K extent (gate+up with fused activation, or 256 rows of the down
-// projection).  One CTA per SM, persistent, item list derived in-kernel from the
-// group offsets.  Warps: 0 TMA producer (weights), 2 TMA producer (token terms),
+// projection).  One CTA per SM, persistent; the item list is derived in-kernel from the
+// group offsets and handed out by a global counter: the weight producer takes the next
+// item with one atomicAdd and publishes it to the other roles through a mailbox in
+// shared memory, so a CTA that drew short row tiles simply takes more of them.  Items
+// are numbered with the row tiles of one (expert, weight tile) adjacent: CTAs that take
+// neighbouring items stream the same weights at the same time and the second reader
+// finds them in L2.  Warps: 0 TMA producer (weights), 2 TMA producer (token terms),
 // 3 TMA producer (block scales), 1 and 16 MMA issuers (one per weight tile), 4-7
 // scale writers (shared memory -> tensor memory, one lane quadrant each), 8-15
 // epilogue.  All barrier waits are bounded.
@@ -54,6 +59,9 @@ constexpr uint32_t kSfa0Col = 256;                        // kSfBatches x 16 col
 constexpr uint32_t kSfa1Col = kSfa0Col + 16u * kSfBatches;
 constexpr uint32_t kSfbCol = kSfa1Col + 16u * kSfBatches;
 constexpr uint32_t kMaxGroups = 1024;
+constexpr uint32_t kItemSlots = 4;                        // mailbox of item numbers, producer -> other roles
+constexpr uint32_t kItemReaders = 16;                     // term + scale producers, 2 issuers, 4 writers, 8 epilogue warps
+constexpr uint32_t kNoItem = 0xffffffffu;
 constexpr uint32_t kBarBytes = 512;
 constexpr uint32_t kSmemBytes =
     kStages * kStageBytes + kSfSlots * kSfSlotBytes + 1024u + kBarBytes + (kMaxGroups + 1u) * 4u;
@@ -117,6 +125,7 @@ struct GmxArgs {
     uint16_t *out;                       // bf16 [rows, out_width] (may be null in gate/up mode)
     uint8_t *act_hi, *act_lo, *act_sf;   // gate/up mode: E4M3 terms and block scales of the activation
     uint32_t groups, rows, w_rows, k, out_width, m_items;
+    uint32_t *item_counter;              // zero before the launch; items are drawn from it
     int activation;
     float beta, linear_beta;
 };
@@ -125,18 +134,23 @@ struct Item {
     uint32_t group, row_start, rows_valid, m_item;
 };
 
+// Item w -> (group, weight tile, row tile).  prefix[g] = row tiles of the groups before
+// g; group g owns items [prefix[g] * m_items, prefix[g + 1] * m_items), numbered with
+// the row tile fastest.
 K3_DEVINL Item decode_item(uint32_t w, const uint32_t *prefix, const GmxArgs &a) {
     Item it;
-    const uint32_t nt = w / a.m_items;
-    it.m_item = w % a.m_items;
+    const uint32_t nt = w / a.m_items;             // prefix[group] <= nt < prefix[group + 1]
     uint32_t lo = 0, hi = a.groups;
     while (hi - lo > 1u) {
         const uint32_t mid = (lo + hi) >> 1;
         if (prefix[mid] <= nt) lo = mid; else hi = mid;
     }
     it.group = lo;
+    const uint32_t tiles = prefix[lo + 1u] - prefix[lo];
+    const uint32_t j = w - prefix[lo] * a.m_items;
+    it.m_item = j / tiles;
     const uint32_t begin = a.offsets[lo], end = a.offsets[lo + 1u];
-    it.row_start = begin + (nt - prefix[lo]) * BN;
+    it.row_start = begin + (j % tiles) * BN;
     it.rows_valid = min(BN, end - it.row_start);
     return it;
 }
@@ -159,9 +173,11 @@ grouped_mx_kernel(const __grid_constant__ GmxMaps maps, GmxArgs a) {
     uint64_t *sf_full = empty + kStages, *sf_empty = sf_full + kSfBatches;
     uint64_t *sfs_full = sf_empty + kSfBatches, *sfs_empty = sfs_full + kSfSlots;
     uint64_t *acc_full = sfs_empty + kSfSlots, *acc_empty = acc_full + 1;
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(acc_empty + 1);
+    uint64_t *item_full = acc_empty + 1, *item_empty = item_full + kItemSlots;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(item_empty + kItemSlots);
     volatile uint32_t *abort_flag = tmem_slot + 1;
     uint32_t *total_items_s = tmem_slot + 2;
+    volatile uint32_t *item_box = tmem_slot + 3;          // [kItemSlots]
     uint32_t *prefix = reinterpret_cast<uint32_t *>(reinterpret_cast<unsigned char *>(bars) + kBarBytes);
     const uint32_t warp = threadIdx.x / kWarp, lane = threadIdx.x % kWarp;
     const uint32_t steps = a.k / KS;
@@ -183,6 +199,10 @@ grouped_mx_kernel(const __grid_constant__ GmxMaps maps, GmxArgs a) {
         }
         mbar_init(acc_full, 2);
         mbar_init(acc_empty, 8);
+        for (uint32_t b = 0; b < kItemSlots; b++) {
+            mbar_init(&item_full[b], 1);
+            mbar_init(&item_empty[b], kItemReaders);
+        }
         fence_barrier_init();
     }
     {   // exclusive prefix of ceil(rows_g / BN) over the groups (<= 1024)
@@ -226,36 +246,74 @@ grouped_mx_kernel(const __grid_constant__ GmxMaps maps, GmxArgs a) {
     const uint32_t tmem = *tmem_slot;
     const uint32_t total_items = *total_items_s;
 
-    if (warp == 0 || warp == 2) {
-        // ================================ TMA producers: weights / token terms
+    // Reader side of the item mailbox (whole warp, or one thread with lane_count 1):
+    // the n-th call returns the n-th item this CTA drew, kNoItem when there are no more.
+    uint32_t item_seq = 0;
+    auto next_item = [&]() -> uint32_t {
+        const uint32_t slot = item_seq % kItemSlots, parity = (item_seq / kItemSlots) & 1u;
+        item_seq++;
+        uint32_t w = kNoItem;
         if (lane == 0) {
-            const bool weights = warp == 0;
-            prefetch_tensormap(weights ? (const void *)&maps.a0 : (const void *)&maps.bhi);
-            prefetch_tensormap(weights ? (const void *)&maps.a1 : (const void *)&maps.blo);
-            uint32_t s = 0, ph = 0;
+            if (mbar_wait(&item_full[slot], parity, abort_flag)) {
+                w = item_box[slot];
+                mbar_arrive(&item_empty[slot]);
+            }
+        }
+        return w;
+    };
+
+    if (warp == 0) {
+        // ================================ TMA producer: weights; draws the items
+        if (lane == 0) {
+            prefetch_tensormap(&maps.a0);
+            prefetch_tensormap(&maps.a1);
+            uint32_t s = 0, ph = 0, seq = 0;
             bool ok = true;
-            for (uint32_t w = blockIdx.x; ok && w < total_items; w += gridDim.x) {
+            uint32_t w = atomicAdd(a.item_counter, 1u);
+            while (ok) {
+                const uint32_t slot = seq % kItemSlots, parity = (seq / kItemSlots) & 1u;
+                seq++;
+                if (!mbar_wait(&item_empty[slot], parity ^ 1u, abort_flag)) break;
+                const bool valid = w < total_items;
+                item_box[slot] = valid ? w : kNoItem;
+                mbar_arrive(&item_full[slot]);
+                if (!valid) break;
                 const Item it = decode_item(w, prefix, a);
+                w = atomicAdd(a.item_counter, 1u);                 // the next draw travels while this item streams
                 const int32_t y0 = (int32_t)(it.group * a.w_rows + it.m_item * tile_rows);
                 const int32_t y1 = kE == kEAct ? y0 : y0 + (int32_t)BM;
+                for (uint32_t st = 0; st < steps; st++) {
+                    if (!mbar_wait(&empty[s], ph ^ 1u, abort_flag)) { ok = false; break; }
+                    unsigned char *dst = base + s * kStageBytes;
+                    const int32_t x = (int32_t)(st * KS);
+                    mbar_arrive_expect_tx(&full[s], 2u * kATx);
+                    tma_load_2d(dst, &maps.a0, &full[s], x, y0);
+                    tma_load_2d(dst + kATile, &maps.a1, &full[s], x, y1);
+                    if (++s == kStages) { s = 0; ph ^= 1u; }
+                }
+            }
+        }
+    } else if (warp == 2) {
+        // ================================ TMA producer: token terms
+        if (lane == 0) {
+            prefetch_tensormap(&maps.bhi);
+            prefetch_tensormap(&maps.blo);
+            uint32_t s = 0, ph = 0;
+            bool ok = true;
+            for (uint32_t w = next_item(); ok && w != kNoItem; w = next_item()) {
+                const Item it = decode_item(w, prefix, a);
                 const uint32_t boxes = (it.rows_valid + kBBox - 1u) / kBBox;
                 for (uint32_t st = 0; st < steps; st++) {
                     if (!mbar_wait(&empty[s], ph ^ 1u, abort_flag)) { ok = false; break; }
                     unsigned char *dst = base + s * kStageBytes;
                     const int32_t x = (int32_t)(st * KS);
-                    if (weights) {
-                        mbar_arrive_expect_tx(&full[s], 2u * kATx);
-                        tma_load_2d(dst, &maps.a0, &full[s], x, y0);
-                        tma_load_2d(dst + kATile, &maps.a1, &full[s], x, y1);
-                    } else {
-                        // only as many 32-row boxes as the tile has rows
-                        mbar_arrive_expect_tx(&full[s], 2u * boxes * kBBox * 128u);
-                        unsigned char *bh = dst + 2u * kATile, *bl = bh + kBTile;
-                        for (uint32_t b = 0; b < boxes; b++) {
-                            const int32_t y = (int32_t)(it.row_start + b * kBBox);
-                            tma_load_2d(bh + b * kBBox * 128u, &maps.bhi, &full[s], x, y);
-                            tma_load_2d(bl + b * kBBox * 128u, &maps.blo, &full[s], x, y);
-                        }
+                    // only as many 32-row boxes as the tile has rows
+                    mbar_arrive_expect_tx(&full[s], 2u * boxes * kBBox * 128u);
+                    unsigned char *bh = dst + 2u * kATile, *bl = bh + kBTile;
+                    for (uint32_t b = 0; b < boxes; b++) {
+                        const int32_t y = (int32_t)(it.row_start + b * kBBox);
+                        tma_load_2d(bh + b * kBBox * 128u, &maps.bhi, &full[s], x, y);
+                        tma_load_2d(bl + b * kBBox * 128u, &maps.blo, &full[s], x, y);
                     }
                     if (++s == kStages) { s = 0; ph ^= 1u; }
                 }
@@ -269,7 +327,7 @@ grouped_mx_kernel(const __grid_constant__ GmxMaps maps, GmxArgs a) {
             prefetch_tensormap(&maps.sfb);
             uint32_t s = 0, ph = 0;
             bool ok = true;
-            for (uint32_t w = blockIdx.x; ok && w < total_items; w += gridDim.x) {
+            for (uint32_t w = next_item(); ok && w != kNoItem; w = next_item()) {
                 const Item it = decode_item(w, prefix, a);
                 const int32_t y0 = (int32_t)(it.group * a.w_rows + it.m_item * tile_rows);
                 const int32_t y1 = kE == kEAct ? y0 : y0 + (int32_t)BM;
@@ -294,7 +352,7 @@ grouped_mx_kernel(const __grid_constant__ GmxMaps maps, GmxArgs a) {
             const uint32_t q = warp == 1 ? 0u : 1u;
             uint32_t s = 0, ph = 0, pacc = 0, sb = 0, sph = 0;
             bool ok = true;
-            for (uint32_t w = blockIdx.x; ok && w < total_items; w += gridDim.x) {
+            for (uint32_t w = next_item(); ok && w != kNoItem; w = next_item()) {
                 const Item it = decode_item(w, prefix, a);
                 const uint32_t n_eff = max(16u, (it.rows_valid + 15u) & ~15u);
                 uint32_t idesc[4];
@@ -343,7 +401,8 @@ grouped_mx_kernel(const __grid_constant__ GmxMaps maps, GmxArgs a) {
         const uint32_t lane_base = (32u * quad) << 16;
         uint32_t sb = 0, sph = 0, ss = 0, ssph = 0;
         bool ok = true;
-        for (uint32_t w = blockIdx.x; ok && w < total_items; w += gridDim.x) {
+        for (uint32_t w = __shfl_sync(0xffffffffu, next_item(), 0); ok && w != kNoItem;
+             w = __shfl_sync(0xffffffffu, next_item(), 0)) {
             for (uint32_t st = 0; st < steps; st += 4u) {
                 if (!mbar_wait(&sfs_full[ss], ssph, abort_flag)) { ok = false; break; }
                 const unsigned char *src = sf_smem + ss * kSfSlotBytes;
@@ -386,7 +445,8 @@ grouped_mx_kernel(const __grid_constant__ GmxMaps maps, GmxArgs a) {
         const uint32_t half = (warp - 8u) >> 2;
         const uint32_t m = 32u * quad + lane;            // weight row inside the tile
         uint32_t pacc = 0;
-        for (uint32_t w = blockIdx.x; w < total_items; w += gridDim.x) {
+        for (uint32_t w = __shfl_sync(0xffffffffu, next_item(), 0); w != kNoItem;
+             w = __shfl_sync(0xffffffffu, next_item(), 0)) {
             const Item it = decode_item(w, prefix, a);
             if (!mbar_wait(acc_full, pacc, abort_flag)) break;
             pacc ^= 1u;
@@ -586,6 +646,7 @@ struct Scratch {
     uint8_t *t_hi, *t_lo, *t_sf;       // per source row (only with an index)
     uint8_t *x_hi, *x_lo, *x_sf;       // per product row
     uint8_t *a_hi, *a_lo, *a_sf;       // activation, per product row
+    uint32_t *counters;                // item counters of the two launches (zeroed per call)
     size_t total;
 };
 
@@ -608,6 +669,7 @@ Scratch carve_scratch(const k3_moe_layer_desc *d, uint32_t rows, uint32_t source
     s.a_hi = take(R * I);
     s.a_lo = take(R * I);
     s.a_sf = take(R * (I / 32u));
+    s.counters = (uint32_t *)take(256);
     s.total = off + 256u;
     return s;
 }
@@ -664,8 +726,13 @@ bool k3_grouped_mx_experts(const k3_moe_layer_desc *d, void *rows_out, void *act
                                                        (const uint32_t *)index, rows, H / 512u);
         if (!launch_ok()) return false;
     }
+    if (cudaMemsetAsync(s.counters, 0, 256, stream) != cudaSuccess) {
+        (void)cudaGetLastError();
+        return false;
+    }
     GmxArgs a{};
     a.offsets = (const uint32_t *)offsets;
+    a.item_counter = s.counters;
     a.groups = d->local_expert_count;
     a.rows = rows;
     a.activation = d->activation;
@@ -683,6 +750,7 @@ bool k3_grouped_mx_experts(const k3_moe_layer_desc *d, void *rows_out, void *act
     const Operands gu{d->w1_packed, d->w3_packed, d->w1_scales, d->w3_scales, s.x_hi, s.x_lo, s.x_sf};
     if (!launch<kEAct>(gu, a, stream)) return false;
     // down
+    a.item_counter = s.counters + 32;
     a.out = (uint16_t *)rows_out;
     a.act_hi = a.act_lo = a.act_sf = nullptr;
     a.w_rows = H;
