@@ -88,18 +88,93 @@ const NcclApi *nccl_api(char *error, size_t error_size) {
 
 inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
-// order[grouped position] = received position, inverse[received position] = grouped
-// position, for the rows of every (local expert, source) block; one warp per block.
+// --- each token row crosses to a destination once, however many of its routes go there
+// mask[t] = set of destination ranks of token t's routes
 __global__ void __launch_bounds__(256)
-ep_order_kernel(uint32_t *__restrict__ order, uint32_t *__restrict__ inverse,
-                const uint32_t *__restrict__ block_recv_start, const uint32_t *__restrict__ block_dest_start,
-                const uint32_t *__restrict__ block_rows, uint32_t blocks) {
+ep_mask_kernel(unsigned long long *__restrict__ mask, const uint32_t *__restrict__ ids, uint32_t tokens,
+               uint32_t top_k, uint32_t per) {
+    const uint32_t t = blockIdx.x * blockDim.x + threadIdx.x;
+    if (t >= tokens) return;
+    unsigned long long m = 0ull;
+    for (uint32_t r = 0; r < top_k; r++) m |= 1ull << (ids[(uint64_t)t * top_k + r] / per);
+    mask[t] = m;
+}
+
+// One block per destination g: the tokens that have a route to g, in token order -
+// token_list[g * tokens + slot] = t, slot[t * world + g] = slot, unique[g] = how many.
+__global__ void __launch_bounds__(1024)
+ep_unique_kernel(uint32_t *__restrict__ slot, uint32_t *__restrict__ token_list, uint32_t *__restrict__ unique,
+                 const unsigned long long *__restrict__ mask, uint32_t tokens, uint32_t world) {
+    __shared__ uint32_t warp_total[32];
+    __shared__ uint32_t running_s;
+    const uint32_t g = blockIdx.x, lane = threadIdx.x % kWarp, warp = threadIdx.x / kWarp;
+    if (threadIdx.x == 0) running_s = 0u;
+    __syncthreads();
+    for (uint32_t base = 0; base < tokens; base += blockDim.x) {
+        const uint32_t t = base + threadIdx.x;
+        const bool flag = t < tokens && ((mask[t] >> g) & 1ull) != 0ull;
+        const uint32_t ballot = __ballot_sync(0xffffffffu, flag);
+        if (lane == 0) warp_total[warp] = __popc(ballot);
+        __syncthreads();
+        uint32_t before = running_s;
+        for (uint32_t w = 0; w < warp; w++) before += warp_total[w];
+        if (flag) {
+            const uint32_t pos = before + __popc(ballot & ((1u << lane) - 1u));
+            slot[(uint64_t)t * world + g] = pos;
+            token_list[(uint64_t)g * tokens + pos] = t;
+        }
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            uint32_t total = 0;
+            for (uint32_t w = 0; w < blockDim.x / kWarp; w++) total += warp_total[w];
+            running_s += total;
+        }
+        __syncthreads();
+    }
+    if (threadIdx.x == 0) unique[g] = running_s;
+}
+
+// route_slot[p] = slot of the route's token among the rows sent to the route's destination
+__global__ void __launch_bounds__(256)
+ep_route_slot_kernel(uint32_t *__restrict__ route_slot, const uint32_t *__restrict__ slot,
+                     const uint32_t *__restrict__ sorted_route, const uint32_t *__restrict__ sorted_token,
+                     const uint32_t *__restrict__ ids, uint32_t routes, uint32_t per, uint32_t world) {
+    const uint32_t p = blockIdx.x * blockDim.x + threadIdx.x;
+    if (p >= routes) return;
+    const uint32_t g = ids[sorted_route[p]] / per;
+    route_slot[p] = slot[(uint64_t)sorted_token[p] * world + g];
+}
+
+// rows_send[g * tokens + i] = x[token_list[g * tokens + i]] for i < unique[g]; one warp per row
+__global__ void __launch_bounds__(256)
+ep_gather_unique_kernel(uint4 *__restrict__ rows_send, const uint4 *__restrict__ x,
+                        const uint32_t *__restrict__ token_list, const uint32_t *__restrict__ unique,
+                        uint32_t tokens, uint32_t world, uint32_t units) {
+    const uint32_t lane = threadIdx.x % kWarp;
+    const uint32_t warps = gridDim.x * blockDim.x / kWarp;
+    for (uint32_t row = (blockIdx.x * blockDim.x + threadIdx.x) / kWarp; row < world * tokens; row += warps) {
+        const uint32_t g = row / tokens, i = row % tokens;
+        if (i >= unique[g]) continue;
+        const uint4 *src = x + (uint64_t)token_list[row] * units;
+        uint4 *dst = rows_send + (uint64_t)row * units;
+        for (uint32_t u = lane; u < units; u += kWarp) dst[u] = src[u];
+    }
+}
+
+// like ep_order_kernel, for rows sent once per destination: the product row at a grouped
+// position reads the received row (first row of the block's source + the route's slot)
+__global__ void __launch_bounds__(256)
+ep_order_slots_kernel(uint32_t *__restrict__ row_index, uint32_t *__restrict__ inverse,
+                      const uint32_t *__restrict__ slots_recv, const uint32_t *__restrict__ block_recv_start,
+                      const uint32_t *__restrict__ block_dest_start, const uint32_t *__restrict__ block_rows,
+                      const uint32_t *__restrict__ source_first_row, uint32_t blocks, uint32_t world) {
     const uint32_t warp = (blockIdx.x * blockDim.x + threadIdx.x) / kWarp, lane = threadIdx.x % kWarp;
     const uint32_t warps = gridDim.x * blockDim.x / kWarp;
     for (uint32_t b = warp; b < blocks; b += warps) {
         const uint32_t from = block_recv_start[b], to = block_dest_start[b], n = block_rows[b];
+        const uint32_t first = source_first_row[b % world];
         for (uint32_t i = lane; i < n; i += kWarp) {
-            order[to + i] = from + i;
+            row_index[to + i] = first + slots_recv[from + i];
             inverse[from + i] = to + i;
         }
     }
@@ -113,11 +188,13 @@ struct k3_moe_ep {
     ncclComm_t comm = nullptr;
     uint32_t *pinned = nullptr;          // [world][kPinnedRow] offsets of every rank, then the plan tables
     size_t pinned_words = 0;
+    cudaStream_t side = nullptr;         // the shared expert runs here, beside the exchange
+    cudaEvent_t fork = nullptr, join = nullptr;
     cudaEvent_t counts_ready = nullptr, t_begin = nullptr, t_experts0 = nullptr, t_experts1 = nullptr,
                 t_end = nullptr;
     uint32_t last_recv_rows = 0;
     bool timed = false;
-    std::vector<uint32_t> send_rows, recv_rows;
+    std::vector<uint32_t> send_rows, recv_rows, send_unique, recv_unique;
 };
 
 namespace {
@@ -141,8 +218,11 @@ struct EpWorkspace {
     uint32_t *offsets, *sorted_route, *sorted_token, *inv_perm;
     void *dispatch_ws;
     size_t dispatch_bytes;
-    uint32_t *offsets_all;                 // [world][E + 1]
-    uint32_t *tables;                      // block_recv_start | block_dest_start | block_rows | offsets_local
+    uint32_t *offsets_all;                 // [world][E + 1 + world]: every rank's offsets and unique-row counts
+    uint32_t *tables;                      // block_recv_start | block_dest_start | block_rows | offsets_local | source_first_row
+    unsigned long long *dest_mask;         // [tokens]
+    uint32_t *slot, *token_list;           // [tokens, world], [world, tokens]
+    uint32_t *route_slot, *slots_recv;     // [routes], [max_recv]
     uint32_t *order, *inverse;             // [max_recv]
     uint16_t *rows_send, *rows_home;       // [routes, d]
     uint16_t *rows_recv, *rows_out, *rows_back;   // [max_recv, d]
@@ -172,17 +252,22 @@ EpWorkspace carve_ep(const k3_moe_layer_desc *d, uint32_t world, uint32_t tokens
     w.logits = (float *)take((size_t)t1 * d->expert_count * 4u);
     w.ids = (uint32_t *)take(routes * 4u);
     w.weights = (float *)take(routes * 4u);
-    w.offsets = (uint32_t *)take((size_t)(d->expert_count + 1u) * 4u);
+    w.offsets = (uint32_t *)take((size_t)(d->expert_count + 1u + world) * 4u);   // + this rank's unique-row counts
     w.sorted_route = (uint32_t *)take(routes * 4u);
     w.sorted_token = (uint32_t *)take(routes * 4u);
     w.inv_perm = (uint32_t *)take(routes * 4u);
     w.dispatch_bytes = k3_moe_dispatch_workspace_bytes(t1, d->top_k, d->expert_count);
     w.dispatch_ws = take(w.dispatch_bytes);
-    w.offsets_all = (uint32_t *)take((size_t)world * (d->expert_count + 1u) * 4u);
-    w.tables = (uint32_t *)take(((size_t)3u * per * world + per + 1u) * 4u);
+    w.offsets_all = (uint32_t *)take((size_t)world * (d->expert_count + 1u + world) * 4u);
+    w.tables = (uint32_t *)take(((size_t)3u * per * world + per + 1u + world) * 4u);
+    w.dest_mask = (unsigned long long *)take((size_t)t1 * 8u);
+    w.slot = (uint32_t *)take((size_t)t1 * world * 4u);
+    w.token_list = (uint32_t *)take((size_t)t1 * world * 4u);
+    w.route_slot = (uint32_t *)take(routes * 4u);
+    w.slots_recv = (uint32_t *)take((size_t)cap * 4u);
     w.order = (uint32_t *)take((size_t)cap * 4u);
     w.inverse = (uint32_t *)take((size_t)cap * 4u);
-    w.rows_send = (uint16_t *)take(routes * d->hidden * 2u);
+    w.rows_send = (uint16_t *)take((size_t)t1 * world * d->hidden * 2u);       // one region of t1 rows per destination
     w.rows_home = (uint16_t *)take(routes * d->hidden * 2u);
     w.rows_recv = (uint16_t *)take((size_t)cap * d->hidden * 2u);
     w.rows_out = (uint16_t *)take((size_t)cap * d->hidden * 2u);
@@ -279,13 +364,18 @@ extern "C" bool k3_moe_ep_create(k3_moe_ep **out, const void *id_bytes, int rank
     ep->device = current_device();
     ep->send_rows.resize(world);
     ep->recv_rows.resize(world);
+    ep->send_unique.resize(world);
+    ep->recv_unique.resize(world);
     // every rank's offsets, then the plan tables of the largest shard
-    ep->pinned_words = (size_t)world * (kMaxExpertsEp + 1u) + (size_t)3u * kMaxExpertsEp + kMaxExpertsEp + 1u;
+    ep->pinned_words = (size_t)world * (kMaxExpertsEp + 1u + kMaxWorld) + (size_t)3u * kMaxExpertsEp + kMaxExpertsEp + 1u + kMaxWorld;
     bool ok = cudaHostAlloc((void **)&ep->pinned, ep->pinned_words * 4u, cudaHostAllocDefault) == cudaSuccess;
     for (cudaEvent_t *e : {&ep->t_begin, &ep->t_experts0, &ep->t_experts1, &ep->t_end}) {
         ok = ok && cudaEventCreate(e) == cudaSuccess;
     }
     ok = ok && cudaEventCreateWithFlags(&ep->counts_ready, cudaEventDisableTiming) == cudaSuccess;
+    ok = ok && cudaEventCreateWithFlags(&ep->fork, cudaEventDisableTiming) == cudaSuccess;
+    ok = ok && cudaEventCreateWithFlags(&ep->join, cudaEventDisableTiming) == cudaSuccess;
+    ok = ok && cudaStreamCreateWithFlags(&ep->side, cudaStreamNonBlocking) == cudaSuccess;
     if (!ok) {
         (void)cudaGetLastError();
         set_error(error, error_size, "host buffer or event creation failed");
@@ -314,23 +404,38 @@ extern "C" void k3_moe_ep_destroy(k3_moe_ep *ep) {
     if (!ep) return;
     if (ep->comm && ep->api) (void)ep->api->CommDestroy(ep->comm);
     if (ep->pinned) (void)cudaFreeHost(ep->pinned);
-    for (cudaEvent_t e : {ep->counts_ready, ep->t_begin, ep->t_experts0, ep->t_experts1, ep->t_end}) {
+    for (cudaEvent_t e : {ep->counts_ready, ep->t_begin, ep->t_experts0, ep->t_experts1, ep->t_end, ep->fork, ep->join}) {
         if (e) (void)cudaEventDestroy(e);
     }
+    if (ep->side) (void)cudaStreamDestroy(ep->side);
     delete ep;
 }
 
 extern "C" int k3_moe_ep_rank(const k3_moe_ep *ep) { return ep ? ep->rank : -1; }
 extern "C" int k3_moe_ep_world(const k3_moe_ep *ep) { return ep ? ep->world : 0; }
 
+namespace {
+bool plan_impl(const uint32_t *offsets_all, uint32_t stride, uint32_t world, uint32_t rank, uint32_t experts,
+               uint32_t *send_rows, uint32_t *recv_rows, uint32_t *block_recv_start, uint32_t *block_dest_start,
+               uint32_t *block_rows, uint32_t *offsets_local);
+}
+
 extern "C" bool k3_moe_ep_plan(const uint32_t *offsets_all, uint32_t world, uint32_t rank, uint32_t experts,
                                uint32_t *send_rows, uint32_t *recv_rows, uint32_t *block_recv_start,
                                uint32_t *block_dest_start, uint32_t *block_rows, uint32_t *offsets_local) {
+    return plan_impl(offsets_all, experts + 1u, world, rank, experts, send_rows, recv_rows, block_recv_start,
+                     block_dest_start, block_rows, offsets_local);
+}
+
+namespace {
+bool plan_impl(const uint32_t *offsets_all, uint32_t stride, uint32_t world, uint32_t rank, uint32_t experts,
+               uint32_t *send_rows, uint32_t *recv_rows, uint32_t *block_recv_start, uint32_t *block_dest_start,
+               uint32_t *block_rows, uint32_t *offsets_local) {
     if (!offsets_all || !send_rows || !recv_rows || !block_recv_start || !block_dest_start || !block_rows ||
         !offsets_local || world == 0 || rank >= world || experts == 0 || experts % world != 0) {
         return false;
     }
-    const uint32_t per = experts / world, first = rank * per, stride = experts + 1u;
+    const uint32_t per = experts / world, first = rank * per;
     const uint32_t *own = offsets_all + (size_t)rank * stride;
     for (uint32_t g = 0; g < world; g++) send_rows[g] = own[(g + 1u) * per] - own[g * per];
     // rows arrive source by source; inside a source (expert asc, route asc)
@@ -358,6 +463,7 @@ extern "C" bool k3_moe_ep_plan(const uint32_t *offsets_all, uint32_t world, uint
     offsets_local[per] = dest;
     return true;
 }
+}  // namespace
 
 extern "C" size_t k3_moe_ep_workspace_bytes(const k3_moe_ep *ep, const k3_moe_layer_desc *d,
                                             uint32_t local_tokens, uint32_t max_recv_rows) {
@@ -392,19 +498,23 @@ extern "C" bool k3_moe_ep_layer_forward(k3_moe_ep *ep, const k3_moe_layer_desc *
     if (cudaEventRecord(ep->t_begin, stream) != cudaSuccess) return fail("event record failed");
     ep->timed = false;
 
-    // 1. routing and dispatch of the local tokens
+    // 1. routing and dispatch of the local tokens; which destinations each token goes to
+    const uint32_t stride = E + 1u + world;                 // offsets, then unique-row counts per destination
+    uint32_t *unique_dev = w.offsets + E + 1u;
     if (tokens != 0) {
         if (!k3_moe_route(d, w.ids, w.weights, w.logits, x, tokens, stream)) return fail("k3_moe_route failed");
         if (!k3_moe_dispatch_build(w.offsets, w.sorted_route, w.sorted_token, w.inv_perm, w.ids, tokens, k, E,
                                    w.dispatch_ws, w.dispatch_bytes, stream)) {
             return fail("k3_moe_dispatch_build failed");
         }
-    } else if (cudaMemsetAsync(w.offsets, 0, (size_t)(E + 1u) * 4u, stream) != cudaSuccess) {
+        ep_mask_kernel<<<(tokens + 255u) / 256u, 256, 0, stream>>>(w.dest_mask, w.ids, tokens, k, per);
+        ep_unique_kernel<<<world, 1024, 0, stream>>>(w.slot, w.token_list, unique_dev, w.dest_mask, tokens, world);
+        if (!launch_ok()) return fail("destination kernels failed");
+    } else if (cudaMemsetAsync(w.offsets, 0, (size_t)stride * 4u, stream) != cudaSuccess) {
         return fail("memset failed");
     }
 
-    // 2. every rank's offsets to every rank, and on to the host
-    const uint32_t stride = E + 1u;
+    // 2. every rank's offsets and unique-row counts to every rank, and on to the host
     uint32_t *host_offsets = ep->pinned;
     if (world > 1) {
         if (!nccl_ok(ep, ep->api->AllGather(w.offsets, w.offsets_all, stride, ncclUint32, ep->comm, stream), error,
@@ -421,26 +531,45 @@ extern "C" bool k3_moe_ep_layer_forward(k3_moe_ep *ep, const k3_moe_layer_desc *
         return fail("copy of the offsets to the host failed");
     }
 
-    // 3. while they travel: rows in sorted order (one per route) and the shared expert
+    // 3. while they travel: the rows to send (each token once per destination it has a route
+    // to, in token order, destination g's rows in region g), the slot of every route among
+    // them, and the shared expert
     if (tokens != 0) {
-        if (!k3_rocm_gather_rows_bf16(w.rows_send, x, w.sorted_token, routes, H, stream)) {
-            return fail("row gather failed");
-        }
-        if (d->shared_hidden &&
-            !(w.sh_bytes != 0 ? k3_grouped_shared_expert(d, w.sh_out, w.sh_act, x, tokens, w.sh_ws, stream)
-                              : k3_moe_shared_expert(d, w.sh_out, w.sh_gate, w.sh_up, w.sh_act, x, tokens, stream))) {
-            return fail("shared expert failed");
+        ep_gather_unique_kernel<<<std::min<uint32_t>((world * tokens + 7u) / 8u, (uint32_t)sm_count() * 16u), 256, 0,
+                                  stream>>>((uint4 *)w.rows_send, (const uint4 *)x, w.token_list, unique_dev, tokens,
+                                            world, H / 8u);
+        ep_route_slot_kernel<<<(routes + 255u) / 256u, 256, 0, stream>>>(w.route_slot, w.slot, w.sorted_route,
+                                                                         w.sorted_token, w.ids, routes, per, world);
+        if (!launch_ok()) return fail("row gather failed");
+        // the shared expert depends only on the local tokens: on the handle's second stream it
+        // runs beside the exchange (whose kernels take a few SMs) and is joined before the combine
+        if (d->shared_hidden) {
+            if (cudaEventRecord(ep->fork, stream) != cudaSuccess || cudaStreamWaitEvent(ep->side, ep->fork, 0) != cudaSuccess)
+                return fail("stream fork failed");
+            if (!(w.sh_bytes != 0 ? k3_grouped_shared_expert(d, w.sh_out, w.sh_act, x, tokens, w.sh_ws, ep->side)
+                                  : k3_moe_shared_expert(d, w.sh_out, w.sh_gate, w.sh_up, w.sh_act, x, tokens, ep->side))) {
+                return fail("shared expert failed");
+            }
+            if (cudaEventRecord(ep->join, ep->side) != cudaSuccess) return fail("stream join failed");
         }
     }
 
     // 4. the one host wait of the pass, then the plan
     if (cudaEventSynchronize(ep->counts_ready) != cudaSuccess) return fail("waiting for the offsets failed");
-    uint32_t *plan = ep->pinned + (size_t)world * (kMaxExpertsEp + 1u);
+    uint32_t *plan = ep->pinned + (size_t)world * (kMaxExpertsEp + 1u + kMaxWorld);
     uint32_t *block_recv_start = plan, *block_dest_start = plan + (size_t)per * world,
-             *block_rows = plan + (size_t)2u * per * world, *offsets_local = plan + (size_t)3u * per * world;
-    if (!k3_moe_ep_plan(host_offsets, world, rank, E, ep->send_rows.data(), ep->recv_rows.data(), block_recv_start,
-                        block_dest_start, block_rows, offsets_local)) {
+             *block_rows = plan + (size_t)2u * per * world, *offsets_local = plan + (size_t)3u * per * world,
+             *source_first_row = offsets_local + per + 1u;
+    if (!plan_impl(host_offsets, stride, world, rank, E, ep->send_rows.data(), ep->recv_rows.data(), block_recv_start,
+                   block_dest_start, block_rows, offsets_local)) {
         return fail("exchange plan failed");
+    }
+    uint32_t n_unique = 0;
+    for (uint32_t g = 0; g < world; g++) {
+        ep->send_unique[g] = host_offsets[(size_t)rank * stride + E + 1u + g];
+        ep->recv_unique[g] = host_offsets[(size_t)g * stride + E + 1u + rank];
+        source_first_row[g] = n_unique;
+        n_unique += ep->recv_unique[g];
     }
     const uint32_t n_recv = offsets_local[per];
     ep->last_recv_rows = n_recv;
@@ -450,55 +579,64 @@ extern "C" bool k3_moe_ep_layer_forward(k3_moe_ep *ep, const k3_moe_layer_desc *
                  max_recv);
         return fail(text);
     }
-    const size_t table_words = (size_t)3u * per * world + per + 1u;
+    const size_t table_words = (size_t)3u * per * world + per + 1u + world;
     if (cudaMemcpyAsync(w.tables, plan, table_words * 4u, cudaMemcpyHostToDevice, stream) != cudaSuccess) {
         return fail("plan upload failed");
     }
 
-    // 5. dispatch: one grouped send/recv, the own rank's rows by a device copy
-    auto exchange = [&](const uint16_t *send_base, const std::vector<uint32_t> &send, uint16_t *recv_base,
-                        const std::vector<uint32_t> &recv, const char *what) -> bool {
-        size_t soff = 0, roff = 0, self_soff = 0, self_roff = 0;
+    // 5. dispatch: one grouped send/recv (token rows once per destination + a slot per route),
+    // the own rank's share by device copies
+    {
+        size_t roff_rows = 0, roff_routes = 0, soff_routes = 0, self_rows = 0, self_routes_s = 0, self_routes_r = 0;
         if (world > 1 && !nccl_ok(ep, ep->api->GroupStart(), error, error_size, "ncclGroupStart")) return false;
         for (uint32_t g = 0; g < world; g++) {
+            const uint16_t *region = w.rows_send + (size_t)g * std::max(tokens, 1u) * H;
             if (g == rank) {
-                self_soff = soff;
-                self_roff = roff;
+                self_rows = roff_rows;
+                self_routes_s = soff_routes;
+                self_routes_r = roff_routes;
             } else {
-                if (send[g] != 0 &&
-                    !nccl_ok(ep, ep->api->Send(send_base + soff * H, (size_t)send[g] * H, ncclBfloat16, (int)g, ep->comm,
-                                               stream), error, error_size, what)) {
+                if (ep->send_unique[g] != 0 &&
+                    (!nccl_ok(ep, ep->api->Send(region, (size_t)ep->send_unique[g] * H, ncclBfloat16, (int)g, ep->comm, stream),
+                              error, error_size, "dispatch send") ||
+                     !nccl_ok(ep, ep->api->Send(w.route_slot + soff_routes, ep->send_rows[g], ncclUint32, (int)g, ep->comm,
+                                                stream), error, error_size, "dispatch send of the slots"))) {
                     return false;
                 }
-                if (recv[g] != 0 &&
-                    !nccl_ok(ep, ep->api->Recv(recv_base + roff * H, (size_t)recv[g] * H, ncclBfloat16, (int)g, ep->comm,
-                                               stream), error, error_size, what)) {
+                if (ep->recv_unique[g] != 0 &&
+                    (!nccl_ok(ep, ep->api->Recv(w.rows_recv + roff_rows * H, (size_t)ep->recv_unique[g] * H, ncclBfloat16,
+                                                (int)g, ep->comm, stream), error, error_size, "dispatch recv") ||
+                     !nccl_ok(ep, ep->api->Recv(w.slots_recv + roff_routes, ep->recv_rows[g], ncclUint32, (int)g, ep->comm,
+                                                stream), error, error_size, "dispatch recv of the slots"))) {
                     return false;
                 }
             }
-            soff += send[g];
-            roff += recv[g];
+            soff_routes += ep->send_rows[g];
+            roff_rows += ep->recv_unique[g];
+            roff_routes += ep->recv_rows[g];
         }
         if (world > 1 && !nccl_ok(ep, ep->api->GroupEnd(), error, error_size, "ncclGroupEnd")) return false;
-        if (send[rank] != 0 &&
-            cudaMemcpyAsync(recv_base + self_roff * H, send_base + self_soff * H, (size_t)send[rank] * H * 2u,
-                            cudaMemcpyDeviceToDevice, stream) != cudaSuccess) {
+        if (ep->send_unique[rank] != 0 &&
+            (cudaMemcpyAsync(w.rows_recv + self_rows * H, w.rows_send + (size_t)rank * std::max(tokens, 1u) * H,
+                             (size_t)ep->send_unique[rank] * H * 2u, cudaMemcpyDeviceToDevice, stream) != cudaSuccess ||
+             cudaMemcpyAsync(w.slots_recv + self_routes_r, w.route_slot + self_routes_s, (size_t)ep->send_rows[rank] * 4u,
+                             cudaMemcpyDeviceToDevice, stream) != cudaSuccess)) {
             return fail("copy of the rank's own rows failed");
         }
-        return true;
-    };
-    if (!exchange(w.rows_send, ep->send_rows, w.rows_recv, ep->recv_rows, "dispatch send/recv")) return false;
+    }
 
-    // 6. grouped order of the received rows, expert products on the local shard
+    // 6. grouped order of the received routes, expert products on the local shard
     if (n_recv != 0) {
         const uint32_t blocks = per * world;
-        ep_order_kernel<<<std::min<uint32_t>((blocks + 7u) / 8u, (uint32_t)sm_count() * 4u), 256, 0, stream>>>(
-            w.order, w.inverse, w.tables, w.tables + blocks, w.tables + 2u * blocks, blocks);
-        if (!launch_ok()) return fail("order kernel launch failed");
         const uint32_t *offsets_local_dev = w.tables + 3u * blocks;
+        ep_order_slots_kernel<<<std::min<uint32_t>((blocks + 7u) / 8u, (uint32_t)sm_count() * 4u), 256, 0, stream>>>(
+            w.order, w.inverse, w.slots_recv, w.tables, w.tables + blocks, w.tables + 2u * blocks,
+            offsets_local_dev + per + 1u, blocks, world);
+        if (!launch_ok()) return fail("order kernel launch failed");
         if (cudaEventRecord(ep->t_experts0, stream) != cudaSuccess) return fail("event record failed");
         if (w.mx_bytes != 0 && k3_grouped_mx_supported(d, n_recv)) {
-            if (!k3_grouped_mx_experts(d, w.rows_out, nullptr, w.rows_recv, w.order, n_recv, offsets_local_dev, n_recv,
+            // product row p reads received row order[p]; the received rows are converted once each
+            if (!k3_grouped_mx_experts(d, w.rows_out, nullptr, w.rows_recv, w.order, n_unique, offsets_local_dev, n_recv,
                                        w.mx_ws, stream)) {
                 return fail("grouped expert products failed");
             }
@@ -511,15 +649,44 @@ extern "C" bool k3_moe_ep_layer_forward(k3_moe_ep *ep, const k3_moe_layer_desc *
         }
         if (cudaEventRecord(ep->t_experts1, stream) != cudaSuccess) return fail("event record failed");
         ep->timed = true;
-        // 7. back into received order, and home
+        // 7. back into received order, and home (one row per route: the combine stays exact)
         if (!k3_rocm_gather_rows_bf16(w.rows_back, w.rows_out, w.inverse, n_recv, H, stream)) {
             return fail("return gather failed");
         }
     }
-    if (!exchange(w.rows_back, ep->recv_rows, w.rows_home, ep->send_rows, "return send/recv")) return false;
+    {
+        size_t soff = 0, roff = 0, self_soff = 0, self_roff = 0;
+        if (world > 1 && !nccl_ok(ep, ep->api->GroupStart(), error, error_size, "ncclGroupStart")) return false;
+        for (uint32_t g = 0; g < world; g++) {
+            if (g == rank) {
+                self_soff = soff;
+                self_roff = roff;
+            } else {
+                if (ep->recv_rows[g] != 0 &&
+                    !nccl_ok(ep, ep->api->Send(w.rows_back + soff * H, (size_t)ep->recv_rows[g] * H, ncclBfloat16, (int)g,
+                                               ep->comm, stream), error, error_size, "return send")) {
+                    return false;
+                }
+                if (ep->send_rows[g] != 0 &&
+                    !nccl_ok(ep, ep->api->Recv(w.rows_home + roff * H, (size_t)ep->send_rows[g] * H, ncclBfloat16, (int)g,
+                                               ep->comm, stream), error, error_size, "return recv")) {
+                    return false;
+                }
+            }
+            soff += ep->recv_rows[g];
+            roff += ep->send_rows[g];
+        }
+        if (world > 1 && !nccl_ok(ep, ep->api->GroupEnd(), error, error_size, "ncclGroupEnd")) return false;
+        if (ep->send_rows[rank] != 0 &&
+            cudaMemcpyAsync(w.rows_home + self_roff * H, w.rows_back + self_soff * H, (size_t)ep->send_rows[rank] * H * 2u,
+                            cudaMemcpyDeviceToDevice, stream) != cudaSuccess) {
+            return fail("copy of the rank's own rows failed");
+        }
+    }
 
     // 8. combine in rank order on the token's own rank
     if (tokens != 0) {
+        if (d->shared_hidden && cudaStreamWaitEvent(stream, ep->join, 0) != cudaSuccess) return fail("stream join failed");
         if (!k3_moe_combine(out, w.rows_home, w.inv_perm, w.weights, d->shared_hidden ? w.sh_out : nullptr, tokens, k,
                             H, stream)) {
             return fail("combine failed");
