@@ -269,7 +269,9 @@ def run_config(args, cfg, tokens, world):
     return {"workload": args.workload, "tokens": tokens, "experts": cfg["experts"],
             "top_k": cfg["top_k"], "hidden": cfg["hidden"], "expert_hidden": cfg["expert_hidden"],
             "shared_hidden": cfg["shared_hidden"], "router_bias": cfg["bias_mode"],
-            "parallelism": (f"ep{world}: tokens data-parallel, experts sharded, exact rank-ordered combine"
+            "parallelism": (f"ep{world}: tokens data-parallel, experts sharded, "
+                            + ("exact rank-ordered combine" if args.ep_exact else
+                               "token rows sent once per rank, one weighted partial sum per (token, rank) returned")
                             + (f" x {args.ep_pieces} pipelined row ranges" if args.ep_pieces > 1 else ""))
             if world > 1 else "single",
             "l2": "inputs larger than L2 (expert weights 20.96 GB per pass)"}
@@ -360,7 +362,7 @@ def kind_peaks(torch) -> dict:
     return out
 
 
-def parity_check(world, rank, device, torch, dist):
+def parity_check(world, rank, device, torch, dist, reduced=False):
     """The layer against the CPU oracle on the small case the smoke check uses (hidden 1024,
     64 experts, top-8, shared expert), one token and 40 tokens, through the same entry
     points the timed region uses at this N (expert-parallel exchange included)."""
@@ -371,7 +373,7 @@ def parity_check(world, rank, device, torch, dist):
     worst = {"ids_exact": True, "near_ties": 0, "rel_l2": 0.0, "tokens_checked": 0}
     if world > 1:
         from moonshine_b200.ep import ExpertParallelLayer
-        layer = ExpertParallelLayer(cfg, seed=3, device=device, tokens=40, weights=weights)
+        layer = ExpertParallelLayer(cfg, seed=3, device=device, tokens=40, weights=weights, reduced_return=reduced)
     else:
         layer = MoELayer(cfg, weights, seed=3, device=device, max_tokens=40)
     for tokens in (1, 40):
@@ -650,11 +652,12 @@ def run_layer(args, device, peaks, torch, dist, world, rank, local_rank, MoELaye
         if world > 1:
             raise SystemExit("the latent workload runs on one GPU")
         return run_latent(args, cfg, tokens, device, peaks, torch)
-    parity = None if args.lean else parity_check(world, rank, device, torch, dist)
+    parity = None if args.lean else parity_check(world, rank, device, torch, dist, reduced=not args.ep_exact)
     one_token = tokens == 1
     if world > 1:
         from moonshine_b200.ep import ExpertParallelLayer
-        layer = ExpertParallelLayer(cfg, seed=0, device=device, tokens=max(tokens, world), pieces=args.ep_pieces)
+        layer = ExpertParallelLayer(cfg, seed=0, device=device, tokens=max(tokens, world), pieces=args.ep_pieces,
+                                    reduced_return=not args.ep_exact)
         local_tokens = 1 if one_token else layer.local_tokens
     else:
         layer = MoELayer(cfg, None, seed=0, device=device, max_tokens=tokens)
@@ -865,6 +868,9 @@ def main():
     ap.add_argument("--lean", action="store_true", help="timed region only (for profiler captures)")
     ap.add_argument("--ep-pieces", type=int, default=1,
                     help="expert-parallel runs: row ranges per pass pipelined against each other")
+    ap.add_argument("--ep-exact", action="store_true",
+                    help="expert-parallel runs: return every expert row and combine in rank order (bit-identical to "
+                         "one GPU) instead of one partial sum per (token, rank)")
     ap.add_argument("--experts", type=int, default=0, help="override the expert count (profiler captures)")
     ap.add_argument("--tokens", type=int, default=0, help="override the token count (profiler captures; decode_stack: tokens decoded)")
     args = ap.parse_args()

@@ -18,8 +18,10 @@
  *            blocks that is the single-GPU grouping order
  *            (k3_engine_prefill.inc:1175-1194), so results equal the one-GPU
  *            layer bit for bit
+ *   dispatch sends each token row once per destination rank (however many of its
+ *            routes go there) plus a 4-byte slot per route
  *   return   the reverse grouped send/recv, then the weighted combine in rank
- *            order on the source
+ *            order on the source (or partial sums per rank, k3_moe_ep_set_reduced_return)
  *
  * One token (decode): x is replicated, every rank routes it identically, runs
  * the selected experts it holds, and one all-reduce merges the rows (integer
@@ -52,6 +54,16 @@ bool k3_moe_ep_unique_id(void *id_bytes, char *error, size_t error_size);
 bool k3_moe_ep_create(k3_moe_ep **out, const void *id_bytes, int rank, int world,
                       char *error, size_t error_size);
 void k3_moe_ep_destroy(k3_moe_ep *ep);
+/* Return direction of k3_moe_ep_layer_forward.  Default (false): every expert row comes
+ * back and the token's own rank sums the top_k rows in rank order - results equal the
+ * one-GPU layer bit for bit.  Reduced (true): the expert rank forms, per token it
+ * served, the weighted sum of that token's rows in rank order (fp32, rounded to bf16
+ * once) and returns ONE row per (token, rank); the token's rank adds the partial sums
+ * in rank-of-GPU order.  top_k / (distinct ranks per token) times fewer bytes come back
+ * (8x at 2 ranks, 2.3x at 8 for top-16); the result differs from the exact mode by
+ * the extra roundings (rel-L2 about 1e-3, inside the layer tolerance of 1e-2).  All
+ * ranks must use the same setting. */
+bool k3_moe_ep_set_reduced_return(k3_moe_ep *ep, bool reduced);
 int k3_moe_ep_rank(const k3_moe_ep *ep);
 int k3_moe_ep_world(const k3_moe_ep *ep);
 

@@ -153,6 +153,7 @@ SIGNATURES = {
     "k3_moe_ep_unique_id": (C.c_bool, [vp, C.c_char_p, sz]),
     "k3_moe_ep_create": (C.c_bool, [C.POINTER(vp), vp, C.c_int, C.c_int, C.c_char_p, sz]),
     "k3_moe_ep_destroy": (None, [vp]),
+    "k3_moe_ep_set_reduced_return": (C.c_bool, [vp, C.c_bool]),
     "k3_moe_ep_rank": (C.c_int, [vp]),
     "k3_moe_ep_world": (C.c_int, [vp]),
     "k3_moe_ep_plan": (C.c_bool, [_U32P, u32, u32, u32, _U32P, _U32P, _U32P, _U32P, _U32P, _U32P]),

@@ -180,6 +180,108 @@ ep_order_slots_kernel(uint32_t *__restrict__ row_index, uint32_t *__restrict__ i
     }
 }
 
+// --- reduced return: the expert rank forms sum_r w_r * row_r over the routes of one token
+// that it served (in rank order) and sends ONE row per (token, destination) back.
+// On the source: for every (destination g, unique row i) the positions of the token's
+// routes among the routes sent to g (rank order, 0xffffffff = none) and their weights.
+__global__ void __launch_bounds__(256)
+ep_unique_routes_kernel(uint32_t *__restrict__ unique_routes, float *__restrict__ unique_weights,
+                        const uint32_t *__restrict__ ids, const float *__restrict__ weights,
+                        const uint32_t *__restrict__ inv_perm, const uint32_t *__restrict__ offsets,
+                        const uint32_t *__restrict__ slot, uint32_t tokens, uint32_t top_k, uint32_t per,
+                        uint32_t world) {
+    const uint32_t t = blockIdx.x * blockDim.x + threadIdx.x;
+    if (t >= tokens) return;
+    uint8_t count[64];                           // routes of this token per destination so far
+    for (uint32_t g = 0; g < world; g++) count[g] = 0;
+    for (uint32_t r = 0; r < top_k; r++) {
+        const uint32_t route = t * top_k + r;
+        const uint32_t g = ids[route] / per;
+        const uint32_t j = count[g]++;
+        const uint64_t at = ((uint64_t)g * tokens + slot[(uint64_t)t * world + g]) * top_k + j;
+        unique_routes[at] = inv_perm[route] - offsets[g * per];
+        unique_weights[at] = weights[route];
+    }
+    for (uint32_t g = 0; g < world; g++) {
+        if (count[g] == 0) continue;
+        const uint64_t at = ((uint64_t)g * tokens + slot[(uint64_t)t * world + g]) * top_k;
+        for (uint32_t j = count[g]; j < top_k; j++) unique_routes[at + j] = 0xffffffffu;
+    }
+}
+
+// On the expert rank: partial[u] = bf16(sum_j w_j * rows_out[inverse[route_base(u) + pos_j]]), one
+// 64-thread group per unique row, 8 columns per thread and pass.
+__global__ void __launch_bounds__(256)
+ep_reduce_kernel(uint16_t *__restrict__ partial, const uint16_t *__restrict__ rows_out,
+                 const uint32_t *__restrict__ inverse, const uint32_t *__restrict__ routes_recv,
+                 const float *__restrict__ weights_recv, const uint32_t *__restrict__ source_first_row,
+                 const uint32_t *__restrict__ source_route_base, uint32_t world, uint32_t n_unique, uint32_t top_k,
+                 uint32_t hidden) {
+    const uint32_t groups = gridDim.x * (blockDim.x / 64u);
+    const uint32_t lane64 = threadIdx.x % 64u;
+    for (uint32_t u = blockIdx.x * (blockDim.x / 64u) + threadIdx.x / 64u; u < n_unique; u += groups) {
+        uint32_t src = 0;                                  // the source whose rows contain unique row u
+        while (src + 1u < world && source_first_row[src + 1u] <= u) src++;
+        const uint32_t base = source_route_base[src];
+        for (uint32_t c = lane64; c < hidden / 8u; c += 64u) {
+            float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+            for (uint32_t j = 0; j < top_k; j++) {
+                const uint32_t pos = routes_recv[(uint64_t)u * top_k + j];
+                if (pos == 0xffffffffu) break;
+                const float w = weights_recv[(uint64_t)u * top_k + j];
+                const uint4 q = reinterpret_cast<const uint4 *>(rows_out + (uint64_t)inverse[base + pos] * hidden)[c];
+                acc[0] = fmaf(w, bf16_lo(q.x), acc[0]); acc[1] = fmaf(w, bf16_hi(q.x), acc[1]);
+                acc[2] = fmaf(w, bf16_lo(q.y), acc[2]); acc[3] = fmaf(w, bf16_hi(q.y), acc[3]);
+                acc[4] = fmaf(w, bf16_lo(q.z), acc[4]); acc[5] = fmaf(w, bf16_hi(q.z), acc[5]);
+                acc[6] = fmaf(w, bf16_lo(q.w), acc[6]); acc[7] = fmaf(w, bf16_hi(q.w), acc[7]);
+            }
+            uint32_t o[4];
+#pragma unroll
+            for (int i = 0; i < 4; i++)
+                o[i] = (uint32_t)float_to_bf16_bits(acc[2 * i]) | ((uint32_t)float_to_bf16_bits(acc[2 * i + 1]) << 16);
+            reinterpret_cast<uint4 *>(partial + (uint64_t)u * hidden)[c] = make_uint4(o[0], o[1], o[2], o[3]);
+        }
+    }
+}
+
+// On the source: out[t] = bf16( bf16(sum over the token's destinations g, ascending, of
+// partial_home[g * tokens + slot[t, g]]) + shared[t] )
+__global__ void __launch_bounds__(256)
+ep_combine_partials_kernel(uint16_t *__restrict__ out, const uint16_t *__restrict__ partial_home,
+                           const unsigned long long *__restrict__ mask, const uint32_t *__restrict__ slot,
+                           const uint16_t *__restrict__ shared, uint32_t tokens, uint32_t world, uint32_t hidden) {
+    for (uint32_t t = blockIdx.x; t < tokens; t += gridDim.x) {
+        const unsigned long long m = mask[t];
+        for (uint32_t c = threadIdx.x; c < hidden / 8u; c += blockDim.x) {
+            float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+            for (uint32_t g = 0; g < world; g++) {
+                if (((m >> g) & 1ull) == 0ull) continue;
+                const uint64_t row = (uint64_t)g * tokens + slot[(uint64_t)t * world + g];
+                const uint4 q = reinterpret_cast<const uint4 *>(partial_home + row * hidden)[c];
+                acc[0] += bf16_lo(q.x); acc[1] += bf16_hi(q.x); acc[2] += bf16_lo(q.y); acc[3] += bf16_hi(q.y);
+                acc[4] += bf16_lo(q.z); acc[5] += bf16_hi(q.z); acc[6] += bf16_lo(q.w); acc[7] += bf16_hi(q.w);
+            }
+            float sh[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+            if (shared) {
+                const uint4 q = reinterpret_cast<const uint4 *>(shared + (uint64_t)t * hidden)[c];
+                sh[0] = bf16_lo(q.x); sh[1] = bf16_hi(q.x); sh[2] = bf16_lo(q.y); sh[3] = bf16_hi(q.y);
+                sh[4] = bf16_lo(q.z); sh[5] = bf16_hi(q.z); sh[6] = bf16_lo(q.w); sh[7] = bf16_hi(q.w);
+            }
+            uint32_t o[4];
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                uint32_t lo = float_to_bf16_bits(acc[2 * i]), hi = float_to_bf16_bits(acc[2 * i + 1]);
+                if (shared) {
+                    lo = float_to_bf16_bits(bf16_bits_to_float(lo) + sh[2 * i]);
+                    hi = float_to_bf16_bits(bf16_bits_to_float(hi) + sh[2 * i + 1]);
+                }
+                o[i] = lo | (hi << 16);
+            }
+            reinterpret_cast<uint4 *>(out + (uint64_t)t * hidden)[c] = make_uint4(o[0], o[1], o[2], o[3]);
+        }
+    }
+}
+
 }  // namespace
 
 struct k3_moe_ep {
@@ -194,6 +296,7 @@ struct k3_moe_ep {
                 t_end = nullptr;
     uint32_t last_recv_rows = 0;
     bool timed = false;
+    bool reduced_return = false;
     std::vector<uint32_t> send_rows, recv_rows, send_unique, recv_unique;
 };
 
@@ -223,6 +326,8 @@ struct EpWorkspace {
     unsigned long long *dest_mask;         // [tokens]
     uint32_t *slot, *token_list;           // [tokens, world], [world, tokens]
     uint32_t *route_slot, *slots_recv;     // [routes], [max_recv]
+    uint32_t *unique_routes, *routes_recv; // reduced return: [world * tokens, top_k] sent, [max_recv rows of top_k] received
+    float *unique_weights, *weights_recv;
     uint32_t *order, *inverse;             // [max_recv]
     uint16_t *rows_send, *rows_home;       // [routes, d]
     uint16_t *rows_recv, *rows_out, *rows_back;   // [max_recv, d]
@@ -259,12 +364,16 @@ EpWorkspace carve_ep(const k3_moe_layer_desc *d, uint32_t world, uint32_t tokens
     w.dispatch_bytes = k3_moe_dispatch_workspace_bytes(t1, d->top_k, d->expert_count);
     w.dispatch_ws = take(w.dispatch_bytes);
     w.offsets_all = (uint32_t *)take((size_t)world * (d->expert_count + 1u + world) * 4u);
-    w.tables = (uint32_t *)take(((size_t)3u * per * world + per + 1u + world) * 4u);
+    w.tables = (uint32_t *)take(((size_t)3u * per * world + per + 1u + 2u * world) * 4u);
     w.dest_mask = (unsigned long long *)take((size_t)t1 * 8u);
     w.slot = (uint32_t *)take((size_t)t1 * world * 4u);
     w.token_list = (uint32_t *)take((size_t)t1 * world * 4u);
     w.route_slot = (uint32_t *)take(routes * 4u);
     w.slots_recv = (uint32_t *)take((size_t)cap * 4u);
+    w.unique_routes = (uint32_t *)take((size_t)t1 * world * d->top_k * 4u);
+    w.unique_weights = (float *)take((size_t)t1 * world * d->top_k * 4u);
+    w.routes_recv = (uint32_t *)take((size_t)cap * 4u);          // at most max_recv / 1 unique rows x top_k ... see below
+    w.weights_recv = (float *)take((size_t)cap * 4u);
     w.order = (uint32_t *)take((size_t)cap * 4u);
     w.inverse = (uint32_t *)take((size_t)cap * 4u);
     w.rows_send = (uint16_t *)take((size_t)t1 * world * d->hidden * 2u);       // one region of t1 rows per destination
@@ -367,7 +476,7 @@ extern "C" bool k3_moe_ep_create(k3_moe_ep **out, const void *id_bytes, int rank
     ep->send_unique.resize(world);
     ep->recv_unique.resize(world);
     // every rank's offsets, then the plan tables of the largest shard
-    ep->pinned_words = (size_t)world * (kMaxExpertsEp + 1u + kMaxWorld) + (size_t)3u * kMaxExpertsEp + kMaxExpertsEp + 1u + kMaxWorld;
+    ep->pinned_words = (size_t)world * (kMaxExpertsEp + 1u + kMaxWorld) + (size_t)3u * kMaxExpertsEp + kMaxExpertsEp + 1u + 2u * kMaxWorld;
     bool ok = cudaHostAlloc((void **)&ep->pinned, ep->pinned_words * 4u, cudaHostAllocDefault) == cudaSuccess;
     for (cudaEvent_t *e : {&ep->t_begin, &ep->t_experts0, &ep->t_experts1, &ep->t_end}) {
         ok = ok && cudaEventCreate(e) == cudaSuccess;
@@ -409,6 +518,12 @@ extern "C" void k3_moe_ep_destroy(k3_moe_ep *ep) {
     }
     if (ep->side) (void)cudaStreamDestroy(ep->side);
     delete ep;
+}
+
+extern "C" bool k3_moe_ep_set_reduced_return(k3_moe_ep *ep, bool reduced) {
+    if (!ep) return false;
+    ep->reduced_return = reduced;
+    return true;
 }
 
 extern "C" int k3_moe_ep_rank(const k3_moe_ep *ep) { return ep ? ep->rank : -1; }
@@ -540,6 +655,10 @@ extern "C" bool k3_moe_ep_layer_forward(k3_moe_ep *ep, const k3_moe_layer_desc *
                                             world, H / 8u);
         ep_route_slot_kernel<<<(routes + 255u) / 256u, 256, 0, stream>>>(w.route_slot, w.slot, w.sorted_route,
                                                                          w.sorted_token, w.ids, routes, per, world);
+        if (ep->reduced_return) {
+            ep_unique_routes_kernel<<<(tokens + 255u) / 256u, 256, 0, stream>>>(
+                w.unique_routes, w.unique_weights, w.ids, w.weights, w.inv_perm, w.offsets, w.slot, tokens, k, per, world);
+        }
         if (!launch_ok()) return fail("row gather failed");
         // the shared expert depends only on the local tokens: on the handle's second stream it
         // runs beside the exchange (whose kernels take a few SMs) and is joined before the combine
@@ -559,18 +678,22 @@ extern "C" bool k3_moe_ep_layer_forward(k3_moe_ep *ep, const k3_moe_layer_desc *
     uint32_t *plan = ep->pinned + (size_t)world * (kMaxExpertsEp + 1u + kMaxWorld);
     uint32_t *block_recv_start = plan, *block_dest_start = plan + (size_t)per * world,
              *block_rows = plan + (size_t)2u * per * world, *offsets_local = plan + (size_t)3u * per * world,
-             *source_first_row = offsets_local + per + 1u;
+             *source_first_row = offsets_local + per + 1u, *source_route_base = source_first_row + world;
     if (!plan_impl(host_offsets, stride, world, rank, E, ep->send_rows.data(), ep->recv_rows.data(), block_recv_start,
                    block_dest_start, block_rows, offsets_local)) {
         return fail("exchange plan failed");
     }
-    uint32_t n_unique = 0;
+    uint32_t n_unique = 0, n_routes_before = 0;
     for (uint32_t g = 0; g < world; g++) {
         ep->send_unique[g] = host_offsets[(size_t)rank * stride + E + 1u + g];
         ep->recv_unique[g] = host_offsets[(size_t)g * stride + E + 1u + rank];
         source_first_row[g] = n_unique;
+        source_route_base[g] = n_routes_before;
         n_unique += ep->recv_unique[g];
+        n_routes_before += ep->recv_rows[g];
     }
+    const bool reduced = ep->reduced_return;
+    if (reduced && (size_t)n_unique * k > (size_t)max_recv) return fail("workspace too small for the reduced return");
     const uint32_t n_recv = offsets_local[per];
     ep->last_recv_rows = n_recv;
     if (n_recv > max_recv) {
@@ -579,7 +702,7 @@ extern "C" bool k3_moe_ep_layer_forward(k3_moe_ep *ep, const k3_moe_layer_desc *
                  max_recv);
         return fail(text);
     }
-    const size_t table_words = (size_t)3u * per * world + per + 1u + world;
+    const size_t table_words = (size_t)3u * per * world + per + 1u + 2u * world;
     if (cudaMemcpyAsync(w.tables, plan, table_words * 4u, cudaMemcpyHostToDevice, stream) != cudaSuccess) {
         return fail("plan upload failed");
     }
@@ -603,11 +726,27 @@ extern "C" bool k3_moe_ep_layer_forward(k3_moe_ep *ep, const k3_moe_layer_desc *
                                                 stream), error, error_size, "dispatch send of the slots"))) {
                     return false;
                 }
+                if (reduced && ep->send_unique[g] != 0 &&
+                    (!nccl_ok(ep, ep->api->Send(w.unique_routes + (size_t)g * std::max(tokens, 1u) * k,
+                                                (size_t)ep->send_unique[g] * k, ncclUint32, (int)g, ep->comm, stream), error,
+                              error_size, "dispatch send of the route lists") ||
+                     !nccl_ok(ep, ep->api->Send(w.unique_weights + (size_t)g * std::max(tokens, 1u) * k,
+                                                (size_t)ep->send_unique[g] * k, ncclUint32, (int)g, ep->comm, stream), error,
+                              error_size, "dispatch send of the route weights"))) {
+                    return false;
+                }
                 if (ep->recv_unique[g] != 0 &&
                     (!nccl_ok(ep, ep->api->Recv(w.rows_recv + roff_rows * H, (size_t)ep->recv_unique[g] * H, ncclBfloat16,
                                                 (int)g, ep->comm, stream), error, error_size, "dispatch recv") ||
                      !nccl_ok(ep, ep->api->Recv(w.slots_recv + roff_routes, ep->recv_rows[g], ncclUint32, (int)g, ep->comm,
                                                 stream), error, error_size, "dispatch recv of the slots"))) {
+                    return false;
+                }
+                if (reduced && ep->recv_unique[g] != 0 &&
+                    (!nccl_ok(ep, ep->api->Recv(w.routes_recv + roff_rows * k, (size_t)ep->recv_unique[g] * k, ncclUint32,
+                                                (int)g, ep->comm, stream), error, error_size, "dispatch recv of the route lists") ||
+                     !nccl_ok(ep, ep->api->Recv(w.weights_recv + roff_rows * k, (size_t)ep->recv_unique[g] * k, ncclUint32,
+                                                (int)g, ep->comm, stream), error, error_size, "dispatch recv of the route weights"))) {
                     return false;
                 }
             }
@@ -622,6 +761,13 @@ extern "C" bool k3_moe_ep_layer_forward(k3_moe_ep *ep, const k3_moe_layer_desc *
              cudaMemcpyAsync(w.slots_recv + self_routes_r, w.route_slot + self_routes_s, (size_t)ep->send_rows[rank] * 4u,
                              cudaMemcpyDeviceToDevice, stream) != cudaSuccess)) {
             return fail("copy of the rank's own rows failed");
+        }
+        if (reduced && ep->send_unique[rank] != 0 &&
+            (cudaMemcpyAsync(w.routes_recv + self_rows * k, w.unique_routes + (size_t)rank * std::max(tokens, 1u) * k,
+                             (size_t)ep->send_unique[rank] * k * 4u, cudaMemcpyDeviceToDevice, stream) != cudaSuccess ||
+             cudaMemcpyAsync(w.weights_recv + self_rows * k, w.unique_weights + (size_t)rank * std::max(tokens, 1u) * k,
+                             (size_t)ep->send_unique[rank] * k * 4u, cudaMemcpyDeviceToDevice, stream) != cudaSuccess)) {
+            return fail("copy of the rank's own route lists failed");
         }
     }
 
@@ -649,12 +795,44 @@ extern "C" bool k3_moe_ep_layer_forward(k3_moe_ep *ep, const k3_moe_layer_desc *
         }
         if (cudaEventRecord(ep->t_experts1, stream) != cudaSuccess) return fail("event record failed");
         ep->timed = true;
-        // 7. back into received order, and home (one row per route: the combine stays exact)
-        if (!k3_rocm_gather_rows_bf16(w.rows_back, w.rows_out, w.inverse, n_recv, H, stream)) {
+        // 7. back into received order, and home (one row per route: the combine stays exact) -
+        // or, in the reduced mode, one weighted partial sum per (token, this rank)
+        if (reduced) {
+            ep_reduce_kernel<<<std::min<uint32_t>((n_unique + 3u) / 4u, (uint32_t)sm_count() * 8u), 256, 0, stream>>>(
+                w.rows_back, w.rows_out, w.inverse, w.routes_recv, w.weights_recv, offsets_local_dev + per + 1u,
+                offsets_local_dev + per + 1u + world, world, n_unique, k, H);
+            if (!launch_ok()) return fail("partial sum kernel failed");
+        } else if (!k3_rocm_gather_rows_bf16(w.rows_back, w.rows_out, w.inverse, n_recv, H, stream)) {
             return fail("return gather failed");
         }
     }
-    {
+    if (reduced) {
+        // partial rows go home into the regions the token rows were sent from (same slots)
+        size_t soff = 0;
+        if (world > 1 && !nccl_ok(ep, ep->api->GroupStart(), error, error_size, "ncclGroupStart")) return false;
+        for (uint32_t g = 0; g < world; g++) {
+            uint16_t *region = w.rows_send + (size_t)g * std::max(tokens, 1u) * H;
+            if (g != rank) {
+                if (ep->recv_unique[g] != 0 &&
+                    !nccl_ok(ep, ep->api->Send(w.rows_back + soff * H, (size_t)ep->recv_unique[g] * H, ncclBfloat16, (int)g,
+                                               ep->comm, stream), error, error_size, "return send")) {
+                    return false;
+                }
+                if (ep->send_unique[g] != 0 &&
+                    !nccl_ok(ep, ep->api->Recv(region, (size_t)ep->send_unique[g] * H, ncclBfloat16, (int)g, ep->comm, stream),
+                             error, error_size, "return recv")) {
+                    return false;
+                }
+            }
+            soff += ep->recv_unique[g];
+        }
+        if (world > 1 && !nccl_ok(ep, ep->api->GroupEnd(), error, error_size, "ncclGroupEnd")) return false;
+        if (ep->send_unique[rank] != 0 &&
+            cudaMemcpyAsync(w.rows_send + (size_t)rank * std::max(tokens, 1u) * H, w.rows_back + (size_t)source_first_row[rank] * H,
+                            (size_t)ep->send_unique[rank] * H * 2u, cudaMemcpyDeviceToDevice, stream) != cudaSuccess) {
+            return fail("copy of the rank's own rows failed");
+        }
+    } else {
         size_t soff = 0, roff = 0, self_soff = 0, self_roff = 0;
         if (world > 1 && !nccl_ok(ep, ep->api->GroupStart(), error, error_size, "ncclGroupStart")) return false;
         for (uint32_t g = 0; g < world; g++) {
@@ -687,8 +865,12 @@ extern "C" bool k3_moe_ep_layer_forward(k3_moe_ep *ep, const k3_moe_layer_desc *
     // 8. combine in rank order on the token's own rank
     if (tokens != 0) {
         if (d->shared_hidden && cudaStreamWaitEvent(stream, ep->join, 0) != cudaSuccess) return fail("stream join failed");
-        if (!k3_moe_combine(out, w.rows_home, w.inv_perm, w.weights, d->shared_hidden ? w.sh_out : nullptr, tokens, k,
-                            H, stream)) {
+        if (reduced) {
+            ep_combine_partials_kernel<<<std::min<uint32_t>(tokens, (uint32_t)sm_count() * 8u), 256, 0, stream>>>(
+                (uint16_t *)out, w.rows_send, w.dest_mask, w.slot, d->shared_hidden ? w.sh_out : nullptr, tokens, world, H);
+            if (!launch_ok()) return fail("combine failed");
+        } else if (!k3_moe_combine(out, w.rows_home, w.inv_perm, w.weights, d->shared_hidden ? w.sh_out : nullptr,
+                                   tokens, k, H, stream)) {
             return fail("combine failed");
         }
         if (ids_out && cudaMemcpyAsync(ids_out, w.ids, (size_t)routes * 4u, cudaMemcpyDefault, stream) != cudaSuccess)

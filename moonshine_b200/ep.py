@@ -369,9 +369,14 @@ class ExpertParallelLayer:
     to the other ranks.  ``pieces`` > 1 selects the Python-driven pipelined form instead
     (``ep_forward_pipelined``; same results, kept for comparison)."""
 
-    def __init__(self, cfg: dict, seed: int, device, tokens: int, weights: dict | None = None, pieces: int = 1):
+    def __init__(self, cfg: dict, seed: int, device, tokens: int, weights: dict | None = None, pieces: int = 1,
+                 reduced_return: bool = False):
+        """``reduced_return``: the expert ranks return one weighted partial sum per (token, rank)
+        instead of every expert row (``k3_moe_ep_set_reduced_return``): fewer bytes, results
+        within the layer tolerance of the exact mode instead of bit-identical."""
         import ctypes as C
         self.world, self.rank = dist.get_world_size(), dist.get_rank()
+        self.reduced_return = bool(reduced_return)
         if tokens % self.world != 0:
             raise ValueError("token count must divide evenly over the ranks")
         self.cfg = dict(cfg)
@@ -397,6 +402,8 @@ class ExpertParallelLayer:
             if not ops.k3_moe_ep_create(C.byref(handle), C.addressof(ident_host), self.rank, self.world, err, 256):
                 raise RuntimeError("k3_moe_ep_create: " + err.value.decode())
         self.handle = handle
+        if not ops.k3_moe_ep_set_reduced_return(self.handle, self.reduced_return):
+            raise RuntimeError("k3_moe_ep_set_reduced_return failed")
         # every route of the batch may land on one rank: the sure bound
         self.max_recv = tokens * cfg["top_k"]
         need = ops.k3_moe_ep_workspace_bytes(self.handle, self.layer.desc, self.local_tokens, self.max_recv)

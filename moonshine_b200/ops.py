@@ -40,7 +40,7 @@ def _make(name, restype, argtypes):
         fn = getattr(_native.lib(), name)
         has_stream = (len(argtypes) > 0 and argtypes[-1] is C.c_void_p
                       and not name.startswith(("k3_moe_event_", "k3_moe_device_status", "k3_moe_ep_destroy",
-                                                   "k3_moe_ep_rank", "k3_moe_ep_world")))
+                                                   "k3_moe_ep_rank", "k3_moe_ep_world", "k3_moe_ep_set_reduced_return")))
         has_stream = has_stream and len(argtypes) > 0
         n_user = len(argtypes) - (1 if has_stream else 0)
         if len(args) == len(argtypes) and has_stream:      # stream passed positionally
