@@ -278,10 +278,10 @@ def run_config(args, cfg, tokens, world):
 
 
 # DRAM bytes per launch measured with ncu on these workloads (one-pass metrics,
-# summary kept under profiles/): prefill = gate/up (28.81 GB) + down (11.73 GB)
-# launches of the grouped expert phase; decode = the five kernels of one token.
-PREFILL_TRAFFIC_BYTES = 40.54e9
-DECODE_TRAFFIC_BYTES = 435.6e6
+# summary kept under profiles/): prefill = gate/up (16.70 GB) + down (9.39 GB)
+# launches of the grouped expert phase; decode = the four kernels of one token.
+PREFILL_TRAFFIC_BYTES = 26.09e9
+DECODE_TRAFFIC_BYTES = 434.9e6
 
 
 # --------------------------------------------------------------- native arm
