@@ -137,4 +137,24 @@ inline bool set_max_dynamic_smem(const void *kernel, size_t bytes) {
     return true;
 }
 
+// Kernels meant to share an SM with a kernel that needs most of its shared memory must
+// ask for the same split between L1 and shared memory: an SM changes the split only when
+// it is empty, so a block with a smaller preference waits for the large kernel to leave
+// (and the other way round).  Sets the preference to the maximum once per (device, kernel).
+inline bool prefer_max_shared_carveout(const void *kernel) {
+    static std::mutex lock;
+    static std::map<std::pair<int, const void *>, bool> done;
+    const int dev = current_device();
+    std::lock_guard<std::mutex> guard(lock);
+    const auto key = std::make_pair(dev, kernel);
+    if (done.count(key)) return true;
+    if (cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout,
+                             (int)cudaSharedmemCarveoutMaxShared) != cudaSuccess) {
+        (void)cudaGetLastError();
+        return false;
+    }
+    done[key] = true;
+    return true;
+}
+
 }  // namespace k3

@@ -63,10 +63,13 @@ struct DecodeArgs {
     float *route_words;       // front: [2][1024] scores and choices written by the row tasks, or null
     unsigned int *ticket;     // front: completion counter of this call
     uint32_t *control;        // front: words the expert kernel needs zeroed (64), or null
+    uint32_t *front_done;     // router kernel: count of finished blocks for the expert kernel, or null
+    uint32_t rows_in_flight;  // router kernel: rows a block fetches at once (<= kRouterRowsInFlight)
     uint32_t route_elsewhere; // front: only the row tasks; the expert kernel routes from the scores
     uint32_t shared_elsewhere;  // front: the shared expert runs in its own kernels (side stream)
     DecodeTail tail;            // shared down: its share of the layer's tail (tail.out null: none)
 };
+
 
 // ------------------------------------------------------------------- front
 // Tickets of the "last block finishes the job" step of the front kernel.  A call
@@ -305,6 +308,123 @@ decode_front_kernel(DecodeArgs a) {
     }
 }
 
+// ------------------------------------------------------------ router rows
+// Front kernel of the block-scaled path: router rows and the token's E2M1 terms, nothing
+// else (the expert kernel routes, the shared expert has its own kernels).  A block owns
+// rows b, b + G, b + 2G, b + 3G of a grid of G blocks and has all of them in flight at
+// once (16-byte asynchronous copies into shared memory, no registers held), so the whole
+// router table is requested in the kernel's first microsecond.  The arithmetic is the
+// reference's: thread v sums columns v, v + 256, ... in order, then the 256-lane tree.
+constexpr uint32_t kRouterRowsInFlight = 6;      // at most; a launch asks for what its grid needs
+
+K3_DEVINL void cp_async_16(void *dst_shared, const void *src_global) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(dst_shared)),
+                 "l"(src_global)
+                 : "memory");
+}
+
+__global__ void __launch_bounds__(256, 2)
+decode_router_kernel(DecodeArgs a) {
+    extern __shared__ __align__(16) unsigned char router_smem[];
+    const uint32_t E = a.d.expert_count, H = a.d.hidden, G = gridDim.x;
+    float *xf = reinterpret_cast<float *>(router_smem);                                    // [H] fp32
+    uint16_t *rows = reinterpret_cast<uint16_t *>(router_smem + (size_t)H * 4u);          // [4][H] bf16
+    __shared__ float red[kRouterRowsInFlight][kRowBlock];
+    const uint32_t warp = threadIdx.x / kWarp, lane = threadIdx.x % kWarp;
+    if (blockIdx.x == 0 && a.control != nullptr && threadIdx.x < 64u) a.control[threadIdx.x] = 0u;
+    // the expert kernel, queued behind this one with programmatic serialization, may take
+    // its places as soon as every block of this grid has started
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    const uint16_t *table = (const uint16_t *)a.d.router_weight;
+    bool staged = false;
+    const uint32_t batch = a.rows_in_flight;
+    for (uint32_t first = blockIdx.x; first < E; first += batch * G) {
+#pragma unroll
+        for (uint32_t j = 0; j < kRouterRowsInFlight; j++) {
+            const uint32_t row = first + j * G;
+            if (j < batch && row < E) {
+                for (uint32_t c = threadIdx.x; c < H / 8u; c += blockDim.x)
+                    cp_async_16(rows + (size_t)j * H + 8u * c, table + (uint64_t)row * H + 8u * c);
+            }
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+        if (!staged) {
+            // the token as fp32, loaded while the rows travel
+            for (uint32_t i = threadIdx.x; i < H / 8u; i += blockDim.x) {
+                const uint4 v = __ldg(reinterpret_cast<const uint4 *>(a.x) + i);
+                float4 *dst = reinterpret_cast<float4 *>(xf + 8u * i);
+                dst[0] = make_float4(__uint_as_float(v.x << 16), __uint_as_float(v.x & 0xffff0000u),
+                                     __uint_as_float(v.y << 16), __uint_as_float(v.y & 0xffff0000u));
+                dst[1] = make_float4(__uint_as_float(v.z << 16), __uint_as_float(v.z & 0xffff0000u),
+                                     __uint_as_float(v.w << 16), __uint_as_float(v.w & 0xffff0000u));
+            }
+            staged = true;
+        }
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
+        __syncthreads();
+#pragma unroll
+        for (uint32_t j = 0; j < kRouterRowsInFlight; j++) {
+            if (j < batch && first + j * G < E) {
+                const uint16_t *wr = rows + (size_t)j * H;
+                float sum = 0.f;
+                for (uint32_t c = threadIdx.x; c < H; c += 256u) sum = fmaf(bf16_bits_to_float(wr[c]), xf[c], sum);
+                red[j][threadIdx.x] = sum;
+            }
+        }
+        __syncthreads();
+        if (warp < batch && first + warp * G < E) {
+            // the tree of block_tree_256, one warp per row
+            const uint32_t row = first + warp * G;
+            const float *r = red[warp];
+            float a0 = r[lane] + r[lane + 128u], a1 = r[lane + 32u] + r[lane + 160u];
+            float a2 = r[lane + 64u] + r[lane + 192u], a3 = r[lane + 96u] + r[lane + 224u];
+            a0 += a2; a1 += a3;
+            float v = a0 + a1;
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) v += __shfl_down_sync(0xffffffffu, v, o);
+            if (lane == 0) {
+                a.logits[row] = v;
+                const float sc = sigmoid_exact(v);
+                a.route_words[row] = sc;
+                a.route_words[1024u + row] = sc + __ldg((const float *)a.d.router_bias + row);
+            }
+        }
+        __syncthreads();            // `rows` and `red` are reused by the next batch
+    }
+    if (!staged) {
+        for (uint32_t i = threadIdx.x; i < H; i += blockDim.x) xf[i] = bf16_bits_to_float(a.x[i]);
+        __syncthreads();
+    }
+    // the token's E2M1 terms: 32-column blocks, one per warp, taken from the far end of the
+    // grid (the blocks there own one row fewer)
+    const uint32_t split_tasks = (H / 32u + 7u) / 8u;
+    for (uint32_t task = G - 1u - blockIdx.x; task < split_tasks; task += G) {
+        const uint32_t blk = task * 8u + warp;
+        if (blk < H / 32u) {
+            uint32_t code[kTerms], sbyte[kTerms];
+            split_block_e2m1(xf[blk * 32u + lane], code, sbyte);
+            store_block_e2m1(a.x_terms, a.x_sf, H / 2u, H / 32u, blk, code, sbyte, lane);
+        }
+    }
+    if (a.front_done != nullptr) {
+        // everything this block wrote is in memory before its count
+        __threadfence();
+        __syncthreads();
+        if (threadIdx.x == 0) atomicAdd(a.front_done, 1u);
+    }
+}
+
+// ------------------------------------------------------------------ tail
+// The layer's tail as a kernel of its own, queued behind the expert kernel with programmatic
+// serialization: its blocks take their places while the experts stream and wait for the
+// grids in front (the expert kernel, and through it the shared expert's) to finish.
+__global__ void __launch_bounds__(128)
+decode_tail_kernel(DecodeTail t) {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    const uint32_t group = blockIdx.x * 4u + threadIdx.x / kWarp;
+    if (group * 32u < t.hidden) tail_columns(t, group, threadIdx.x % kWarp);
+}
+
 // ------------------------------------------------------- persistent experts
 struct Prefetched {
     uint4 wa, wb;
@@ -477,7 +597,7 @@ decode_down_kernel(DecodeArgs a) {
 // kernels run on a side stream next to the front and expert kernels.
 
 // gate and up rows: one 256-thread block per 16 rows, K split over the 8 warps
-__global__ void __launch_bounds__(256, 2)
+__global__ void __maxnreg__(120)
 decode_shared_gateup_kernel(DecodeArgs a) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     __half *xh = reinterpret_cast<__half *>(smem_raw);                       // [hidden] f16, rescaled
@@ -673,12 +793,23 @@ bool k3_decode_layer(const k3_moe_layer_desc *d, const void *x, void *logits, vo
         }
     }
     a.ticket = tickets + next_ticket.fetch_add(1u) % kTicketSlots;
-    // Block-scaled path: the shared expert runs on a side stream next to everything
-    // that depends on the routing.  With every expert in this table there is no
-    // combine launch either: the down kernel's epilogue warps and the shared-down
-    // blocks count arrivals per 32 output columns and the last one adds them up.
-    const bool fused_tail = combine && mx && d->local_expert_first == 0u &&
+    // rows by 16-byte copies: the table and the token 16-byte aligned, whole 16-byte chunks per row
+    const bool router_kernel = mx && d->shared_hidden != 0 && d->hidden % 8u == 0 &&
+                               ((((uintptr_t)d->router_weight) | ((uintptr_t)x)) & 15u) == 0;
+    // The shared expert depends only on the token.  Main form (ring path): a ring kernel on a
+    // few SMs (k3_decode_shared.cu), all on the caller's stream: ring kernel (lets its
+    // successors start at once) -> router kernel (programmatic launch, never waits for the ring
+    // kernel, counts its finished blocks) -> expert kernel (programmatic launch, waits for that
+    // count) -> tail kernel (programmatic launch, waits for everything in front).  Other
+    // shapes: two row kernels on a low-priority side stream, and with every expert in this
+    // table no tail launch - the down epilogue warps and the shared-down blocks count arrivals
+    // per 32 output columns and the last one adds them up.
+    const bool ring = router_kernel && k3_decode_shared_ring_supported(d) &&
+                      ((((uintptr_t)sh_gate) | ((uintptr_t)sh_up)) & 15u) == 0;
+    const bool whole_tail = combine && mx && d->local_expert_first == 0u &&
                             d->local_expert_count == d->expert_count && d->hidden % 32u == 0u;
+    const bool tail_kernel = ring && whole_tail;
+    const bool fused_tail = whole_tail && !ring;
     static std::atomic<uint32_t> tail_epoch{1};
     if (fused_tail) {
         a.tail.out = (uint16_t *)out;
@@ -692,13 +823,22 @@ bool k3_decode_layer(const k3_moe_layer_desc *d, const void *x, void *logits, vo
         a.tail.ranks = d->top_k;
         a.tail.hidden = d->hidden;
     }
+    uint32_t ring_ctas = 0;
+    if (ring) {
+        a.front_done = (uint32_t *)k3_decode_mx_front_done_word(d, scratch);
+        if (!k3_decode_shared_ring(d, x, sh_gate, sh_up, sh_out, a.front_done, stream)) {
+            return false;
+        }
+        ring_ctas = k3_decode_shared_ring_ctas();
+    }
     SideStream *side = nullptr;
-    if (mx && d->shared_hidden != 0) {
+    if (mx && d->shared_hidden != 0 && !ring) {
         side = side_stream();
         if (!side) return false;
         a.shared_elsewhere = 1u;
         // the side stream may start once everything queued before this call is done
-        if (cudaEventRecord(side->fork, stream) != cudaSuccess) {
+        if (cudaEventRecord(side->fork, stream) != cudaSuccess ||
+            cudaStreamWaitEvent(side->stream, side->fork, 0) != cudaSuccess) {
             (void)cudaGetLastError();
             return false;
         }
@@ -709,17 +849,16 @@ bool k3_decode_layer(const k3_moe_layer_desc *d, const void *x, void *logits, vo
     // second stays zero).  Without them four blocks fit on an SM and the grid is one wave.
     const size_t front_smem = (size_t)d->hidden * (side ? 4u : 8u);
     auto launch_side = [&]() -> bool {
-        if (cudaStreamWaitEvent(side->stream, side->fork, 0) != cudaSuccess) {
-            (void)cudaGetLastError();
-            return false;
-        }
         const size_t gu_smem = (size_t)d->hidden * 2u;
         const size_t dn_smem = (size_t)d->shared_hidden * 6u;
         if (!set_max_dynamic_smem((const void *)decode_shared_gateup_kernel, gu_smem) ||
-            !set_max_dynamic_smem((const void *)decode_shared_down_kernel, dn_smem)) {
+            !set_max_dynamic_smem((const void *)decode_shared_down_kernel, dn_smem) ||
+            !prefer_max_shared_carveout((const void *)decode_shared_gateup_kernel) ||
+            !prefer_max_shared_carveout((const void *)decode_shared_down_kernel)) {
             return false;
         }
-        decode_shared_gateup_kernel<<<2u * d->shared_hidden / 16u, 256, gu_smem, side->stream>>>(a);
+        decode_shared_gateup_kernel<<<std::min<uint32_t>(2u * d->shared_hidden / 16u, (uint32_t)sms), 256, gu_smem,
+                                      side->stream>>>(a);
         decode_shared_down_kernel<<<d->hidden / 16u, 128, dn_smem, side->stream>>>(a);
         if (!launch_ok() || cudaEventRecord(side->join, side->stream) != cudaSuccess) {
             (void)cudaGetLastError();
@@ -727,8 +866,41 @@ bool k3_decode_layer(const k3_moe_layer_desc *d, const void *x, void *logits, vo
         }
         return true;
     };
-    if (side) {
-        if (!set_max_dynamic_smem((const void *)decode_front_kernel<false>, front_smem)) return false;
+    uint32_t router_blocks = 0;
+    if (router_kernel) {
+        // two blocks on every SM the ring kernel leaves free, each with as many rows in flight
+        // as one pass over the table needs (fewer, and more passes, if shared memory says so)
+        const uint32_t grid = std::min<uint32_t>(d->expert_count, ((uint32_t)sms - ring_ctas) * 2u);
+        uint32_t batch = std::min<uint32_t>((d->expert_count + grid - 1u) / grid, kRouterRowsInFlight);
+        while (batch > 1u && (size_t)d->hidden * (4u + 2u * batch) + 8u * 1024u > 113u * 1024u) batch--;
+        a.rows_in_flight = batch;
+        const size_t smem = (size_t)d->hidden * (4u + 2u * batch);
+        if (!set_max_dynamic_smem((const void *)decode_router_kernel, smem) ||
+            !prefer_max_shared_carveout((const void *)decode_router_kernel)) {
+            return false;
+        }
+        // behind the ring kernel with programmatic serialization and without waiting for it
+        // (nothing here reads its results)
+        cudaLaunchConfig_t config{};
+        config.gridDim = dim3(grid);
+        config.blockDim = dim3(256);
+        config.dynamicSmemBytes = smem;
+        config.stream = stream;
+        cudaLaunchAttribute attribute{};
+        attribute.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attribute.val.programmaticStreamSerializationAllowed = 1;
+        config.attrs = &attribute;
+        config.numAttrs = ring ? 1u : 0u;
+        router_blocks = config.gridDim.x;
+        if (cudaLaunchKernelEx(&config, decode_router_kernel, a) != cudaSuccess) {
+            (void)cudaGetLastError();
+            return false;
+        }
+    } else if (side) {
+        if (!set_max_dynamic_smem((const void *)decode_front_kernel<false>, front_smem) ||
+            !prefer_max_shared_carveout((const void *)decode_front_kernel<false>)) {
+            return false;
+        }
         decode_front_kernel<false><<<std::min<uint32_t>(front_tasks, (uint32_t)sms * 4u - 1u) + (mx ? 0u : 1u), 256,
                                      front_smem, stream>>>(a);
     } else {
@@ -744,7 +916,7 @@ bool k3_decode_layer(const k3_moe_layer_desc *d, const void *x, void *logits, vo
     if (mx) {
         k3_decode_tail tail{out, weights, a.tail.shared, residual, a.tail.epoch, a.tail.expected};
         if (!k3_decode_mx_experts(d, ids, weights, a.route_words, act, rows_out, scratch, events ? events[3] : nullptr,
-                                  fused_tail ? &tail : nullptr, stream) ||
+                                  fused_tail ? &tail : nullptr, ring ? router_blocks : 0u, stream) ||
             !mark(4)) {
             return false;
         }
@@ -754,6 +926,30 @@ bool k3_decode_layer(const k3_moe_layer_desc *d, const void *x, void *logits, vo
             return false;
         }
         if (fused_tail || !combine) return true;
+        if (tail_kernel) {
+            DecodeTail t{};
+            t.out = (uint16_t *)out;
+            t.rows = (const uint16_t *)rows_out;
+            t.weights = (const float *)weights;
+            t.shared = (const uint16_t *)sh_out;
+            t.residual = (const uint16_t *)residual;
+            t.ranks = d->top_k;
+            t.hidden = d->hidden;
+            cudaLaunchConfig_t config{};
+            config.gridDim = dim3((d->hidden / 32u + 3u) / 4u);
+            config.blockDim = dim3(128);
+            config.stream = stream;
+            cudaLaunchAttribute attribute{};
+            attribute.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+            attribute.val.programmaticStreamSerializationAllowed = 1;
+            config.attrs = &attribute;
+            config.numAttrs = 1u;
+            if (cudaLaunchKernelEx(&config, decode_tail_kernel, t) != cudaSuccess) {
+                (void)cudaGetLastError();
+                return false;
+            }
+            return true;
+        }
         return k3_moe_combine_residual(out, rows_out, nullptr, weights, d->shared_hidden ? sh_out : nullptr,
                                        residual, 1u, d->top_k, d->hidden, stream);
     }

@@ -126,6 +126,8 @@ struct MxArgs {
     uint8_t *act_terms;         // E2M1 terms of the activation [ranks * kTerms, I / 2]
     uint8_t *act_sf;            // and their block scales [ranks * kTerms, I / 32]
     uint32_t *control;          // kControlWords words, zero at launch
+    const uint32_t *front_done; // blocks of the front kernel that have finished, or null
+    uint32_t front_blocks;      // its grid size
     DecodeTail tail;            // the layer's tail, run by the D epilogues (tail.out null: none)
 };
 
@@ -168,6 +170,7 @@ K3_DEVINL uint64_t make_desc_sw128_split(uint32_t first, uint32_t second) {
     return d;
 }
 
+
 K3_DEVINL void fence_proxy_async_global() { asm volatile("fence.proxy.async.global;" ::: "memory"); }
 
 K3_DEVINL uint32_t ld_acquire(const uint32_t *p) {
@@ -178,7 +181,7 @@ K3_DEVINL uint32_t ld_acquire(const uint32_t *p) {
 
 // (72 registers: a 256-thread block of the shared expert's kernels, which run beside this
 // one on another stream, still fits in the register file of the SM)
-__global__ void __maxnreg__(72)
+__global__ void __maxnreg__(64)
 decode_experts_kernel(const __grid_constant__ MxMaps maps, MxArgs a) {
     extern __shared__ unsigned char smem_raw[];
     unsigned char *base = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
@@ -242,21 +245,43 @@ decode_experts_kernel(const __grid_constant__ MxMaps maps, MxArgs a) {
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = *tmem_slot;
+    // a kernel queued behind this one with programmatic serialization (the layer's tail) may
+    // take its places now; it waits for this grid to finish before it reads anything
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
     // Everything above needed nothing from the front kernel; what follows does (scores,
     // token terms, cleared control words).
-    asm volatile("griddepcontrol.wait;" ::: "memory");
+    if (a.front_done == nullptr) {
+        asm volatile("griddepcontrol.wait;" ::: "memory");
+    } else {
+        // Waiting for the grid in front would also wait for the grid in front of that one
+        // (the shared expert's, which runs until the layer's end).  The front kernel's blocks
+        // are all resident by the time this grid was allowed to start, so their count of
+        // finished blocks is waited for instead.
+        if (threadIdx.x == 0) {
+            const unsigned long long t0 = global_timer_ns();
+            uint32_t spins = 0;
+            while (ld_acquire(a.front_done) < a.front_blocks) {
+                if ((++spins & 63u) == 0u && global_timer_ns() - t0 > kWaitLimitNs) {
+                    *abort_flag = 1u;
+                    break;
+                }
+            }
+            fence_proxy_async_global();          // the token's terms are read by bulk copies
+        }
+        __syncthreads();
+    }
     if (a.route_words != nullptr) {
         // every CTA routes the token itself (the ring is still free: it serves as scratch)
         RouteScratch &rs = *reinterpret_cast<RouteScratch *>(base + lay.ring);
         route_topk_block(rs, ids_s, weights_s, a.route_words, a.experts, a.ranks, a.route_scale);
-        // the same values from every CTA: whoever reads them later (the tail, the caller)
-        // is ordered behind at least one of these stores
+        // the same values from every CTA; whoever reads them later is ordered behind at least
+        // one of these stores (the kernel's end, or the fence in front of a tail arrival of
+        // the CTA whose epilogue completes the count)
         if (threadIdx.x < a.ranks) {
             a.ids[threadIdx.x] = ids_s[threadIdx.x];
             a.weights[threadIdx.x] = weights_s[threadIdx.x];
         }
-        __threadfence();
     } else if (threadIdx.x < a.ranks) {
         ids_s[threadIdx.x] = a.ids[threadIdx.x];
     }
@@ -693,11 +718,15 @@ void *k3_decode_mx_control_words(const k3_moe_layer_desc *d, void *scratch) {
     return (void *)(((uintptr_t)(route + 2u * 1024u * 4u) + 255u) & ~(uintptr_t)255u);
 }
 
+void *k3_decode_mx_front_done_word(const k3_moe_layer_desc *d, void *scratch) {
+    return (uint32_t *)k3_decode_mx_control_words(d, scratch) + kControlWords;
+}
+
 // Routed experts of one token: act [top_k, I] and rows_out [top_k, hidden] in rank
 // order (ids on the device) from the token's E2M1 terms in `scratch`.
 bool k3_decode_mx_experts(const k3_moe_layer_desc *d, void *ids, void *weights, const void *route_words,
                           void *act, void *rows_out, void *scratch, void *between, const k3_decode_tail *tail,
-                          cudaStream_t stream) {
+                          uint32_t front_blocks, cudaStream_t stream) {
     if (route_words != nullptr && (d->expert_count > 1024u || !weights)) return false;
     const uint32_t H = d->hidden, I = d->expert_hidden, k = d->top_k;
     auto align = [](uint8_t *p) { return (uint8_t *)(((uintptr_t)p + 255u) & ~(uintptr_t)255u); };
@@ -771,6 +800,8 @@ bool k3_decode_mx_experts(const k3_moe_layer_desc *d, void *ids, void *weights, 
     a.act_terms = a_terms;
     a.act_sf = a_sf;
     a.control = (uint32_t *)k3_decode_mx_control_words(d, scratch);
+    a.front_done = front_blocks != 0u ? (const uint32_t *)k3_decode_mx_front_done_word(d, scratch) : nullptr;
+    a.front_blocks = front_blocks;
     if (tail != nullptr) {
         if (d->local_expert_first != 0u || d->local_expert_count != d->expert_count) return false;
         a.tail.out = (uint16_t *)tail->out;

@@ -41,16 +41,8 @@ K3_DEVINL uint32_t count_arrival(uint32_t *word, uint32_t epoch24) {
     return 0u;
 }
 
-// Whole warp, after its stores to the group's inputs.  False if the count failed.
-K3_DEVINL bool tail_arrive(const DecodeTail &t, uint32_t group, uint32_t lane) {
-    __threadfence();
-    __syncwarp();
-    uint32_t arrivals = 0u;
-    if (lane == 0) arrivals = count_arrival(t.count + group, t.epoch);
-    arrivals = __shfl_sync(0xffffffffu, arrivals, 0);
-    if (arrivals == 0u) return false;
-    if (arrivals != t.expected) return true;
-    __threadfence();
+// The 32 output columns of `group` from parts that are complete in memory (whole warp).
+K3_DEVINL void tail_columns(const DecodeTail &t, uint32_t group, uint32_t lane) {
     const uint32_t col = group * 32u + lane;
     // eight rows in flight at a time, summed in rank order
     float acc = 0.f;
@@ -74,6 +66,19 @@ K3_DEVINL bool tail_arrive(const DecodeTail &t, uint32_t group, uint32_t lane) {
     if (t.residual != nullptr)
         bits = float_to_bf16_bits(bf16_bits_to_float(__ldcg(t.residual + col)) + bf16_bits_to_float(bits));
     t.out[col] = bits;
+}
+
+// Whole warp, after its stores to the group's inputs.  False if the count failed.
+K3_DEVINL bool tail_arrive(const DecodeTail &t, uint32_t group, uint32_t lane) {
+    __threadfence();
+    __syncwarp();
+    uint32_t arrivals = 0u;
+    if (lane == 0) arrivals = count_arrival(t.count + group, t.epoch);
+    arrivals = __shfl_sync(0xffffffffu, arrivals, 0);
+    if (arrivals == 0u) return false;
+    if (arrivals != t.expected) return true;
+    __threadfence();
+    tail_columns(t, group, lane);
     // Last toucher of the group's word: leave it at zero, so that the same call
     // replayed with the same epoch (a captured graph launched again) counts from
     // zero like a fresh one instead of finding the full count of its last run.

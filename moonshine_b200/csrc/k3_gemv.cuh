@@ -209,6 +209,38 @@ K3_DEVINL float q8_scale_at(const void *scales, uint64_t index, int scale_f16) {
                      : reinterpret_cast<const float *>(scales)[index];
 }
 
+// One 128-column step of 16 Q8 rows on this lane: `cur` holds the lane's 32 int8 of rows g
+// and g + 8 and their two group scales, `x_step` points at the lane's 32 f16 of the vector
+// for this step (only lanes with b_active carry vector values, the others zeros).
+K3_DEVINL void q8_step_apply(float &acc_a, float &acc_b, const Q8Step &cur, const __half *x_step, bool b_active) {
+    uint32_t xr[16];
+    if (b_active) {
+        const uint4 *p = reinterpret_cast<const uint4 *>(x_step);
+#pragma unroll
+        for (int w = 0; w < 4; w++) {
+            const uint4 v = p[w];
+            xr[4 * w] = v.x; xr[4 * w + 1] = v.y; xr[4 * w + 2] = v.z; xr[4 * w + 3] = v.w;
+        }
+    } else {
+#pragma unroll
+        for (int w = 0; w < 16; w++) xr[w] = 0u;
+    }
+    float c[4] = {0.f, 0.f, 0.f, 0.f};
+    const uint32_t wa[8] = {cur.a0.x, cur.a0.y, cur.a0.z, cur.a0.w, cur.a1.x, cur.a1.y, cur.a1.z, cur.a1.w};
+    const uint32_t wb[8] = {cur.b0.x, cur.b0.y, cur.b0.z, cur.b0.w, cur.b1.x, cur.b1.y, cur.b1.z, cur.b1.w};
+#pragma unroll
+    for (int w = 0; w < 8; w++) {
+        uint32_t a01, a23, b01, b23;
+        int8x4_to_f16(wa[w], a01, a23);
+        int8x4_to_f16(wb[w], b01, b23);
+        mma_f16_m16n8k16(c, a01, b01, a23, b23, xr[2 * w], xr[2 * w + 1]);
+    }
+    acc_a = fmaf(cur.sa0, c[0], acc_a);
+    acc_a = fmaf(cur.sa1, c[1], acc_a);
+    acc_b = fmaf(cur.sb0, c[2], acc_b);
+    acc_b = fmaf(cur.sb1, c[3], acc_b);
+}
+
 // One warp: partial dot products of 16 consecutive Q8 rows [row0, row0+16) of a
 // [rows, k] matrix (k % 128 == 0, block % 32 == 0) with the f16 vector xs over the
 // 128-column steps [step_begin, step_end).  After the call lanes with t == 0 hold
@@ -252,32 +284,7 @@ K3_DEVINL void q8_rows16_partial(float &r0, float &r1, const int8_t *q, const vo
             if (step >= step_end) break;
             const Q8Step cur = pf[i];
             if (step + kDepth < step_end) pf[i] = fetch(step + kDepth);
-            uint32_t xr[16];
-            if (b_active) {
-                const uint4 *p = reinterpret_cast<const uint4 *>(xv + 128u * step);
-#pragma unroll
-                for (int w = 0; w < 4; w++) {
-                    const uint4 v = p[w];
-                    xr[4 * w] = v.x; xr[4 * w + 1] = v.y; xr[4 * w + 2] = v.z; xr[4 * w + 3] = v.w;
-                }
-            } else {
-#pragma unroll
-                for (int w = 0; w < 16; w++) xr[w] = 0u;
-            }
-            float c[4] = {0.f, 0.f, 0.f, 0.f};
-            const uint32_t wa[8] = {cur.a0.x, cur.a0.y, cur.a0.z, cur.a0.w, cur.a1.x, cur.a1.y, cur.a1.z, cur.a1.w};
-            const uint32_t wb[8] = {cur.b0.x, cur.b0.y, cur.b0.z, cur.b0.w, cur.b1.x, cur.b1.y, cur.b1.z, cur.b1.w};
-#pragma unroll
-            for (int w = 0; w < 8; w++) {
-                uint32_t a01, a23, b01, b23;
-                int8x4_to_f16(wa[w], a01, a23);
-                int8x4_to_f16(wb[w], b01, b23);
-                mma_f16_m16n8k16(c, a01, b01, a23, b23, xr[2 * w], xr[2 * w + 1]);
-            }
-            acc_a = fmaf(cur.sa0, c[0], acc_a);
-            acc_a = fmaf(cur.sa1, c[1], acc_a);
-            acc_b = fmaf(cur.sb0, c[2], acc_b);
-            acc_b = fmaf(cur.sb1, c[3], acc_b);
+            q8_step_apply(acc_a, acc_b, cur, xv + 128u * step, b_active);
         }
     }
     // lanes t = 0 and 1 hold the two halves (groups 0,1 and 2,3) of every step

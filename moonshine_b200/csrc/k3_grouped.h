@@ -79,13 +79,26 @@ void *k3_decode_mx_route_words(const k3_moe_layer_desc *desc, void *scratch);
 // 64 words inside `scratch` that must be zero when the expert kernel starts (its item
 // counter and the per-rank arrival counts); the front kernel clears them
 void *k3_decode_mx_control_words(const k3_moe_layer_desc *desc, void *scratch);
+void *k3_decode_mx_front_done_word(const k3_moe_layer_desc *desc, void *scratch);
 // With route_words (the scores and choices the front kernel's row tasks wrote) the kernel
 // routes the token itself in its prologue and writes ids / weights [top_k]; it is then
 // launched with programmatic stream serialization behind the front kernel.  With
-// route_words null it reads ids (weights untouched).
+// route_words null it reads ids (weights untouched).  front_blocks != 0: the front kernel
+// counts its finished blocks in word kControlWords of the control words (cleared before it
+// started) and the expert kernel waits for that count instead of for the whole chain of
+// grids in front of it (k3_decode_mx_front_done_word()).
 bool k3_decode_mx_experts(const k3_moe_layer_desc *desc, void *ids, void *weights, const void *route_words,
                           void *act, void *rows_out, void *scratch, void *between, const k3_decode_tail *tail,
+                          uint32_t front_blocks,
                           cudaStream_t stream);
+// Shared expert of one token as a persistent ring kernel on a few SMs (k3_decode_shared.cu).
+bool k3_decode_shared_ring_supported(const k3_moe_layer_desc *desc);
+uint32_t k3_decode_shared_ring_ctas();
+// zero_word: a word cleared before the kernels queued behind may start (or null).
+bool k3_decode_shared_ring(const k3_moe_layer_desc *desc, const void *x, void *sh_gate, void *sh_up, void *sh_out,
+                           void *zero_word, cudaStream_t stream);
+uint32_t k3_decode_shared_status();
+bool k3_decode_shared_status_clear();
 uint32_t k3_decode_mx_status();
 uint32_t k3_decode_status();
 uint32_t k3_dispatch_status();

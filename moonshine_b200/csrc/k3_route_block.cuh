@@ -29,9 +29,23 @@ struct RouteScratch {          // shared memory, 10.5 KB
 K3_DEVINL void route_topk_block(RouteScratch &rs, uint32_t *ids_s, float *weights_s, const float *route_words,
                                 uint32_t experts, uint32_t top_k, float route_scale) {
     const uint32_t warp = threadIdx.x / kWarp, lane = threadIdx.x % kWarp;
-    for (uint32_t e = threadIdx.x; e < 1024u; e += blockDim.x) {
-        rs.score[e] = e < experts ? __ldcg(route_words + e) : 0.f;
-        rs.choice[e] = e < experts ? __ldcg(route_words + 1024u + e) : 0.f;
+    {
+        // all of a thread's loads in flight at once (blockDim >= 256: at most four experts each)
+        float sc[4], ch[4];
+#pragma unroll
+        for (uint32_t j = 0; j < 4u; j++) {
+            const uint32_t e = threadIdx.x + j * blockDim.x;
+            sc[j] = e < experts ? __ldcg(route_words + e) : 0.f;
+            ch[j] = e < experts ? __ldcg(route_words + 1024u + e) : 0.f;
+        }
+#pragma unroll
+        for (uint32_t j = 0; j < 4u; j++) {
+            const uint32_t e = threadIdx.x + j * blockDim.x;
+            if (e < 1024u) {
+                rs.score[e] = sc[j];
+                rs.choice[e] = ch[j];
+            }
+        }
     }
     __syncthreads();
     if (warp < 8u) {
