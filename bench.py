@@ -288,7 +288,7 @@ DECODE_TRAFFIC_BYTES = 434.9e6
 def launches_per_step(tokens: int, shared: bool) -> int:
     """Kernels of this library one layer pass launches (baseline shapes)."""
     if tokens == 1:
-        return 5                                   # front, gate/up, down (+ combine) + shared gate/up, shared down
+        return 4                                   # shared-expert ring kernel, router rows, experts, tail
     route, shared_k, dispatch, combine = 2, (5 if shared else 0), 3, 1
     experts = 1 + 3 + 2                            # row split, 3 gathers, gate/up and down GEMMs
     return route + shared_k + dispatch + experts + combine
@@ -317,15 +317,38 @@ def time_decode(call, cfg, device, torch, iters: int = 40):
     return statistics.median(times), min(times)
 
 
+def time_decode_rotating(calls, cfg, device, torch, iters: int = 48):
+    """One-token decode with a cold L2 by input size: `calls` are layers with distinct weight
+    tables taken in turn, so any byte is read again only after every layer's 434 MB (3.4x the
+    L2) has gone through; nothing is written between iterations, so no write-back of a flush
+    buffer shares the memory system with the token.  Per-iteration events as in time_decode."""
+    d = cfg["hidden"]
+    xs = torch.from_numpy(synth.activations(7, 8, d).view(np.int16)).to(device).view(torch.bfloat16)
+    k = len(calls)
+    for i in range(2 * k + 2):
+        calls[i % k](xs[i % 8:i % 8 + 1])
+    starts = [torch.cuda.Event(enable_timing=True) for _ in range(iters)]
+    stops = [torch.cuda.Event(enable_timing=True) for _ in range(iters)]
+    for i in range(iters):
+        starts[i].record()
+        calls[i % k](xs[i % 8:i % 8 + 1])
+        stops[i].record()
+    torch.cuda.synchronize()
+    times = [a.elapsed_time(b) for a, b in zip(starts, stops)]
+    return statistics.median(times), min(times)
+
+
 def decode_kernels(layer, cfg, device, torch):
     """Per-kernel times of the one-token layer from events the library records between
     its launches (single GPU)."""
     xs = torch.from_numpy(synth.activations(7, 1, cfg["hidden"]).view(np.int16)).to(device).view(torch.bfloat16)
     ph = layer.phase_times(xs[0:1], 10)
-    return {"front_ms": ph["router_ms"] + ph["shared_ms"], "gate_up_ms": ph["dispatch_ms"],
-            "down_ms": ph["experts_ms"], "combine_ms": ph["combine_ms"],
-            "note": "events between launches on the main stream; the shared expert runs beside them on a "
-                    "side stream; front includes host launch latency after an idle device"}
+    return {"ring_launch_and_router_ms": ph["router_ms"] + ph["shared_ms"], "experts_ms": ph["dispatch_ms"],
+            "tail_ms": ph["experts_ms"] + ph["combine_ms"],
+            "note": "events recorded between the launches: a programmatic launch needs its predecessor next to it "
+                    "in the stream, so with the events in between the kernels run one after the other - these are "
+                    "per-kernel times, not a decomposition of the token time (the shared expert's ring kernel runs "
+                    "under all of them; the first figure includes host launch latency after an idle device)"}
 
 
 def kind_peaks(torch) -> dict:
@@ -752,12 +775,19 @@ def run_layer(args, device, peaks, torch, dist, world, rank, local_rank, MoELaye
                 dlayer = MoELayer(dcfg, None, seed=0, device=device)
             else:
                 dlayer = layer
-            dms, dmin = time_decode(lambda x: dlayer.forward(x), dcfg, device, torch)
+            fms, fmin = time_decode(lambda x: dlayer.forward(x), dcfg, device, torch)
             dkernels = decode_kernels(dlayer, dcfg, device, torch)
+            # cold L2 by input size: four layers' distinct tables in turn (a model's layers do this)
+            others = [MoELayer(dcfg, None, seed=s, device=device) for s in (1, 2, 3)]
+            calls = [lambda x, l=l: l.forward(x) for l in [dlayer] + others]
+            dms, dmin = time_decode_rotating(calls, dcfg, device, torch)
+            del others, calls
+            torch.cuda.empty_cache()
             launches = launches_per_step(1, bool(dcfg["shared_hidden"]))
         else:
             # the same tensors as the prefill layer apart from the router bias: reuse the shard
             dms, dmin = time_decode(lambda x: layer.decode(x), dcfg, device, torch)
+            fms = fmin = None
             t = torch.tensor([dms], device=device)
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
             dms = float(t.item())
@@ -773,8 +803,17 @@ def run_layer(args, device, peaks, torch, dist, world, rank, local_rank, MoELaye
                                "peak_source": peaks["source"]},
                   "kernels_ms": dkernels,
                   "router_bias": cfg["bias_mode"] if world > 1 else "uniform",
-                  "l2": "flushed between iterations (252 MiB buffer rewritten), 8 tokens round-robin",
+                  "l2": ("cold by input size: 4 layers with distinct tables taken in turn (1.7 GB read between two "
+                         "reads of a byte, L2 126 MB), nothing written between iterations, 8 tokens round-robin"
+                         if world == 1 else
+                         "flushed between iterations (252 MiB buffer rewritten), 8 tokens round-robin"),
                   "gpu_launches_per_token": launches}
+        if fms is not None:
+            fg = nbytes / (fms * 1e-3) / 1e9
+            decode["write_flushed"] = {
+                "ms_per_token": fms, "ms_min": fmin, "achieved": fg, "frac": fg / peaks["hbm_gbs"],
+                "l2": "one layer, a 252 MiB buffer rewritten before every token: its dirty lines (up to the L2's 126 MB) "
+                      "are written back while the token's reads evict them, which shares the memory system with the token"}
         if world > 1:
             decode["parallelism"] = ("token replicated, router and shared expert on every rank, the selected experts "
                                      "where they live, one all-reduce (exact integer sum) of the 16 expert rows")

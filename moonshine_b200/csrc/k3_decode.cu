@@ -804,7 +804,7 @@ bool k3_decode_layer(const k3_moe_layer_desc *d, const void *x, void *logits, vo
     // shapes: two row kernels on a low-priority side stream, and with every expert in this
     // table no tail launch - the down epilogue warps and the shared-down blocks count arrivals
     // per 32 output columns and the last one adds them up.
-    const bool ring = router_kernel && k3_decode_shared_ring_supported(d) &&
+    const bool ring = router_kernel && k3_decode_shared_ring_supported(d) && k3_decode_shared_ring_ctas() != 0u &&
                       ((((uintptr_t)sh_gate) | ((uintptr_t)sh_up)) & 15u) == 0;
     const bool whole_tail = combine && mx && d->local_expert_first == 0u &&
                             d->local_expert_count == d->expert_count && d->hidden % 32u == 0u;

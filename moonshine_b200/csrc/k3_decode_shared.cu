@@ -466,12 +466,15 @@ bool k3_decode_shared_ring_supported(const k3_moe_layer_desc *d) {
     return (all & 15u) == 0u && encode_fn() != nullptr;
 }
 
-// CTAs (= SMs) the shared expert's kernel holds; K3MOE_SHARED_CTAS overrides the default.
+// CTAs (= SMs) the shared expert's kernel holds: 32 by default (8 gate / up tasks and 14 down
+// tasks each at the benchmark shape).  The environment variable K3MOE_SHARED_CTAS, read once,
+// overrides it (1..64); 0 turns the ring kernel off (the row kernels on a side stream run).
 uint32_t k3_decode_shared_ring_ctas() {
     static const uint32_t value = [] {
         const char *env = std::getenv("K3MOE_SHARED_CTAS");
-        const long v = env ? std::strtol(env, nullptr, 10) : 0;
-        return (uint32_t)(v >= 1 && v <= 64 ? v : 32);
+        if (env == nullptr || *env == '\0') return 32u;
+        const long v = std::strtol(env, nullptr, 10);
+        return (uint32_t)(v >= 0 && v <= 64 ? v : 32);
     }();
     return std::min<uint32_t>(value, (uint32_t)sm_count() / 2u);
 }

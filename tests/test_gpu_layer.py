@@ -125,3 +125,38 @@ def test_full_shape_decode_properties(oracle):
         same = np.all(got_ids == want_ids, axis=1)
         assert np.all((gaps[~same] > 0) & (gaps[~same] < 1e-6))
         assert G.rel_l2(bf16_tensor_to_bits(out)[same], want_out[same]) <= REL_L2_TOLERANCE
+
+
+_PATHS_SCRIPT = r"""
+import sys
+import numpy as np, torch
+from moonshine_b200 import synth
+from moonshine_b200.layer import MoELayer, bf16_tensor_to_bits
+out = []
+for block, scale in ((32, synth.Q8_F16), (128, synth.Q8_F32)):
+    cfg = synth.baseline_config(experts=32, hidden=2048, expert_hidden=1024, shared_hidden=1024, top_k=8,
+                                q8_block=block, q8_scale_type=scale)
+    layer = MoELayer(cfg, None, seed=5, device=torch.device("cuda:0"), max_tokens=4)
+    x = torch.from_numpy(synth.activations(9, 3, cfg["hidden"]).view(np.int16)).cuda().view(torch.bfloat16)
+    for t in range(3):
+        out.append(bf16_tensor_to_bits(layer.forward(x[t:t + 1].contiguous())).copy())
+np.save(sys.argv[1], np.concatenate(out))
+"""
+
+
+def test_one_token_shared_expert_paths_give_the_same_bits(tmp_path):
+    """The shared expert of the one-token layer as the ring kernel (bulk copies into shared
+    memory, K3MOE_SHARED_CTAS default) and as the row kernels on a side stream
+    (K3MOE_SHARED_CTAS=0) run the same arithmetic: layer outputs equal bit for bit, for f16
+    scales per 32 columns and f32 scales per 128."""
+    import subprocess
+    import sys
+    root = os.path.dirname(HERE)
+    got = []
+    for ctas in ("32", "0"):
+        path = str(tmp_path / f"out_{ctas}.npy")
+        env = dict(os.environ, K3MOE_SHARED_CTAS=ctas, PYTHONPATH=root)
+        subprocess.run([sys.executable, "-c", _PATHS_SCRIPT, path], check=True, env=env, cwd=root, timeout=600)
+        got.append(np.load(path))
+    assert got[0].shape == got[1].shape and got[0].size == 6 * 2048
+    assert np.array_equal(got[0], got[1])
