@@ -1,26 +1,26 @@
-// One-token (decode) routed-MoE layer: three launches on the caller's stream and two
-// on a side stream, no host round trip.
+// One-token (decode) routed-MoE layer: four launches on the caller's stream, one chain of
+// programmatic launches, no host round trip.
 //
-//   front    router logits (one 256-thread block per BF16 row, the reference's
-//            reduction order) and the token's E2M1 terms; the last block
-//            to finish routes the token (sigmoid + bias top-k).  On shapes the
-//            block-scaled expert kernels do not take it also carries the shared
-//            expert's gate/up rows and activation.
-//   gate/up  the top_k selected experts' gate and up rows + activation
-//   down     the selected experts' down rows
-// and, on a low-priority side stream next to them (it depends only on the token):
-//   shared gate/up, shared activation + down (Q8 rows on mma.sync)
-// The weighted sum in rank order + shared output + residual has no launch of its
-// own: the producers of its inputs (down epilogue warps, shared-down blocks) count
-// arrivals per 32 output columns and the last one forms them (k3_decode_tail.cuh).
-// With an expert-parallel shard (not every expert local) a combine launch follows.
+//   shared   the shared expert (Q8 rows on mma.sync) as a ring kernel on a few SMs
+//            (k3_decode_shared.cu); it depends only on the token, starts first and lets
+//            the kernels behind it start at once
+//   router   router logits (the reference's reduction order, all rows of a block in
+//            flight at once), scores, and the token's E2M1 terms
+//   experts  every CTA routes the token (sigmoid + bias top-k), then the selected
+//            experts' gate/up + activation and down products (k3_decode_mx.cu)
+//   tail     weighted sum in rank order + shared output + residual (k3_decode_tail.cuh)
+// Shapes the ring kernel does not take run the shared expert as two row kernels on a
+// low-priority side stream, and the tail then has no launch of its own: the producers of
+// its inputs (down epilogue warps, shared-down blocks) count arrivals per 32 output
+// columns and the last one forms them.  With an expert-parallel shard (not every expert
+// local) a combine launch follows instead of the tail.
 //
 // It replaces the per-token sequence of the reference's decode_routed_layer
 // (k3_engine.cu:1554-1563 router, :1668-1689 static projections, :1032-1066
 // launch_expert x 16, :1851-1897 tail), which needs three host synchronisations
 // and ~70 launches per layer.
 //
-// The expert kernels of the main path are the block-scaled tensor-core kernels of
+// The expert kernel of the main path is the block-scaled tensor-core kernel of
 // k3_decode_mx.cu.  The ones in this file serve the remaining shapes: persistent,
 // a CTA stages the activation vector(s) in shared memory once (as f16 after an
 // exact power-of-two rescale), then each warp streams whole 16-row blocks of

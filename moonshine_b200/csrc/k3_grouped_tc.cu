@@ -599,7 +599,8 @@ bool tc_shape_ok(uint32_t k, uint32_t rows) {
 extern "C" uint32_t k3_moe_device_status(void) {
     uint32_t v = 0xffffffffu;
     if (cudaMemcpyFromSymbol(&v, g_tc_status, sizeof(v)) != cudaSuccess) (void)cudaGetLastError();
-    return v | k3_decode_mx_status() | k3_decode_status() | k3_grouped_mx_status() | k3_dispatch_status();
+    return v | k3_decode_mx_status() | k3_decode_status() | k3_decode_shared_status() | k3_grouped_mx_status() |
+           k3_dispatch_status();
 }
 
 bool k3_status_words_clear() {
@@ -608,6 +609,7 @@ bool k3_status_words_clear() {
     if (!ok) (void)cudaGetLastError();
     ok = k3_decode_status_clear() && ok;
     ok = k3_decode_mx_status_clear() && ok;
+    ok = k3_decode_shared_status_clear() && ok;
     ok = k3_dispatch_status_clear() && ok;
     ok = k3_grouped_mx_status_clear() && ok;
     return ok;
