@@ -245,6 +245,11 @@ decode_experts_kernel(const __grid_constant__ MxMaps maps, MxArgs a) {
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = *tmem_slot;
+    if (threadIdx.x == 0) {
+        prefetch_tensormap(&maps.w1);
+        prefetch_tensormap(&maps.w3);
+        prefetch_tensormap(&maps.w2);
+    }
     // a kernel queued behind this one with programmatic serialization (the layer's tail) may
     // take its places now; it waits for this grid to finish before it reads anything
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
@@ -271,6 +276,9 @@ decode_experts_kernel(const __grid_constant__ MxMaps maps, MxArgs a) {
         }
         __syncthreads();
     }
+    // the first work item is drawn now, so that the counter's round trip runs under the routing
+    uint32_t first_item = 0u;
+    if (threadIdx.x == 0) first_item = atomicAdd(a.control, 1u);
     if (a.route_words != nullptr) {
         // every CTA routes the token itself (the ring is still free: it serves as scratch)
         RouteScratch &rs = *reinterpret_cast<RouteScratch *>(base + lay.ring);
@@ -324,12 +332,7 @@ decode_experts_kernel(const __grid_constant__ MxMaps maps, MxArgs a) {
         uint32_t s = 0, ph = 0, seq = 0;
         bool ok = true;
         uint32_t w = 0;
-        if (lane == 0) {
-            prefetch_tensormap(&maps.w1);
-            prefetch_tensormap(&maps.w3);
-            prefetch_tensormap(&maps.w2);
-            w = atomicAdd(a.control, 1u);
-        }
+        if (lane == 0) w = first_item;
         while (ok) {
             const uint32_t slot = seq % kItemSlots, parity = (seq / kItemSlots) & 1u;
             seq++;

@@ -160,3 +160,28 @@ def test_one_token_shared_expert_paths_give_the_same_bits(tmp_path):
         got.append(np.load(path))
     assert got[0].shape == got[1].shape and got[0].size == 6 * 2048
     assert np.array_equal(got[0], got[1])
+
+
+@pytest.mark.parametrize("ties", [False, True])
+def test_one_token_routing_prefilter_and_general_method(oracle, ties):
+    """The expert kernel routes the token itself: a threshold from a few arg-max rounds per
+    warp leaves a few dozen candidates to rank; when more than 256 experts reach the
+    threshold (here: every choice value equal, 384 experts) the general method runs.  Both
+    must give the oracle's ids (lower id first on ties) and weights."""
+    cfg = synth.baseline_config(experts=384, hidden=2048, expert_hidden=1024, shared_hidden=1024, top_k=8)
+    weights = synth.make_layer(cfg, seed=11)
+    if ties:
+        weights["router_weight"][...] = 0          # every logit 0: sigmoid 0.5
+        weights["router_bias"][...] = 0.25
+    layer = MoELayer(cfg, weights, seed=11, max_tokens=2)
+    x = synth.activations(21, 1, cfg["hidden"])
+    out, ids, w = layer.forward(G.dev(x).view(torch.bfloat16), want_routes=True)
+    want_out, want_ids, want_w, logits, _ = oracle.moe_layer(weights, x)
+    got_ids = G.host(ids, np.uint32)
+    if ties:
+        assert np.array_equal(got_ids[0], np.arange(cfg["top_k"], dtype=np.uint32))
+    gaps = oracle.router_min_gap(logits, weights["router_bias"], cfg["top_k"])
+    assert np.array_equal(got_ids, want_ids) or (0 < gaps[0] < 1e-6)
+    if np.array_equal(got_ids, want_ids):
+        assert np.allclose(G.host(w), want_w, rtol=1e-6, atol=0)
+        assert G.rel_l2(bf16_tensor_to_bits(out), want_out) <= REL_L2_TOLERANCE
