@@ -382,6 +382,23 @@ def kind_peaks(torch) -> dict:
         b.record()
         torch.cuda.synchronize()
         out[name] = {"burst_tflops": best, "sustained_tflops": launches * flop.value / (a.elapsed_time(b) * 1e-3) / 1e12}
+    # the same instruction at the N extents the prefill kernel issues (a row tile has at most 128
+    # rows): a chain of MMAs into one accumulator costs ~55 ns each for every N <= 128
+    by_n = {}
+    for n in (128, 64, 32):
+        flop = C.c_double()
+        best = 0.0
+        for i in range(4):
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            if not ops.k3_moe_peak_launch_n(1, n, 16000, C.byref(flop)):
+                raise RuntimeError("k3_moe_peak_launch_n failed")
+            b.record()
+            torch.cuda.synchronize()
+            if i:
+                best = max(best, flop.value / (a.elapsed_time(b) * 1e-3) / 1e12)
+        by_n[f"n{n}"] = best
+    out["mxf8f6f4"]["burst_tflops_by_n"] = by_n
     return out
 
 

@@ -290,6 +290,10 @@ bool k3_moe_selftest_bounded_wait(uint32_t limit_us, void *gave_up, void *stream
  * *flop_per_launch (optional) receives the operations of the launch; time the
  * launch with events.  No counterpart in the reference. */
 bool k3_moe_peak_launch(int kind, uint32_t iterations, double *flop_per_launch, void *stream);
+/* The same with N = n (16 .. 256, a multiple of 16): the rate of the MMA shape a
+ * kernel actually issues (the prefill expert kernel: N = rows of the tile, at
+ * most 128; half the operations per operand byte of N = 256). */
+bool k3_moe_peak_launch_n(int kind, uint32_t n, uint32_t iterations, double *flop_per_launch, void *stream);
 
 /* Event helpers for hosts without CUDA runtime bindings: create / destroy a
  * timing event and read the milliseconds between two recorded events (waits

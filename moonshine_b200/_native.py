@@ -141,6 +141,7 @@ SIGNATURES = {
     "k3_moe_layer_forward_events": (C.c_bool, [_DP, vp, vp, u32, vp, sz, C.POINTER(vp), vp]),
     "k3_moe_device_status": (u32, []),
     "k3_moe_peak_launch": (C.c_bool, [i32, u32, C.POINTER(C.c_double), vp]),
+    "k3_moe_peak_launch_n": (C.c_bool, [i32, u32, u32, C.POINTER(C.c_double), vp]),
     "k3_moe_device_status_clear": (C.c_bool, []),
     "k3_moe_selftest_bounded_wait": (C.c_bool, [u32, vp, vp]),
     "k3_moe_phase_stats_add": (C.c_bool, [C.POINTER(PhaseStats), C.POINTER(vp)]),

@@ -155,6 +155,32 @@ K3_DEVINL Item decode_item(uint32_t w, const uint32_t *prefix, const GmxArgs &a)
     return it;
 }
 
+// Accumulator columns [0, 256) as two buffers of 128: a row tile of at most 64 rows takes
+// one buffer (tile 0 in its first 64 columns, tile 1 in the other 64), so that its MMAs run
+// while the epilogue still reads the item before; a larger tile takes both (tile 0 in
+// [0, 128), tile 1 in [128, 256)).  Issuers and epilogue warps walk the items in the same
+// order and keep the same books: uses per buffer (the barriers' phase) and whose turn it is.
+struct AccBuffers {
+    uint32_t use0 = 0u, use1 = 0u;
+    uint32_t turn = 0u;
+    __device__ uint32_t uses(uint32_t b) const { return b == 0u ? use0 : use1; }
+    __device__ bool small(uint32_t rows_valid) const { return rows_valid <= 64u; }
+    __device__ uint32_t first(bool is_small) const { return is_small ? turn : 0u; }
+    __device__ uint32_t column(bool is_small, uint32_t b0, uint32_t tile) const {
+        return is_small ? b0 * 128u + tile * 64u : tile * BN;
+    }
+    __device__ void advance(bool is_small, uint32_t b0) {
+        if (is_small) {
+            if (b0 == 0u) use0++; else use1++;
+            turn ^= 1u;
+        } else {
+            use0++;
+            use1++;
+            turn = 0u;
+        }
+    }
+};
+
 struct GmxMaps {
     CUtensorMap a0, a1;        // packed E2M1 weights (4-bit elements, expanded by the copy)
     CUtensorMap bhi, blo;      // token terms, E4M3 bytes
@@ -172,8 +198,8 @@ grouped_mx_kernel(const __grid_constant__ GmxMaps maps, GmxArgs a) {
     uint64_t *full = bars, *empty = full + kStages;
     uint64_t *sf_full = empty + kStages, *sf_empty = sf_full + kSfBatches;
     uint64_t *sfs_full = sf_empty + kSfBatches, *sfs_empty = sfs_full + kSfSlots;
-    uint64_t *acc_full = sfs_empty + kSfSlots, *acc_empty = acc_full + 1;
-    uint64_t *item_full = acc_empty + 1, *item_empty = item_full + kItemSlots;
+    uint64_t *acc_full = sfs_empty + kSfSlots, *acc_empty = acc_full + 2;      // two accumulator buffers
+    uint64_t *item_full = acc_empty + 2, *item_empty = item_full + kItemSlots;
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(item_empty + kItemSlots);
     volatile uint32_t *abort_flag = tmem_slot + 1;
     uint32_t *total_items_s = tmem_slot + 2;
@@ -197,8 +223,10 @@ grouped_mx_kernel(const __grid_constant__ GmxMaps maps, GmxArgs a) {
             mbar_init(&sfs_full[b], 1);
             mbar_init(&sfs_empty[b], 4);
         }
-        mbar_init(acc_full, 2);
-        mbar_init(acc_empty, 8);
+        for (uint32_t b = 0; b < 2u; b++) {
+            mbar_init(&acc_full[b], 2);
+            mbar_init(&acc_empty[b], 8);
+        }
         for (uint32_t b = 0; b < kItemSlots; b++) {
             mbar_init(&item_full[b], 1);
             mbar_init(&item_empty[b], kItemReaders);
@@ -350,7 +378,8 @@ grouped_mx_kernel(const __grid_constant__ GmxMaps maps, GmxArgs a) {
         // commit to the same stage / scale / accumulator barriers (count 2).
         if (lane == 0) {
             const uint32_t q = warp == 1 ? 0u : 1u;
-            uint32_t s = 0, ph = 0, pacc = 0, sb = 0, sph = 0;
+            uint32_t s = 0, ph = 0, sb = 0, sph = 0;
+            AccBuffers acc;
             bool ok = true;
             for (uint32_t w = next_item(); ok && w != kNoItem; w = next_item()) {
                 const Item it = decode_item(w, prefix, a);
@@ -358,9 +387,14 @@ grouped_mx_kernel(const __grid_constant__ GmxMaps maps, GmxArgs a) {
                 uint32_t idesc[4];
 #pragma unroll
                 for (uint32_t j = 0; j < 4u; j++) idesc[j] = make_idesc_mx(n_eff, j);
-                if (!mbar_wait(acc_empty, pacc ^ 1u, abort_flag)) break;
+                const bool small = acc.small(it.rows_valid);
+                const uint32_t b0 = acc.first(small);
+                if (!mbar_wait(&acc_empty[b0], (acc.uses(b0) & 1u) ^ 1u, abort_flag) ||
+                    (!small && !mbar_wait(&acc_empty[1], (acc.use1 & 1u) ^ 1u, abort_flag))) {
+                    break;
+                }
                 tc_fence_after();
-                const uint32_t d = tmem + kAccCol + q * BN;
+                const uint32_t d = tmem + kAccCol + acc.column(small, b0, q);
                 const uint32_t sfa_col = tmem + (q == 0u ? kSfa0Col : kSfa1Col);
                 for (uint32_t st = 0; st < steps; st++) {
                     if (!mbar_wait(&full[s], ph, abort_flag) ||
@@ -388,8 +422,9 @@ grouped_mx_kernel(const __grid_constant__ GmxMaps maps, GmxArgs a) {
                     }
                 }
                 if (!ok) break;
-                mma_commit(acc_full);
-                pacc ^= 1u;
+                mma_commit(&acc_full[b0]);
+                if (!small) mma_commit(&acc_full[1]);
+                acc.advance(small, b0);
             }
         }
     } else if (warp < 8) {
@@ -444,14 +479,20 @@ grouped_mx_kernel(const __grid_constant__ GmxMaps maps, GmxArgs a) {
         const uint32_t quad = warp & 3u;
         const uint32_t half = (warp - 8u) >> 2;
         const uint32_t m = 32u * quad + lane;            // weight row inside the tile
-        uint32_t pacc = 0;
+        AccBuffers acc;
         for (uint32_t w = __shfl_sync(0xffffffffu, next_item(), 0); w != kNoItem;
              w = __shfl_sync(0xffffffffu, next_item(), 0)) {
             const Item it = decode_item(w, prefix, a);
-            if (!mbar_wait(acc_full, pacc, abort_flag)) break;
-            pacc ^= 1u;
+            const bool small = acc.small(it.rows_valid);
+            const uint32_t b0 = acc.first(small);
+            if (!mbar_wait(&acc_full[b0], acc.uses(b0) & 1u, abort_flag) ||
+                (!small && !mbar_wait(&acc_full[1], acc.use1 & 1u, abort_flag))) {
+                break;
+            }
+            acc.advance(small, b0);
             tc_fence_after();
-            const uint32_t t0 = tmem + ((32u * quad) << 16) + kAccCol;
+            const uint32_t t0 = tmem + ((32u * quad) << 16) + kAccCol + acc.column(small, b0, 0u);
+            const uint32_t tile1 = acc.column(small, b0, 1u) - acc.column(small, b0, 0u);
             const uint32_t col0 = it.m_item * tile_rows + m;
             const uint32_t col1 = kE == kEAct ? col0 : col0 + BM;
             const bool in0 = col0 < a.w_rows, in1 = col1 < a.w_rows;
@@ -462,13 +503,16 @@ grouped_mx_kernel(const __grid_constant__ GmxMaps maps, GmxArgs a) {
                 uint32_t r0[32], r1[32];
                 if (mine) {
                     tmem_ld_32x32(t0 + c, r0);
-                    tmem_ld_32x32(t0 + BN + c, r1);
+                    tmem_ld_32x32(t0 + tile1 + c, r1);
                     tmem_ld_wait();
                 }
                 if (!released && (!mine || c + 64u >= it.rows_valid)) {
                     tc_fence_before();
                     __syncwarp();
-                    if (lane == 0) mbar_arrive(acc_empty);
+                    if (lane == 0) {
+                        mbar_arrive(&acc_empty[b0]);
+                        if (!small) mbar_arrive(&acc_empty[1]);
+                    }
                     released = true;
                 }
                 if (!mine) break;
@@ -516,7 +560,10 @@ grouped_mx_kernel(const __grid_constant__ GmxMaps maps, GmxArgs a) {
             if (!released) {
                 tc_fence_before();
                 __syncwarp();
-                if (lane == 0) mbar_arrive(acc_empty);
+                if (lane == 0) {
+                    mbar_arrive(&acc_empty[b0]);
+                    if (!small) mbar_arrive(&acc_empty[1]);
+                }
             }
         }
     }

@@ -44,7 +44,7 @@ K3_DEVINL void tmem_st_32x4(uint32_t taddr, uint32_t v) {
     asm volatile("tcgen05.st.sync.aligned.32x32b.x4.b32 [%0], {%1, %1, %1, %1};" ::"r"(taddr), "r"(v) : "memory");
 }
 
-__global__ void __launch_bounds__(kPeakThreads, 1) peak_kernel(int kind, uint32_t iterations) {
+__global__ void __launch_bounds__(kPeakThreads, 1) peak_kernel(int kind, uint32_t n, uint32_t iterations) {
     extern __shared__ unsigned char smem_raw[];
     unsigned char *base = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
     uint64_t *done = reinterpret_cast<uint64_t *>(base + kATile + kBTile);
@@ -81,7 +81,7 @@ __global__ void __launch_bounds__(kPeakThreads, 1) peak_kernel(int kind, uint32_
         const uint64_t da = make_desc_sw128(smem_u32(base));
         const uint64_t db = make_desc_sw128(smem_u32(base + kATile));
         if (kind == kPeakBf16) {
-            const uint32_t idesc = make_idesc_bf16(128, 256);
+            const uint32_t idesc = make_idesc_bf16(128, n);
             for (uint32_t it = 0; it < iterations; it++) {
 #pragma unroll
                 for (uint32_t j = 0; j < 4u; j++) mma_f16_ss(tmem, da + 2u * j, db + 2u * j, idesc, (it | j) != 0u);
@@ -90,7 +90,7 @@ __global__ void __launch_bounds__(kPeakThreads, 1) peak_kernel(int kind, uint32_
             const bool mxf4 = kind == kPeakMxf4;
             // A E2M1, B E4M3 (mxf8f6f4) or E2M1 (mxf4), UE8M0 scales, M = 128, N = 256
             const uint32_t formats = mxf4 ? ((1u << 7) | (1u << 10)) : ((5u << 7) | (0u << 10));
-            const uint32_t common = formats | ((256u >> 3) << 17) | (1u << 23) | ((128u >> 4) << 24);
+            const uint32_t common = formats | ((n >> 3) << 17) | (1u << 23) | ((128u >> 4) << 24);
             for (uint32_t it = 0; it < iterations; it++) {
 #pragma unroll
                 for (uint32_t j = 0; j < 4u; j++) {
@@ -115,14 +115,22 @@ __global__ void __launch_bounds__(kPeakThreads, 1) peak_kernel(int kind, uint32_
 }  // namespace
 
 // kind: 0 bf16, 1 mxf8f6f4 block-scaled (E2M1 x E4M3), 2 mxf4 block-scaled.  Launches one
-// CTA per SM, each issuing 4 * iterations MMAs of M = 128, N = 256; *flop_per_launch (optional)
-// receives the floating-point operations of the whole launch.  Time it with events.
-extern "C" bool k3_moe_peak_launch(int kind, uint32_t iterations, double *flop_per_launch, void *stream) {
-    if (kind < 0 || kind > 2 || iterations == 0u || iterations > 4000000u) return false;
+// CTA per SM, each issuing 4 * iterations MMAs of M = 128 and N = n (16 .. 256, a multiple of
+// 16) on operands that stay in shared memory; *flop_per_launch (optional) receives the
+// floating-point operations of the whole launch.  Time it with events.
+extern "C" bool k3_moe_peak_launch_n(int kind, uint32_t n, uint32_t iterations, double *flop_per_launch,
+                                     void *stream) {
+    if (kind < 0 || kind > 2 || iterations == 0u || iterations > 4000000u || n < 16u || n > 256u || n % 16u != 0u)
+        return false;
     if (!set_max_dynamic_smem((const void *)peak_kernel, kSmem)) return false;
     const int sms = sm_count();
     const uint32_t k_per_mma = kind == kPeakBf16 ? 16u : kind == kPeakMxf8f6f4 ? 32u : 64u;
-    if (flop_per_launch) *flop_per_launch = 2.0 * 128.0 * 256.0 * k_per_mma * 4.0 * iterations * sms;
-    peak_kernel<<<sms, kPeakThreads, kSmem, (cudaStream_t)stream>>>(kind, iterations);
+    if (flop_per_launch) *flop_per_launch = 2.0 * 128.0 * (double)n * k_per_mma * 4.0 * iterations * sms;
+    peak_kernel<<<sms, kPeakThreads, kSmem, (cudaStream_t)stream>>>(kind, n, iterations);
     return launch_ok();
+}
+
+// N = 256: the shape with the least operand traffic per operation.
+extern "C" bool k3_moe_peak_launch(int kind, uint32_t iterations, double *flop_per_launch, void *stream) {
+    return k3_moe_peak_launch_n(kind, 256u, iterations, flop_per_launch, stream);
 }
