@@ -124,10 +124,17 @@ def test_phase_ledger_accumulates_under_the_reference_names():
         ops.k3_moe_event_destroy(e)
 
 
-def test_one_token_layer_replays_from_a_cuda_graph():
+RING_SHAPE = dict(hidden=2048, expert_hidden=1024, experts=32, top_k=8, shared_hidden=1024)
+
+
+@pytest.mark.parametrize("shape", ["side_stream", "ring"])
+def test_one_token_layer_replays_from_a_cuda_graph(shape):
     """One captured one-token call launched again with other tokens gives what eager
-    calls give: the arrival words of the fused tail count from zero on every replay."""
-    cfg = synth.baseline_config(**cases.MID)
+    calls give, in both forms of the sequence: row kernels on a side stream with the tail
+    inside the kernels (its arrival words count from zero on every replay), and the chain of
+    four programmatic launches with the shared expert's ring kernel (its counters and the
+    router's done-count are cleared by the kernels themselves)."""
+    cfg = synth.baseline_config(**(cases.MID if shape == "side_stream" else RING_SHAPE))
     weights = synth.make_layer(cfg, 21)
     layer = MoELayer(cfg, weights, seed=21, device=G.DEV, max_tokens=1)
     xs = G.dev(synth.activations(22, 3, cfg["hidden"])).view(torch.bfloat16)
