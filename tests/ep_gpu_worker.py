@@ -1,6 +1,6 @@
 """Worker of tests/test_gpu_ep.py: one rank per GPU (launched by torch.distributed.run).
 Compares the expert-parallel layer with the single-GPU layer on the same seeded
-inputs and writes a verdict line per rank."""
+inputs and writes an outcome line per rank."""
 import os
 import sys
 
@@ -22,7 +22,7 @@ def main():
     torch.cuda.set_device(local)
     device = torch.device("cuda", local)
     dist.init_process_group("nccl", device_id=device)
-    verdicts = []
+    outcomes = []
     for bias_mode, tokens in (("uniform", 128), ("hot4", 256)):
         cfg = synth.baseline_config(hidden=1024, expert_hidden=512, experts=64, top_k=8,
                                     shared_hidden=512, bias_mode=bias_mode)
@@ -41,7 +41,7 @@ def main():
         g = (got.astype(np.uint32) << 16).view(np.float32).astype(np.float64)
         r = (want.astype(np.uint32) << 16).view(np.float32).astype(np.float64)
         rel = float(np.sqrt(((g - r) ** 2).sum() / (r ** 2).sum()))
-        verdicts.append((bias_mode, same_ids, bool(np.array_equal(got, want)), rel))
+        outcomes.append((bias_mode, same_ids, bool(np.array_equal(got, want)), rel))
         # both forms of the exchange (a row per route / a row per destination): same bits
         from moonshine_b200.ep import NativeBackend, ep_forward
         python_path = NativeBackend(ep_layer.layer)      # the same pass driven from Python
@@ -49,7 +49,7 @@ def main():
             out1, ids1, _ = ep_forward(python_path, xl, cfg, once_per_destination=form)
             torch.cuda.synchronize()
             same = bool(np.array_equal(bf16_tensor_to_bits(out1), got)) and bool(torch.equal(ids1, ids))
-            verdicts.append((bias_mode + ("/row per destination" if form else "/row per route"), same, same,
+            outcomes.append((bias_mode + ("/row per destination" if form else "/row per route"), same, same,
                              0.0 if same else 1.0))
         # the same pass cut into two row ranges pipelined against each other: same bits, as long
         # as every range still has enough rows for the same kernels (>= 32 routed rows per rank)
@@ -59,7 +59,7 @@ def main():
                 out2, ids2, _ = piped.forward(xl, want_routes=True)
             torch.cuda.synchronize()
             same = bool(np.array_equal(bf16_tensor_to_bits(out2), got)) and bool(torch.equal(ids2, ids))
-            verdicts.append((bias_mode + "/pipelined", same, same, 0.0 if same else 1.0))
+            outcomes.append((bias_mode + "/pipelined", same, same, 0.0 if same else 1.0))
             piped.close()
         # reduced return (one partial sum per token and expert rank): same routing, output within
         # the layer tolerance of the exact result
@@ -69,7 +69,7 @@ def main():
         torch.cuda.synchronize()
         g3 = (bf16_tensor_to_bits(out3).astype(np.uint32) << 16).view(np.float32).astype(np.float64)
         rel3 = float(np.sqrt(((g3 - r) ** 2).sum() / (r ** 2).sum()))
-        verdicts.append((bias_mode + "/reduced return", bool(torch.equal(ids3, ids)), rel3 <= 1e-2, min(rel3, 1e-3)))
+        outcomes.append((bias_mode + "/reduced return", bool(torch.equal(ids3, ids)), rel3 <= 1e-2, min(rel3, 1e-3)))
         sys.stderr.write(f"rank {rank}: reduced return rel-L2 {rel3:.2e}\n")
         reduced.close()
         # one token, replicated: every rank must end with the single-GPU layer's row
@@ -78,7 +78,7 @@ def main():
             want_one = single.forward(xs[t:t + 1])
             torch.cuda.synchronize()
             same = bool(torch.equal(one, want_one))
-            verdicts.append((f"{bias_mode}/one token {t}", same, same, 0.0 if same else 1.0))
+            outcomes.append((f"{bias_mode}/one token {t}", same, same, 0.0 if same else 1.0))
         ep_layer.close()
     # a stack of 6 layer positions over 3 weight sets, one token at a time, against the
     # same stack on one GPU (a handle of world size 1 in this process)
@@ -105,10 +105,10 @@ def main():
         del full, ws
     for t in range(2):
         same = bool(torch.equal(got_stack[t], h[t]))
-        verdicts.append((f"stack token {t}", same, same, 0.0 if same else 1.0))
-    ok = all(v[1] and v[2] and v[3] <= 1e-3 for v in verdicts)
-    sys.stderr.write(f"rank {rank}: {verdicts}\n")
-    # one verdict line for the whole job (lines of several ranks could interleave)
+        outcomes.append((f"stack token {t}", same, same, 0.0 if same else 1.0))
+    ok = all(v[1] and v[2] and v[3] <= 1e-3 for v in outcomes)
+    sys.stderr.write(f"rank {rank}: {outcomes}\n")
+    # one outcome line for the whole job (lines of several ranks could interleave)
     flag = torch.tensor([1 if ok else 0], device=device)
     dist.all_reduce(flag, op=dist.ReduceOp.MIN)
     all_ok = bool(flag.item())
