@@ -317,9 +317,11 @@ decode_front_kernel(DecodeArgs a) {
 // reference's: thread v sums columns v, v + 256, ... in order, then the 256-lane tree.
 constexpr uint32_t kRouterRowsInFlight = 6;      // at most; a launch asks for what its grid needs
 
-K3_DEVINL void cp_async_16(void *dst_shared, const void *src_global) {
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(dst_shared)),
-                 "l"(src_global)
+// (evict-first in L2: the router table is read once per token)
+K3_DEVINL void cp_async_16(void *dst_shared, const void *src_global, uint64_t policy) {
+    asm volatile("cp.async.cg.shared.global.L2::cache_hint [%0], [%1], 16, %2;" ::"r"(
+                     (uint32_t)__cvta_generic_to_shared(dst_shared)),
+                 "l"(src_global), "l"(policy)
                  : "memory");
 }
 
@@ -336,6 +338,8 @@ decode_router_kernel(DecodeArgs a) {
     // its places as soon as every block of this grid has started
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     const uint16_t *table = (const uint16_t *)a.d.router_weight;
+    uint64_t stream_once;
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(stream_once));
     bool staged = false;
     const uint32_t batch = a.rows_in_flight;
     for (uint32_t first = blockIdx.x; first < E; first += batch * G) {
@@ -344,7 +348,7 @@ decode_router_kernel(DecodeArgs a) {
             const uint32_t row = first + j * G;
             if (j < batch && row < E) {
                 for (uint32_t c = threadIdx.x; c < H / 8u; c += blockDim.x)
-                    cp_async_16(rows + (size_t)j * H + 8u * c, table + (uint64_t)row * H + 8u * c);
+                    cp_async_16(rows + (size_t)j * H + 8u * c, table + (uint64_t)row * H + 8u * c, stream_once);
             }
         }
         asm volatile("cp.async.commit_group;" ::: "memory");

@@ -332,6 +332,7 @@ decode_experts_kernel(const __grid_constant__ MxMaps maps, MxArgs a) {
         uint32_t s = 0, ph = 0, seq = 0;
         bool ok = true;
         uint32_t w = 0;
+        const uint64_t stream_once = l2_policy_evict_first();      // every weight byte is read once
         if (lane == 0) w = first_item;
         while (ok) {
             const uint32_t slot = seq % kItemSlots, parity = (seq / kItemSlots) & 1u;
@@ -359,7 +360,7 @@ decode_experts_kernel(const __grid_constant__ MxMaps maps, MxArgs a) {
                     for (uint32_t st = 0; st < steps; st++) {
                         if (!mbar_wait(&empty[s], ph ^ 1u, abort_flag)) { ok = false; break; }
                         mbar_arrive_expect_tx(&full[s], kATile);
-                        tma_load_2d(base + lay.ring + s * kATile, map, &full[s], (int32_t)(st * 128u), y);
+                        tma_load_2d_hint(base + lay.ring + s * kATile, map, &full[s], (int32_t)(st * 128u), y, stream_once);
                         if (++s == kStages) { s = 0; ph ^= 1u; }
                     }
                 }
@@ -419,6 +420,7 @@ decode_experts_kernel(const __grid_constant__ MxMaps maps, MxArgs a) {
         // ===================================== weight-scale producer: 512 K per box
         uint32_t s = 0, ph = 0;
         bool ok = true;
+        const uint64_t stream_once = l2_policy_evict_first();
         if (lane == 0) {
             prefetch_tensormap(&maps.s1);
             prefetch_tensormap(&maps.s3);
@@ -437,7 +439,8 @@ decode_experts_kernel(const __grid_constant__ MxMaps maps, MxArgs a) {
                     for (uint32_t bt = 0; bt < steps / 2u; bt++) {
                         if (!mbar_wait(&sfs_empty[s], ph ^ 1u, abort_flag)) { ok = false; break; }
                         mbar_arrive_expect_tx(&sfs_full[s], kSfaBytes);
-                        tma_load_2d(base + lay.sfa + s * kSfaBytes, map, &sfs_full[s], (int32_t)(bt * 16u), y);
+                        tma_load_2d_hint(base + lay.sfa + s * kSfaBytes, map, &sfs_full[s], (int32_t)(bt * 16u), y,
+                                         stream_once);
                         if (++s == kSfSlots) { s = 0; ph ^= 1u; }
                     }
                 }

@@ -74,11 +74,11 @@ struct RingMaps {
 };
 
 K3_DEVINL void tma_load_4d(void *dst, const void *map, uint64_t *bar, int32_t c0, int32_t c1, int32_t c2,
-                           int32_t c3) {
+                           int32_t c3, uint64_t policy) {
     asm volatile(
-        "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes "
-        "[%0], [%1, {%3, %4, %5, %6}], [%2];" ::"r"(smem_u32(dst)),
-        "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+        "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint "
+        "[%0], [%1, {%3, %4, %5, %6}], [%2], %7;" ::"r"(smem_u32(dst)),
+        "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "l"(policy)
         : "memory");
 }
 
@@ -150,6 +150,7 @@ decode_shared_ring_kernel(const __grid_constant__ RingMaps maps, RingArgs a) {
             prefetch_tensormap(&maps.down_s);
             uint32_t s = 0, ph = 0, sc[kGroups] = {0u, 0u}, sc_ph[kGroups] = {0u, 0u};
             bool ok = true;
+            const uint64_t stream_once = l2_policy_evict_first();  // every weight byte is read once
             for (uint32_t phase = 0; ok && phase < 2u; phase++) {
                 const uint32_t tasks = phase == 0 ? tasks_gu : tasks_dn;
                 const uint32_t per = phase == 0 ? per_gu : per_dn;
@@ -169,15 +170,15 @@ decode_shared_ring_kernel(const __grid_constant__ RingMaps maps, RingArgs a) {
                                                       : (up ? (const void *)&maps.up_s : (const void *)&maps.gate_s);
                         if (!mbar_wait(&sc_empty[q][sc[q]], sc_ph[q] ^ 1u, abort_flag)) { ok = false; break; }
                         mbar_arrive_expect_tx(&sc_full[q][sc[q]], 16u * scale_row_bytes);
-                        tma_load_2d(scale_slot + (q * kScaleSlots + sc[q]) * kScaleSlotBytes, smap, &sc_full[q][sc[q]],
-                                    0, row0[q]);
+                        tma_load_2d_hint(scale_slot + (q * kScaleSlots + sc[q]) * kScaleSlotBytes, smap,
+                                         &sc_full[q][sc[q]], 0, row0[q], stream_once);
                         if (++sc[q] == kScaleSlots) { sc[q] = 0; sc_ph[q] ^= 1u; }
                     }
                     for (uint32_t j = 0; ok && j < per; j++) {
                         for (uint32_t q = 0; q < kGroups && i0 + q < mine; q++) {
                             if (!mbar_wait(&empty[s], ph ^ 1u, abort_flag)) { ok = false; break; }
                             mbar_arrive_expect_tx(&full[s], kStageBytes);
-                            tma_load_4d(ring + s * kStageBytes, wmap[q], &full[s], 0, row0[q], (int32_t)j, 0);
+                            tma_load_4d(ring + s * kStageBytes, wmap[q], &full[s], 0, row0[q], (int32_t)j, 0, stream_once);
                             if (++s == kStages) { s = 0; ph ^= 1u; }
                         }
                     }

@@ -87,6 +87,24 @@ K3_DEVINL void tma_load_2d(void *dst, const void *map, uint64_t *bar, int32_t x,
         : "memory");
 }
 
+// L2 policy for data that is read once (a weight stream): its lines are the first to be
+// replaced, so the stream does not push out what other kernels left in L2 - in particular
+// not lines that would have to be written back first.
+K3_DEVINL uint64_t l2_policy_evict_first() {
+    uint64_t policy;
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(policy));
+    return policy;
+}
+
+// tma_load_2d with an L2 cache policy
+K3_DEVINL void tma_load_2d_hint(void *dst, const void *map, uint64_t *bar, int32_t x, int32_t y, uint64_t policy) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint "
+        "[%0], [%1, {%3, %4}], [%2], %5;" ::"r"(smem_u32(dst)),
+        "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y), "l"(policy)
+        : "memory");
+}
+
 // 2-D tiled prefetch global -> L2 only (no shared-memory destination, no barrier).
 K3_DEVINL void tma_prefetch_2d(const void *map, int32_t x, int32_t y) {
     asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];" ::"l"(map), "r"(x), "r"(y)
