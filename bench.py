@@ -892,8 +892,9 @@ def run_layer(args, device, peaks, torch, dist, world, rank, local_rank, MoELaye
             roofline = {"bound": "hbm", "kernel": "one-token layer", "achieved": achieved,
                         "peak": peaks["hbm_gbs"] * world, "unit": "GB/s", "frac": achieved / (peaks["hbm_gbs"] * world),
                         "traffic": DECODE_TRAFFIC_BYTES if world == 1 else None, "peak_source": peaks["source"],
-                        "note": "back to back on one token: L2 not flushed (the decode block of the default "
-                                "workload flushes it)"}
+                        "note": "steps back to back on one layer and one token, clocks sampled beside them: its "
+                                "434 MB per step exceed the L2 3.4 times; the `decode` block times single tokens "
+                                "between their own events, with four layers in turn and with a write flush"}
         cpu = cpu_baseline(cfg, tokens) if world == 1 else None
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
