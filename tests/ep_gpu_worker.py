@@ -23,7 +23,9 @@ def main():
     device = torch.device("cuda", local)
     dist.init_process_group("nccl", device_id=device)
     outcomes = []
-    for bias_mode, tokens in (("uniform", 128), ("hot4", 256)):
+    # at least 32 local tokens per rank: fewer take the matrix-vector kernels for the router and the
+    # shared expert, which differ from the single-GPU layer's tensor-core kernels in the last bits
+    for bias_mode, tokens in (("uniform", max(128, 32 * world)), ("hot4", max(256, 32 * world))):
         cfg = synth.baseline_config(hidden=1024, expert_hidden=512, experts=64, top_k=8,
                                     shared_hidden=512, bias_mode=bias_mode)
         weights = synth.make_layer(cfg, seed=5)
