@@ -446,7 +446,7 @@ def parity_check(world, rank, device, torch, dist, reduced=False):
         dist.all_reduce(m, op=dist.ReduceOp.MAX)
         worst = {"ids_exact": t[0].item() == 0.0, "near_ties": int(t[1].item()), "rel_l2": float(m.item()),
                  "tokens_checked": int(t[2].item())}
-    worst["case"] = ("hidden 1024, 64 experts, top-8, shared 512; 1 token and 40 tokens against the CPU oracle; "
+    worst["case"] = ("hidden 1024, 64 experts, top-8, shared 1024; 1 token and 40 tokens against the CPU oracle; "
                      "ids exact except near-ties (score gap < 1e-6), rel-L2 bar 1e-2")
     worst["pass"] = bool(worst["ids_exact"] and worst["rel_l2"] <= 1e-2)
     return worst
