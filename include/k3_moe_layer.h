@@ -145,6 +145,18 @@ bool k3_moe_experts_grouped_ws(const k3_moe_layer_desc *desc, void *rows_out,
                                uint32_t rows, void *workspace,
                                size_t workspace_bytes, void *stream);
 
+/* One token whose routing the host brings (the partially resident store plans
+ * on the host, k3_engine.cu:1580-1590): ids u32 [top_k] on the device index the
+ * descriptor's expert tables (slot numbers for a slot table), weights f32
+ * [top_k] on the device -> out bf16 [hidden] = the weighted sum of the expert
+ * rows in rank order.  Runs the block-scaled one-token expert kernel (three
+ * launches).  k3_moe_experts_token_workspace_bytes returns 0 for shapes that
+ * kernel does not take; the caller then uses dispatch + k3_moe_experts_grouped
+ * + k3_moe_combine. */
+size_t k3_moe_experts_token_workspace_bytes(const k3_moe_layer_desc *desc);
+bool k3_moe_experts_token(const k3_moe_layer_desc *desc, void *out, const void *x, const void *ids,
+                          const void *weights, void *workspace, size_t workspace_bytes, void *stream);
+
 /* Shared expert for `tokens` rows: out bf16 [tokens, d]; gate/up/act are
  * scratch bf16 [tokens, S] (k3_engine_prefill.inc:1530-1551). */
 bool k3_moe_shared_expert(const k3_moe_layer_desc *desc, void *out, void *gate,

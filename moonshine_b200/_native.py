@@ -127,6 +127,8 @@ SIGNATURES = {
     "k3_moe_route": (C.c_bool, [_DP, vp, vp, vp, vp, u32, vp]),
     "k3_moe_experts_grouped": (C.c_bool, [_DP, vp, vp, vp, vp, u32, vp]),
     "k3_moe_experts_workspace_bytes": (sz, [_DP, u32, u32]),
+    "k3_moe_experts_token_workspace_bytes": (sz, [_DP]),
+    "k3_moe_experts_token": (C.c_bool, [_DP, vp, vp, vp, vp, vp, sz, vp]),
     "k3_moe_experts_grouped_ws": (C.c_bool, [_DP, vp, vp, vp, vp, u32, vp, u32, vp, sz, vp]),
     "k3_moe_shared_workspace_bytes": (sz, [_DP, u32]),
     "k3_moe_shared_expert_ws": (C.c_bool, [_DP, vp, vp, vp, u32, vp, sz, vp]),

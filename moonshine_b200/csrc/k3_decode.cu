@@ -418,6 +418,22 @@ decode_router_kernel(DecodeArgs a) {
     }
 }
 
+// ----------------------------------------------------------------- terms
+// The token's E2M1 terms alone (and the expert kernel's control words cleared), for a
+// caller that brings its own routing: 32-column blocks, one per warp.
+__global__ void __launch_bounds__(256)
+decode_terms_kernel(const uint16_t *__restrict__ x, uint8_t *x_terms, uint8_t *x_sf, uint32_t *control,
+                    uint32_t hidden) {
+    const uint32_t warp = threadIdx.x / kWarp, lane = threadIdx.x % kWarp;
+    if (blockIdx.x == 0 && threadIdx.x < 64u) control[threadIdx.x] = 0u;
+    const uint32_t blk = blockIdx.x * 8u + warp;
+    if (blk < hidden / 32u) {
+        uint32_t code[kTerms], sbyte[kTerms];
+        split_block_e2m1(bf16_bits_to_float(x[blk * 32u + lane]), code, sbyte);
+        store_block_e2m1(x_terms, x_sf, hidden / 2u, hidden / 32u, blk, code, sbyte, lane);
+    }
+}
+
 // ------------------------------------------------------------------ tail
 // The layer's tail as a kernel of its own, queued behind the expert kernel with programmatic
 // serialization: its blocks take their places while the experts stream and wait for the
@@ -742,6 +758,24 @@ bool k3_decode_supported(const k3_moe_layer_desc *d) {
            (d->shared_hidden == 0 || (d->shared_hidden % 128u == 0 && d->q8_block % 32u == 0)) &&
            (size_t)(d->top_k + 1u) * d->expert_hidden * 2u + 512u <= 200u * 1024u &&
            ((d->hidden / 32u) % 2u == 0) && ((d->expert_hidden / 32u) % 2u == 0);
+}
+
+// One token's routed experts with the routing given (ids on the device, rank order): act
+// [top_k, I] and rows_out [top_k, hidden] through the block-scaled expert kernel.  False for
+// shapes it does not take (the caller runs the grouped kernels instead).
+bool k3_decode_experts_token(const k3_moe_layer_desc *d, const void *x, const void *ids, void *act, void *rows_out,
+                             void *scratch, size_t scratch_bytes, cudaStream_t stream) {
+    if (scratch == nullptr || !k3_decode_mx_supported(d) || d->top_k >= 32u || d->hidden % 32u != 0u ||
+        scratch_bytes < k3_decode_mx_scratch_bytes(d)) {
+        return false;
+    }
+    uint8_t *x_terms = nullptr, *x_sf = nullptr;
+    k3_decode_mx_vector_scratch(d, scratch, (void **)&x_terms, (void **)&x_sf);
+    decode_terms_kernel<<<(d->hidden / 32u + 7u) / 8u, 256, 0, stream>>>(
+        (const uint16_t *)x, x_terms, x_sf, (uint32_t *)k3_decode_mx_control_words(d, scratch), d->hidden);
+    if (!launch_ok()) return false;
+    return k3_decode_mx_experts(d, const_cast<void *>(ids), nullptr, nullptr, act, rows_out, scratch, nullptr, nullptr,
+                                0u, stream);
 }
 
 // buffers: see DecodeArgs; all caller-owned scratch carved from the layer workspace

@@ -53,6 +53,9 @@ bool k3_decode_layer(const k3_moe_layer_desc *desc, const void *x, void *logits,
                      size_t scratch_bytes, void *const *events, cudaStream_t stream,
                      bool combine = true);
 
+// One token's routed experts with the routing given (k3_decode.cu).
+bool k3_decode_experts_token(const k3_moe_layer_desc *desc, const void *x, const void *ids, void *act, void *rows_out,
+                             void *scratch, size_t scratch_bytes, cudaStream_t stream);
 // Block-scaled tensor-core expert products for one token (k3_decode_mx.cu).
 bool k3_decode_mx_supported(const k3_moe_layer_desc *desc);
 size_t k3_decode_mx_scratch_bytes(const k3_moe_layer_desc *desc);

@@ -337,6 +337,28 @@ extern "C" bool k3_moe_experts_grouped(const k3_moe_layer_desc *d, void *rows_ou
                                d->local_expert_count, false, (cudaStream_t)stream);
 }
 
+// One token with the routing given: the block-scaled one-token expert kernel, then the
+// weighted sum in rank order.  Workspace: act | rows_out | the kernel's scratch.
+extern "C" size_t k3_moe_experts_token_workspace_bytes(const k3_moe_layer_desc *d) {
+    if (!desc_ok(d) || !slot_pointers_aligned(d) || !k3_decode_mx_supported(d) || d->top_k >= 32u) return 0;
+    const size_t act = ((size_t)d->top_k * d->expert_hidden * 2u + 255u) & ~(size_t)255u;
+    const size_t rows = ((size_t)d->top_k * d->hidden * 2u + 255u) & ~(size_t)255u;
+    return act + rows + k3_decode_mx_scratch_bytes(d) + 512u;
+}
+
+extern "C" bool k3_moe_experts_token(const k3_moe_layer_desc *d, void *out, const void *x, const void *ids,
+                                     const void *weights, void *workspace, size_t workspace_bytes, void *stream) {
+    const size_t need = k3_moe_experts_token_workspace_bytes(d);
+    if (need == 0 || !out || !x || !ids || !weights || !workspace || workspace_bytes < need) return false;
+    uint8_t *p = (uint8_t *)(((uintptr_t)workspace + 255u) & ~(uintptr_t)255u);
+    const size_t act_bytes = ((size_t)d->top_k * d->expert_hidden * 2u + 255u) & ~(size_t)255u;
+    const size_t rows_bytes = ((size_t)d->top_k * d->hidden * 2u + 255u) & ~(size_t)255u;
+    void *act = p, *rows_out = p + act_bytes, *scratch = p + act_bytes + rows_bytes;
+    const size_t scratch_bytes = workspace_bytes - (size_t)((uint8_t *)scratch - (uint8_t *)workspace);
+    if (!k3_decode_experts_token(d, x, ids, act, rows_out, scratch, scratch_bytes, (cudaStream_t)stream)) return false;
+    return k3_moe_combine(out, rows_out, nullptr, weights, nullptr, 1u, d->top_k, d->hidden, stream);
+}
+
 extern "C" size_t k3_moe_experts_workspace_bytes(const k3_moe_layer_desc *d, uint32_t rows,
                                                  uint32_t source_rows) {
     if (!desc_ok(d) || rows == 0 || !slot_pointers_aligned(d) || !k3_grouped_mx_supported(d, rows)) return 0;

@@ -182,6 +182,9 @@ class PartialStore:
         self.rows_in = torch.empty((k, d), dtype=torch.bfloat16, device=self.device)
         self.act = torch.empty((k, i), dtype=torch.bfloat16, device=self.device)
         self.rows_out = torch.empty((k, d), dtype=torch.bfloat16, device=self.device)
+        # the one-token expert kernel takes slot numbers as expert ids (shapes it handles)
+        token_bytes = ops.k3_moe_experts_token_workspace_bytes(self.desc)
+        self.token_ws = (torch.empty(token_bytes, dtype=torch.uint8, device=self.device) if token_bytes else None)
         self.bytes_admitted = 0
 
     def token(self, x, expert_ids, weights):
@@ -209,13 +212,18 @@ class PartialStore:
                     raise StoreError("expert neither resident nor admitted: fewer slots than experts per token")
                 self.slot_ids_host[0, rank] = slot - self.layer * self.slots
             self.slot_ids.copy_(self.slot_ids_host, non_blocking=True)
-            ok = ops.k3_moe_dispatch_build(self.offsets, self.sorted_route, self.sorted_token, self.inv_perm,
-                                           self.slot_ids, 1, k, self.slots, self.dispatch_ws,
-                                           self.dispatch_ws.numel())
-            ok = ok and ops.k3_rocm_gather_rows_bf16(self.rows_in, x, self.sorted_token, k, d)
-            ok = ok and ops.k3_moe_experts_grouped(self.desc, self.rows_out, self.act, self.rows_in, self.offsets, k)
             out = torch.empty((1, d), dtype=torch.bfloat16, device=self.device)
-            ok = ok and ops.k3_moe_combine(out, self.rows_out, self.inv_perm, weights, None, 1, k, d)
+            if self.token_ws is not None:
+                # the block-scaled one-token expert kernel, addressed by slot number
+                ok = ops.k3_moe_experts_token(self.desc, out, x, self.slot_ids, weights, self.token_ws,
+                                              self.token_ws.numel())
+            else:
+                ok = ops.k3_moe_dispatch_build(self.offsets, self.sorted_route, self.sorted_token, self.inv_perm,
+                                               self.slot_ids, 1, k, self.slots, self.dispatch_ws,
+                                               self.dispatch_ws.numel())
+                ok = ok and ops.k3_rocm_gather_rows_bf16(self.rows_in, x, self.sorted_token, k, d)
+                ok = ok and ops.k3_moe_experts_grouped(self.desc, self.rows_out, self.act, self.rows_in, self.offsets, k)
+                ok = ok and ops.k3_moe_combine(out, self.rows_out, self.inv_perm, weights, None, 1, k, d)
             if not ok:
                 raise StoreError("expert products failed")
             # the pinned id buffer is rewritten by the next token

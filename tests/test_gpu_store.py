@@ -16,18 +16,25 @@ from moonshine_b200.layer import MoELayer, bf16_tensor_to_bits             # noq
 from moonshine_b200.store import PartialStore, SlotCache, pack_spans       # noqa: E402
 
 
-def resident_token(layer: MoELayer, x, ids_dev, weights):
-    """The store's kernel sequence on the fully resident table."""
+def resident_token(layer: MoELayer, x, ids_dev, weights, grouped=False):
+    """The store's kernel sequence on the fully resident table: the one-token expert kernel
+    where the shape allows it (as the store does), else (or with ``grouped``) dispatch +
+    grouped products + combine."""
     cfg, dev = layer.cfg, layer.device
     k, d, e = cfg["top_k"], cfg["hidden"], cfg["experts"]
     i32 = dict(dtype=torch.int32, device=dev)
+    out = torch.empty((1, d), dtype=torch.bfloat16, device=dev)
+    token_bytes = ops.k3_moe_experts_token_workspace_bytes(layer.desc)
+    if token_bytes and not grouped:
+        ws = torch.empty(token_bytes, dtype=torch.uint8, device=dev)
+        assert ops.k3_moe_experts_token(layer.desc, out, x, ids_dev, weights, ws, ws.numel())
+        return out
     offsets = torch.empty(e + 1, **i32)
     sorted_route, sorted_token, inv_perm = (torch.empty(k, **i32) for _ in range(3))
     ws = torch.empty(max(1, ops.k3_moe_dispatch_workspace_bytes(1, k, e)), dtype=torch.uint8, device=dev)
     rows_in = torch.empty((k, d), dtype=torch.bfloat16, device=dev)
     act = torch.empty((k, cfg["expert_hidden"]), dtype=torch.bfloat16, device=dev)
     rows_out = torch.empty((k, d), dtype=torch.bfloat16, device=dev)
-    out = torch.empty((1, d), dtype=torch.bfloat16, device=dev)
     assert ops.k3_moe_dispatch_build(offsets, sorted_route, sorted_token, inv_perm, ids_dev, 1, k, e, ws, ws.numel())
     assert ops.k3_rocm_gather_rows_bf16(rows_in, x, sorted_token, k, d)
     assert ops.k3_moe_experts_grouped(layer.desc, rows_out, act, rows_in, offsets, k)
@@ -53,6 +60,14 @@ def test_store_matches_resident_table_over_a_trace():
         torch.cuda.synchronize()
         assert mask == int(want_masks[i]), i
         assert np.array_equal(bf16_tensor_to_bits(got), bf16_tensor_to_bits(want)), i
+        if i < 4:
+            # the one-token kernel and the grouped kernels are two schedules of the same products
+            assert store.token_ws is not None
+            slow = resident_token(layer, x, ids_dev, w, grouped=True)
+            a = bf16_tensor_to_bits(got).astype(np.uint32) << 16
+            b = bf16_tensor_to_bits(slow).astype(np.uint32) << 16
+            a, b = a.view(np.float32).astype(np.float64), b.view(np.float32).astype(np.float64)
+            assert np.sqrt(((a - b) ** 2).sum() / (b ** 2).sum()) <= 2e-3
     st = store.cache.stats()
     assert st["evictions"] > 0 and st["hits"] > 0
     assert store.bytes_admitted == st["admissions"] * store.span_bytes
