@@ -33,6 +33,9 @@ struct LatentWorkspace {
     uint16_t *latent, *rows_in, *act, *rows_out, *routed, *routed_norm, *routed_full;
     uint16_t *sh_gate, *sh_up, *sh_act, *sh_out;
     void *mx_ws, *sh_ws, *proj_w;
+    uint16_t *token_act;           // one token through the one-token expert kernel: activation rows
+    void *token_scratch;           //   and the kernel's scratch (null: that kernel does not take the shape)
+    size_t token_scratch_bytes;
     size_t mx_bytes, sh_bytes, total;
 };
 
@@ -80,6 +83,11 @@ LatentWorkspace carve(const k3_moe_latent_desc *d, uint32_t tokens, void *base) 
     w.mx_bytes = k3_grouped_mx_supported(&e, (uint32_t)routes)
                      ? k3_grouped_mx_workspace_bytes(&e, (uint32_t)routes, tokens) : 0;
     w.mx_ws = take(w.mx_bytes);
+    if (tokens == 1u && k3_decode_mx_supported(&e) && e.top_k < 32u) {
+        w.token_act = (uint16_t *)take(routes * I * 2u);
+        w.token_scratch_bytes = k3_decode_mx_scratch_bytes(&e) + 256u;
+        w.token_scratch = take(w.token_scratch_bytes);
+    }
     if (w.mx_bytes == 0) {              // fallback path gathers bf16 rows and keeps the activation
         w.rows_in = (uint16_t *)take(routes * L * 2u);
         w.act = (uint16_t *)take(routes * I * 2u);
@@ -132,11 +140,20 @@ extern "C" bool k3_moe_latent_layer_forward(const k3_moe_latent_desc *d, void *o
                             : k3_moe_shared_expert(&l, w.sh_out, w.sh_gate, w.sh_up, w.sh_act, x, tokens, stream);
         if (!ok) return false;
     }
-    if (!k3_moe_dispatch_build(w.offsets, w.sorted_route, w.sorted_token, w.inv_perm, w.ids, tokens, l.top_k,
-                               l.expert_count, w.dispatch_ws, w.dispatch_bytes, stream)) {
+    // one token: its 16 experts through the block-scaled one-token expert kernel on the latent
+    // vector, rows in rank order (no dispatch); shapes that kernel refuses fall through
+    const bool token_path = tokens == 1u && w.token_scratch != nullptr && workspace != nullptr &&
+                            k3_decode_experts_token(&e, w.latent, w.ids, w.token_act, w.rows_out, w.token_scratch,
+                                                    w.token_scratch_bytes, stream);
+    if (token_path) {
+        // nothing to group
+    } else if (!k3_moe_dispatch_build(w.offsets, w.sorted_route, w.sorted_token, w.inv_perm, w.ids, tokens, l.top_k,
+                                      l.expert_count, w.dispatch_ws, w.dispatch_bytes, stream)) {
         return false;
     }
-    if (w.mx_bytes != 0) {
+    if (token_path) {
+        // rows_out already holds the expert rows
+    } else if (w.mx_bytes != 0) {
         if (!k3_grouped_mx_experts(&e, w.rows_out, nullptr, w.latent, w.sorted_token, tokens, w.offsets, routes,
                                    w.mx_ws, stream)) {
             return false;
@@ -148,7 +165,8 @@ extern "C" bool k3_moe_latent_layer_forward(const k3_moe_latent_desc *d, void *o
         }
     }
     // weighted sum in rank order, norm, projection back to the model width, shared output
-    if (!k3_moe_combine(w.routed, w.rows_out, w.inv_perm, w.weights, nullptr, tokens, l.top_k, L, stream) ||
+    if (!k3_moe_combine(w.routed, w.rows_out, token_path ? nullptr : w.inv_perm, w.weights, nullptr, tokens, l.top_k, L,
+                        stream) ||
         !k3_rocm_rms_norm_bf16(w.routed_norm, w.routed, d->norm_weight, tokens, L, d->norm_epsilon, stream)) {
         return false;
     }
