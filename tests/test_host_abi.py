@@ -85,3 +85,11 @@ def test_invalid_arguments_return_false_without_a_device(native):
     assert lib.k3_moe_selftest_bounded_wait(0, None, None) is False
     assert lib.k3_moe_phase_stats_add(None, None) is False
     assert lib.k3_moe_version().startswith(b"k3moe")
+    # one token with host-given routing: null descriptor or pointers
+    assert lib.k3_moe_experts_token_workspace_bytes(None) == 0
+    assert lib.k3_moe_experts_token(None, p, p, p, p, p, 1 << 20, None) is False
+    # tensor-pipe peak loop: N extent out of range, or not a multiple of 16
+    assert lib.k3_moe_peak_launch_n(1, 8, 10, None, None) is False
+    assert lib.k3_moe_peak_launch_n(1, 272, 10, None, None) is False
+    assert lib.k3_moe_peak_launch_n(1, 40, 10, None, None) is False
+    assert lib.k3_moe_peak_launch_n(3, 128, 10, None, None) is False
