@@ -5,8 +5,8 @@
 // beside everything that depends on the routing.  Next to the routed experts' TMA stream
 // a kernel that fetches its weights with ordinary loads is starved by the memory system
 // (it has a tenth of the bytes in flight), so this one streams too: a producer thread
-// brings 16 KB stages into a shared-memory ring with tiled bulk copies, eight consumer
-// warps take the int8 values from shared memory and run the same tensor-core Q8
+// brings 16 KB stages into a shared-memory ring with tiled bulk copies, two groups of eight
+// consumer warps take the int8 values from shared memory and run the same tensor-core Q8
 // arithmetic as the row kernels (k3_gemv.cuh: int8 -> f16 exactly, block-diagonal vector
 // operand, one fp32 FMA per scale group).  A few CTAs, one per SM, hold their SMs from
 // the start of the layer until the shared expert is done; the expert kernel's CTAs for
@@ -20,7 +20,6 @@
 // decode_shared_down_kernel, so either path gives the same bits.  Stage j of a task holds
 // step j of every warp: one 4-D box {128 bytes, 16 rows, 1 step, 8 warps}, 128-byte
 // swizzle, which puts each warp's 16 x 128 tile in 2 KB of its own.
-#include "k3_decode_tail.cuh"
 #include "k3_gemv.cuh"
 #include "k3_grouped.h"
 #include "k3_moe_ops.h"
@@ -88,8 +87,9 @@ K3_DEVINL void consumer_sync() { asm volatile("bar.sync 1, %0;" ::"n"(kConsumers
 // warps 17 and 18 the groups' finishers.  The CTA's tasks of a phase are c, c + n, ...;
 // group q takes every second one starting with the q-th, and the producer interleaves the
 // stages of the two tasks of a pair, so both groups always have stages in the ring.  A
-// finisher adds the eight partial sums of a finished task, stores the 16 results and (down
-// phase) counts the arrival for the layer's tail, off the consumers' path.
+// finisher adds the eight partial sums of a finished task and stores the 16 results, off
+// the consumers' path.  The layer's tail reads sh_out after this grid has finished (it is
+// a kernel of its own that waits for every grid in front of it).
 __global__ void __launch_bounds__(kThreads, 1)
 decode_shared_ring_kernel(const __grid_constant__ RingMaps maps, RingArgs a) {
     extern __shared__ unsigned char smem_raw[];
