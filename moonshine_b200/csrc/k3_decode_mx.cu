@@ -22,11 +22,16 @@
 //   1, 11   MMA issuers: 4 MMAs of K=64 per stage, even / odd stages, own accumulators
 //   2-5     scale writers: weight scales shared memory -> tensor memory, term scales too
 //   6-9     epilogue: tcgen05.ld of the term columns, sum, bf16; G: activation, its
-//           E2M1 terms, arrival; D: output row and the layer's tail
+//           E2M1 terms, arrival; D: output row (and, where the layer's tail has no
+//           kernel of its own, its arrival for the tail)
 //   10      weight-scale producer (TMA, 512 K per box)
 //   12      term producer: the token's terms once (they serve every G item), then per D
 //           item the rank's activation terms and scales, after its arrival count is full
-// Every wait is bounded (see k3_tc_ptx.cuh).
+// The kernel is launched behind the router rows' kernel with programmatic serialization.
+// In its prologue every CTA waits for that kernel (for its count of finished blocks when a
+// longer-running grid sits in front of it), routes the token itself (k3_route_block.cuh)
+// and draws its first item under the routing.  Weight and scale loads carry the
+// evict-first L2 policy.  Every wait is bounded (see k3_tc_ptx.cuh).
 #include "k3_decode_tail.cuh"
 #include "k3_e2m1_terms.cuh"
 #include "k3_grouped.h"
